@@ -1,0 +1,141 @@
+"""ctypes binding of the C ABI declared in ``include/cumm_b200.h``.
+
+The shared library is built in-tree (``cumm_b200/libcumm_b200.so``) by ``cumm_b200.build``.
+There is no fallback: if the library is missing or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+_HERE = Path(__file__).resolve().parent
+LIB_PATH = _HERE / "libcumm_b200.so"
+
+CB2_OK = 0
+CB2_ERR_INVALID_ARG = -1
+CB2_ERR_RUNTIME = -2
+CB2_ERR_UNSUPPORTED = -3
+CB2_ERR_CUDA = -4
+
+EXPORTED_SYMBOLS = (
+    "cb2_gemm_run",
+    "cb2_conv_run",
+    "cb2_gemm_workspace_size",
+    "cb2_conv_workspace_size",
+    "cb2_tile_m",
+    "cb2_last_error",
+    "cb2_device_status",
+    "cb2_launch_count",
+)
+
+
+class GemmArgs(ctypes.Structure):
+    """``cb2_gemm_args``."""
+    _fields_ = [
+        ("m", ctypes.c_int), ("n", ctypes.c_int), ("k", ctypes.c_int),
+        ("ptr_A", ctypes.c_void_p), ("ptr_B", ctypes.c_void_p), ("ptr_D", ctypes.c_void_p),
+        ("ptr_C", ctypes.c_void_p),
+        ("stride_A", ctypes.c_int64), ("stride_B", ctypes.c_int64),
+        ("stride_C", ctypes.c_int64), ("stride_D", ctypes.c_int64),
+        ("indiceA", ctypes.c_void_p), ("indiceBorC", ctypes.c_void_p), ("indiceD", ctypes.c_void_p),
+        ("alpha", ctypes.c_float), ("beta", ctypes.c_float),
+        ("act_alpha", ctypes.c_float), ("act_beta", ctypes.c_float),
+        ("act_type", ctypes.c_int),
+        ("split_k_slices", ctypes.c_int),
+        ("workspace", ctypes.c_void_p),
+        ("workspace_bytes", ctypes.c_size_t),
+        ("dtype_a", ctypes.c_int), ("dtype_b", ctypes.c_int), ("dtype_c", ctypes.c_int),
+        ("trans_a", ctypes.c_int), ("trans_b", ctypes.c_int), ("trans_c", ctypes.c_int),
+        ("shuffle_type", ctypes.c_int),
+        ("d_is_vector", ctypes.c_int),
+        ("rows_A", ctypes.c_int), ("rows_B", ctypes.c_int),
+    ]
+
+
+class ConvArgs(ctypes.Structure):
+    """``cb2_conv_args``."""
+    _fields_ = [
+        ("ptr_A", ctypes.c_void_p), ("ptr_B", ctypes.c_void_p), ("ptr_D", ctypes.c_void_p),
+        ("ptr_C", ctypes.c_void_p),
+        ("alpha", ctypes.c_float), ("beta", ctypes.c_float),
+        ("act_alpha", ctypes.c_float), ("act_beta", ctypes.c_float),
+        ("act_type", ctypes.c_int),
+        ("split_k_slices", ctypes.c_int),
+        ("workspace", ctypes.c_void_p),
+        ("workspace_bytes", ctypes.c_size_t),
+        ("mask_ptr", ctypes.c_void_p),
+        ("mask_out_ptr", ctypes.c_void_p),
+        ("indice_ptr", ctypes.c_void_p),
+        ("mask_argsort_ptr", ctypes.c_void_p),
+        ("mask_filter", ctypes.c_uint32),
+        ("reverse_mask", ctypes.c_int),
+        ("mask_width", ctypes.c_int),
+        ("ndim", ctypes.c_int), ("N", ctypes.c_int), ("C", ctypes.c_int), ("K", ctypes.c_int),
+        ("kernel_volume", ctypes.c_int),
+        ("mode", ctypes.c_int),
+        ("groups", ctypes.c_int),
+        ("d_is_bias", ctypes.c_int),
+        ("bias_pointer", ctypes.c_void_p),
+        ("scale_pointer", ctypes.c_void_p),
+        ("op_type", ctypes.c_int),
+        ("dtype_a", ctypes.c_int), ("dtype_b", ctypes.c_int), ("dtype_c", ctypes.c_int),
+        ("is_int8_inference", ctypes.c_int),
+        ("rows_A", ctypes.c_int), ("rows_B", ctypes.c_int),
+        ("mask_words", ctypes.c_int),
+    ]
+
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the CUDA library; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: the CUDA extension has not been built "
+            "(run `python -c 'import cumm_b200.build as b; b.build()'`). There is no CPU fallback.")
+    L = ctypes.CDLL(str(LIB_PATH))
+    L.cb2_gemm_run.restype = ctypes.c_int
+    L.cb2_gemm_run.argtypes = [ctypes.POINTER(GemmArgs), ctypes.c_void_p]
+    L.cb2_conv_run.restype = ctypes.c_int
+    L.cb2_conv_run.argtypes = [ctypes.POINTER(ConvArgs), ctypes.c_void_p]
+    L.cb2_gemm_workspace_size.restype = ctypes.c_size_t
+    L.cb2_gemm_workspace_size.argtypes = [ctypes.POINTER(GemmArgs)]
+    L.cb2_conv_workspace_size.restype = ctypes.c_size_t
+    L.cb2_conv_workspace_size.argtypes = [ctypes.POINTER(ConvArgs)]
+    L.cb2_tile_m.restype = ctypes.c_int
+    L.cb2_last_error.restype = ctypes.c_char_p
+    L.cb2_device_status.restype = ctypes.c_int
+    L.cb2_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
+    L.cb2_launch_count.restype = ctypes.c_uint64
+    _lib = L
+    return L
+
+
+def last_error() -> str:
+    return load().cb2_last_error().decode("utf-8", "replace")
+
+
+def raise_for(rc: int) -> None:
+    """Translate a return code into the exception class the reference would raise
+    (std::invalid_argument -> ValueError, std::runtime_error -> RuntimeError)."""
+    if rc == CB2_OK:
+        return
+    msg = last_error()
+    if rc == CB2_ERR_INVALID_ARG:
+        raise ValueError(msg)
+    raise RuntimeError(msg)
+
+
+def device_status() -> int:
+    """Synchronise the current device and return (and clear) the kernels' status word."""
+    v = ctypes.c_int(0)
+    raise_for(load().cb2_device_status(ctypes.byref(v)))
+    return v.value
+
+
+def launch_count() -> int:
+    return int(load().cb2_launch_count())

@@ -1,0 +1,534 @@
+// C ABI of the library: argument validation (the checks of the reference's host
+// prologues, cumm/gemm/nvrtc_code.py:34-146 and cumm/conv/nvrtc_code.py:20-260), kernel
+// selection, TMA descriptor set-up and launches.  No CPU compute path exists here: when
+// no kernel fits the descriptor the call fails with CB2_ERR_UNSUPPORTED.
+#include "../../include/cumm_b200.h"
+#include "rowconv_kernel.cuh"
+#include "wgrad_kernel.cuh"
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+namespace {
+
+using namespace cb2;
+
+thread_local std::string g_err;
+std::atomic<uint64_t> g_launches{0};
+
+int set_err(int code, const char *fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_err = buf;
+  return code;
+}
+
+#define CB2_CHECK_ARG(cond, ...)                                                                   \
+  do {                                                                                             \
+    if (!(cond))                                                                                   \
+      return set_err(CB2_ERR_INVALID_ARG, __VA_ARGS__);                                            \
+  } while (0)
+#define CB2_CHECK_RT(cond, ...)                                                                    \
+  do {                                                                                             \
+    if (!(cond))                                                                                   \
+      return set_err(CB2_ERR_RUNTIME, __VA_ARGS__);                                                \
+  } while (0)
+#define CB2_CUDA(expr)                                                                             \
+  do {                                                                                             \
+    cudaError_t e__ = (expr);                                                                      \
+    if (e__ != cudaSuccess)                                                                        \
+      return set_err(CB2_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__));               \
+  } while (0)
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceState {
+  bool ready = false;
+  int num_sms = 0;
+  int *status = nullptr;
+};
+DeviceState g_dev[kMaxDevices];
+std::mutex g_mu;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+int get_device(DeviceState **out) {
+  int dev = 0;
+  CB2_CUDA(cudaGetDevice(&dev));
+  CB2_CHECK_RT(dev >= 0 && dev < kMaxDevices, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_mu);
+  DeviceState &st = g_dev[dev];
+  if (!st.ready) {
+    cudaDeviceProp prop;
+    CB2_CUDA(cudaGetDeviceProperties(&prop, dev));
+    CB2_CHECK_RT(prop.major == 10, "cumm_b200 kernels are built for sm_100a only; device %d is sm_%d%d",
+                 dev, prop.major, prop.minor);
+    st.num_sms = prop.multiProcessorCount;
+    CB2_CUDA(cudaMalloc(&st.status, 64));
+    CB2_CUDA(cudaMemset(st.status, 0, 64));
+    st.ready = true;
+  }
+  if (!g_encode) {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    CB2_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+    CB2_CHECK_RT(fn != nullptr && q == cudaDriverEntryPointSuccess, "cuTensorMapEncodeTiled not available");
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  *out = &st;
+  return CB2_OK;
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// 3-D tensor map over a weight-like tensor [outer, mid, inner] (inner contiguous).
+int make_weight_map(CUtensorMap *map, const void *ptr, int es, uint64_t inner, uint64_t mid, uint64_t outer,
+                    uint64_t mid_stride_elems, uint64_t outer_stride_elems, uint32_t box_inner,
+                    uint32_t box_outer) {
+  cuuint64_t dims[3] = {inner, mid, outer};
+  cuuint64_t strides[2] = {mid_stride_elems * es, outer_stride_elems * es};
+  cuuint32_t box[3] = {box_inner, 1, box_outer};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CB2_CHECK_ARG(aligned16(ptr), "weight pointer must be 16-byte aligned");
+  CB2_CHECK_ARG(strides[0] % 16 == 0 && strides[1] % 16 == 0, "weight strides must be multiples of 16 bytes");
+  CUresult r = g_encode(map, es == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3,
+                        const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CB2_CHECK_RT(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return CB2_OK;
+}
+
+template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN>
+int launch_rowconv_inst(const CUtensorMap &map, const RowConvParams &p, int grid_x, int grid_y,
+                        cudaStream_t stream) {
+  using Cfg = RowConvCfg<KIND, NATOM_K, BLOCK_N, B_MN>;
+  auto kern = rowconv_kernel<KIND, NATOM_K, BLOCK_N, B_MN>;
+  static std::atomic<uint64_t> configured{0};  // bit per device
+  int dev = 0;
+  CB2_CUDA(cudaGetDevice(&dev));
+  if (!(configured.load() & (1ull << dev))) {
+    CB2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    configured.fetch_or(1ull << dev);
+  }
+  kern<<<dim3(grid_x, grid_y), Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(map, p);
+  CB2_CUDA(cudaGetLastError());
+  g_launches.fetch_add(1);
+  return CB2_OK;
+}
+
+struct RowConvPlan {
+  int kind;     // 0 f16, 1 s8
+  int natom_k;  // 1 or 2
+  int block_n;  // 64 or 128
+  bool b_mn;
+};
+
+int plan_rowconv(int kind, int red, int nn, bool b_mn, RowConvPlan *plan) {
+  plan->kind = kind;
+  plan->b_mn = b_mn;
+  const int atom = kind == 0 ? 64 : 128;
+  plan->natom_k = (kind == 0 && red > atom) ? 2 : 1;
+  plan->block_n = nn <= 64 ? 64 : 128;
+  if (kind == 1 && b_mn)
+    return set_err(CB2_ERR_UNSUPPORTED, "int8 is supported for forward only (the reference skips 1-byte "
+                                        "dtypes for backward ops)");
+  return CB2_OK;
+}
+
+int launch_rowconv(const RowConvPlan &pl, const CUtensorMap &map, const RowConvParams &p, int gx, int gy,
+                   cudaStream_t s) {
+#define CB2_INST(K, A, N, M)                                                                      \
+  if (pl.kind == K && pl.natom_k == A && pl.block_n == N && pl.b_mn == M)                          \
+    return launch_rowconv_inst<K, A, N, M>(map, p, gx, gy, s);
+  CB2_INST(0, 1, 64, false)
+  CB2_INST(0, 1, 128, false)
+  CB2_INST(0, 2, 64, false)
+  CB2_INST(0, 2, 128, false)
+  CB2_INST(0, 1, 64, true)
+  CB2_INST(0, 1, 128, true)
+  CB2_INST(0, 2, 64, true)
+  CB2_INST(0, 2, 128, true)
+  CB2_INST(1, 1, 64, false)
+  CB2_INST(1, 1, 128, false)
+#undef CB2_INST
+  return set_err(CB2_ERR_UNSUPPORTED, "no row-conv kernel for kind=%d natom=%d block_n=%d b_mn=%d", pl.kind,
+                 pl.natom_k, pl.block_n, (int)pl.b_mn);
+}
+
+// Common tail of the row-gather launches (forward, backward input, ShuffleAC GEMM).
+int run_rowconv(DeviceState *dev, RowConvParams &p, int kind, bool b_mn, const void *w_ptr, uint64_t w_inner,
+                uint64_t w_mid, uint64_t w_outer, uint64_t w_mid_stride, uint64_t w_outer_stride,
+                cudaStream_t stream) {
+  RowConvPlan pl;
+  int rc = plan_rowconv(kind, p.red, p.nn, b_mn, &pl);
+  if (rc)
+    return rc;
+  const int es = kind == 0 ? 2 : 1;
+  const int atom = 128 / es;
+  const int kred = pl.natom_k * atom;
+  CB2_CHECK_ARG(p.n_rows >= 0, "negative row count");
+  if (p.n_rows == 0)
+    return CB2_OK;
+  CB2_CHECK_ARG((p.red * es) % 16 == 0, "reduction width %d is not a multiple of 16 bytes", p.red);
+  CB2_CHECK_ARG((p.nn * es) % 16 == 0, "output width %d is not a multiple of 16 bytes", p.nn);
+  CB2_CHECK_ARG((p.lda * es) % 16 == 0 && (p.ldo * es) % 16 == 0, "row strides must be multiples of 16 bytes");
+  CB2_CHECK_ARG(aligned16(p.a) && aligned16(p.out), "operand pointers must be 16-byte aligned");
+  if (p.src_mode == kSrcRows)
+    CB2_CHECK_ARG(aligned16(p.src) && (p.lds * es) % 16 == 0, "source rows must be 16-byte aligned");
+  CUtensorMap map;
+  rc = make_weight_map(&map, w_ptr, es, w_inner, w_mid, w_outer, w_mid_stride, w_outer_stride, atom,
+                       b_mn ? kred : pl.block_n);
+  if (rc)
+    return rc;
+  p.b_lbo = static_cast<uint32_t>(kred * 128);
+  p.b_sbo = 1024;
+  if (const char *v = getenv("CUMM_B200_DEBUG_SWAP_BDESC")) {
+    // Debug aid: exchange the two descriptor offsets of the MN-major weight tile.
+    if (v[0] == '1') {
+      p.b_lbo = 1024;
+      p.b_sbo = static_cast<uint32_t>(kred * 128);
+    }
+  }
+  p.status = dev->status;
+  const int ntiles = (p.n_rows + 127) / 128;
+  const int gy = (p.nn + pl.block_n - 1) / pl.block_n;
+  int gx = dev->num_sms / gy;
+  if (gx < 1)
+    gx = 1;
+  if (gx > ntiles)
+    gx = ntiles;
+  return launch_rowconv(pl, map, p, gx, gy, stream);
+}
+
+// ---------------------------------------------------------------- weight gradient
+struct WgradLayout {
+  int block_n, gy, G, slots;
+  size_t off_flags, off_partials, total;
+};
+
+void wgrad_layout(int num_sms, int m_total, int n_total, WgradLayout *L) {
+  L->block_n = n_total <= 64 ? 64 : 128;
+  const int mt = (m_total + 127) / 128, nt = (n_total + L->block_n - 1) / L->block_n;
+  L->gy = mt * nt;
+  L->G = num_sms / L->gy;
+  if (L->G < 1)
+    L->G = 1;
+  L->slots = L->G + 32;
+  L->off_flags = 512;
+  size_t flags_bytes = ((size_t)L->slots * L->gy * 4 + 255) / 256 * 256;
+  L->off_partials = L->off_flags + flags_bytes;
+  L->total = L->off_partials + (size_t)L->slots * L->gy * 128 * L->block_n * 4;
+}
+
+template <int BLOCK_N> int launch_wgrad_inst(const WgradParams &p, int gx, int gy, cudaStream_t stream) {
+  using Cfg = WgradCfg<BLOCK_N>;
+  auto kern = wgrad_kernel<BLOCK_N>;
+  static std::atomic<uint64_t> configured{0};
+  int dev = 0;
+  CB2_CUDA(cudaGetDevice(&dev));
+  if (!(configured.load() & (1ull << dev))) {
+    CB2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    configured.fetch_or(1ull << dev);
+  }
+  kern<<<dim3(gx, gy), Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(p);
+  CB2_CUDA(cudaGetLastError());
+  g_launches.fetch_add(1);
+  return CB2_OK;
+}
+
+int run_wgrad(DeviceState *dev, WgradParams &p, void *workspace, size_t workspace_bytes, void *out,
+              const void *src, long long ldo, long long f_stride, float alpha, float beta, int out_f32,
+              cudaStream_t stream) {
+  WgradLayout L;
+  wgrad_layout(dev->num_sms, p.m_total, p.n_total, &L);
+  CB2_CHECK_RT(workspace != nullptr && workspace_bytes >= L.total, "workspace at least %zu bytes.", L.total);
+  CB2_CHECK_ARG(reinterpret_cast<uintptr_t>(workspace) % 256 == 0, "workspace must be 256-byte aligned");
+  CB2_CHECK_ARG(p.m_total % 8 == 0 && p.n_total % 8 == 0, "channel counts must be multiples of 8");
+  CB2_CHECK_ARG((p.ld_dout * 2) % 16 == 0 && (p.ld_x * 2) % 16 == 0, "row strides must be multiples of 16 bytes");
+  CB2_CHECK_ARG(aligned16(p.dout) && aligned16(p.x), "operand pointers must be 16-byte aligned");
+  uint8_t *ws = reinterpret_cast<uint8_t *>(workspace);
+  p.sched = reinterpret_cast<int *>(ws);
+  p.unit_flags = reinterpret_cast<int *>(ws + L.off_flags);
+  p.partials = reinterpret_cast<float *>(ws + L.off_partials);
+  p.status = dev->status;
+  const int ntiles = (p.n_rows + 127) / 128;
+  int rc;
+  if (ntiles > 0) {
+    rc = (L.block_n == 64) ? launch_wgrad_inst<64>(p, L.G, L.gy, stream)
+                           : launch_wgrad_inst<128>(p, L.G, L.gy, stream);
+    if (rc)
+      return rc;
+  } else {
+    CB2_CUDA(cudaMemsetAsync(ws, 0, 512, stream));
+  }
+  WgradReduceParams r;
+  r.partials = p.partials;
+  r.sched = p.sched;
+  r.unit_flags = p.unit_flags;
+  r.out = out;
+  r.src = src ? src : out;
+  r.ldo = ldo;
+  r.f_stride = f_stride;
+  r.m_total = p.m_total;
+  r.n_total = p.n_total;
+  r.kv = p.kv;
+  r.block_n = L.block_n;
+  r.gy = L.gy;
+  r.mask_filter = p.mode == kWgradMaskConv ? p.mask_filter : 1u;
+  r.alpha = alpha;
+  r.beta = beta;
+  r.out_f32 = out_f32;
+  const long long total = (long long)p.m_total * p.n_total;
+  int bx = (int)((total + 255) / 256);
+  if (bx > 64)
+    bx = 64;
+  wgrad_reduce_kernel<<<dim3(bx, p.kv), 256, 0, stream>>>(r);
+  CB2_CUDA(cudaGetLastError());
+  g_launches.fetch_add(1);
+  return CB2_OK;
+}
+
+int kind_of(int da, int db, int dc, int is_int8, bool allow_f32_out) {
+  if (da == CB2_DTYPE_F16 && db == CB2_DTYPE_F16 &&
+      (dc == CB2_DTYPE_F16 || (allow_f32_out && dc == CB2_DTYPE_F32)) && !is_int8)
+    return 0;
+  if (da == CB2_DTYPE_I8 && db == CB2_DTYPE_I8 && dc == CB2_DTYPE_I8 && is_int8)
+    return 1;
+  return -1;
+}
+
+} // namespace
+
+extern "C" {
+
+const char *cb2_last_error(void) { return g_err.c_str(); }
+
+int cb2_tile_m(void) { return 128; }
+
+uint64_t cb2_launch_count(void) { return g_launches.load(); }
+
+int cb2_device_status(int *status) {
+  DeviceState *dev;
+  int rc = get_device(&dev);
+  if (rc)
+    return rc;
+  CB2_CUDA(cudaDeviceSynchronize());
+  int v = 0;
+  CB2_CUDA(cudaMemcpy(&v, dev->status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (v != 0)
+    CB2_CUDA(cudaMemset(dev->status, 0, sizeof(int)));
+  if (status)
+    *status = v;
+  return CB2_OK;
+}
+
+size_t cb2_gemm_workspace_size(const cb2_gemm_args *a) {
+  if (!a || a->shuffle_type != CB2_SHUFFLE_AB)
+    return 0;
+  DeviceState *dev;
+  if (get_device(&dev))
+    return 0;
+  WgradLayout L;
+  wgrad_layout(dev->num_sms, a->m, a->n, &L);
+  return L.total;
+}
+
+size_t cb2_conv_workspace_size(const cb2_conv_args *a) {
+  if (!a || a->op_type != CB2_CONV_BACKWARD_WEIGHT)
+    return 0;
+  DeviceState *dev;
+  if (get_device(&dev))
+    return 0;
+  WgradLayout L;
+  wgrad_layout(dev->num_sms, a->K, a->C, &L);
+  return L.total;
+}
+
+int cb2_gemm_run(const cb2_gemm_args *a, void *stream_v) {
+  CB2_CHECK_ARG(a != nullptr, "null arguments");
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  DeviceState *dev;
+  int rc = get_device(&dev);
+  if (rc)
+    return rc;
+  CB2_CHECK_RT(a->ptr_A && a->ptr_B && a->ptr_C, "a,b,c must not empty");
+  CB2_CHECK_RT(!a->trans_c, "trans_c is not supported by the sm_100a kernels");
+  const int kind = kind_of(a->dtype_a, a->dtype_b, a->dtype_c, 0, false);
+  CB2_CHECK_RT(kind == 0, "can't find any suitable algo for dtypes (%d,%d,%d): only f16,f16,f16 is built",
+               a->dtype_a, a->dtype_b, a->dtype_c);
+  CB2_CHECK_ARG(a->m >= 0 && a->n > 0 && a->k >= 0, "bad m,n,k (%d,%d,%d)", a->m, a->n, a->k);
+  if (a->shuffle_type == CB2_SHUFFLE_AB) {
+    CB2_CHECK_RT(a->trans_a && !a->trans_b, "shuffle AB must be nt, i.e. backward weight");
+    CB2_CHECK_RT(a->indiceA && a->indiceBorC, "a_inds,b_inds tensor must not empty");
+    CB2_CHECK_ARG(a->m % 8 == 0 && a->n % 8 == 0,
+                  "this m, n, k isn't supported due to misaligned contiguous dim.");
+    WgradParams p;
+    memset(&p, 0, sizeof(p));
+    p.dout = a->ptr_A;
+    p.x = a->ptr_B;
+    p.a_inds = a->indiceA;
+    p.b_inds = a->indiceBorC;
+    p.ld_dout = a->stride_A;
+    p.ld_x = a->stride_B;
+    p.n_rows = a->k;
+    p.a_rows = a->rows_A;
+    p.b_rows = a->rows_B;
+    p.m_total = a->m;
+    p.n_total = a->n;
+    p.kv = 1;
+    p.mask_width = 128;
+    p.mask_filter = 0xffffffffu;
+    p.mode = kWgradPairList;
+    return run_wgrad(dev, p, a->workspace, a->workspace_bytes, a->ptr_C, a->ptr_D, a->stride_C, 0, a->alpha,
+                     a->beta, 0, stream);
+  }
+  CB2_CHECK_RT(a->shuffle_type == CB2_SHUFFLE_AC || a->shuffle_type == CB2_SHUFFLE_NONE, "unknown shuffle type %d",
+               a->shuffle_type);
+  CB2_CHECK_RT(!a->trans_a, "a of shuffle AB must be row major");
+  if (a->shuffle_type == CB2_SHUFFLE_AC)
+    CB2_CHECK_RT(a->indiceBorC != nullptr, "a_inds,c_inds tensor must not empty");
+  CB2_CHECK_ARG(a->k % 8 == 0 && a->n % 8 == 0, "this m, n, k isn't supported due to misaligned contiguous dim.");
+  RowConvParams p;
+  memset(&p, 0, sizeof(p));
+  p.a = a->ptr_A;
+  p.out = a->ptr_C;
+  p.a_inds = a->indiceA;
+  p.c_inds = a->indiceBorC;
+  p.lda = a->stride_A;
+  p.ldo = a->stride_C;
+  p.n_rows = a->m;
+  p.a_rows = a->rows_A;
+  p.red = a->k;
+  p.nn = a->n;
+  p.kv = 1;
+  p.mode = kModeGatherGemm;
+  p.mask_filter = 0xffffffffu;
+  p.alpha = a->alpha;
+  p.beta = a->beta;
+  p.act_alpha = a->act_alpha;
+  p.act_type = a->act_type;
+  if (a->beta != 0.f) {
+    p.src = a->ptr_D ? a->ptr_D : a->ptr_C;
+    p.src_mode = a->d_is_vector ? kSrcVector : kSrcRows;
+    p.lds = a->ptr_D ? a->stride_D : a->stride_C;
+    if (a->d_is_vector)
+      CB2_CHECK_RT(a->ptr_D != nullptr, "d must be a valid bias");
+  }
+  // B: [n, k] (trans_b) is K-major for the tensor core, [k, n] is MN-major.
+  const bool b_mn = !a->trans_b;
+  const uint64_t inner = b_mn ? a->n : a->k;
+  const uint64_t outer = b_mn ? a->k : a->n;
+  return run_rowconv(dev, p, 0, b_mn, a->ptr_B, inner, 1, outer, a->stride_B, a->stride_B, stream);
+}
+
+int cb2_conv_run(const cb2_conv_args *a, void *stream_v) {
+  CB2_CHECK_ARG(a != nullptr, "null arguments");
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  DeviceState *dev;
+  int rc = get_device(&dev);
+  if (rc)
+    return rc;
+  CB2_CHECK_RT(a->ptr_A && a->ptr_B && a->ptr_C, "input, weight, output must not empty");
+  CB2_CHECK_RT(a->indice_ptr != nullptr, "error: indices empty");
+  CB2_CHECK_RT(a->mask_ptr != nullptr, "error: mask empty");
+  CB2_CHECK_RT(a->mask_argsort_ptr != nullptr, "error: mask_argsort empty");
+  CB2_CHECK_RT(a->kernel_volume >= 1 && a->kernel_volume <= 32,
+               "kernel volume %d: only the static-mask kernels (at most 32 filter offsets) are built",
+               a->kernel_volume);
+  CB2_CHECK_RT(a->groups == 1 || a->groups == 0, "groups must be 1");
+  CB2_CHECK_ARG(a->N >= 0 && a->C > 0 && a->K > 0, "bad N,C,K (%d,%d,%d)", a->N, a->C, a->K);
+  const bool wgrad = a->op_type == CB2_CONV_BACKWARD_WEIGHT;
+  const int kind = kind_of(a->dtype_a, a->dtype_b, a->dtype_c, a->is_int8_inference, wgrad);
+  CB2_CHECK_RT(kind >= 0, "can't find any suitable algo for dtypes (%d,%d,%d) int8_inference=%d", a->dtype_a,
+               a->dtype_b, a->dtype_c, a->is_int8_inference);
+  if (kind == 1) {
+    CB2_CHECK_RT(a->op_type == CB2_CONV_FORWARD, "int8 inference is forward only");
+    CB2_CHECK_RT(a->bias_pointer && a->scale_pointer, "int8 inference must have both scale and bias");
+    CB2_CHECK_ARG(a->C % 16 == 0 && a->K % 16 == 0, "int8 channel counts must be multiples of 16");
+  } else {
+    CB2_CHECK_ARG(a->C % 8 == 0 && a->K % 8 == 0, "fp16 channel counts must be multiples of 8");
+  }
+  if (wgrad) {
+    CB2_CHECK_RT(a->mask_width > 0 && (a->mask_width % 128 == 0 || 128 % a->mask_width == 0),
+                 "error: mask_width must be positive and divide or be a multiple of %d", 128);
+    const int need_words = (a->N + a->mask_width - 1) / a->mask_width;
+    CB2_CHECK_RT(a->mask_words >= need_words, "reduced mask has %d words, %d needed", a->mask_words, need_words);
+    WgradParams p;
+    memset(&p, 0, sizeof(p));
+    p.dout = a->ptr_A;
+    p.x = a->ptr_B;
+    p.indices = a->indice_ptr;
+    p.rmask = a->mask_ptr;
+    p.argsort = a->mask_argsort_ptr;
+    p.ld_dout = a->K;
+    p.ld_x = a->C;
+    p.n_rows = a->N;
+    p.a_rows = a->rows_A;
+    p.b_rows = a->rows_B;
+    p.m_total = a->K;
+    p.n_total = a->C;
+    p.kv = a->kernel_volume;
+    p.mask_width = a->mask_width;
+    p.rmask_words = a->mask_words;
+    p.mask_filter = a->mask_filter;
+    p.mode = kWgradMaskConv;
+    return run_wgrad(dev, p, a->workspace, a->workspace_bytes, a->ptr_C, a->ptr_D,
+                     (long long)a->kernel_volume * a->C, a->C, a->alpha, a->beta,
+                     a->dtype_c == CB2_DTYPE_F32 ? 1 : 0, stream);
+  }
+  const bool dgrad = a->op_type == CB2_CONV_BACKWARD_INPUT;
+  CB2_CHECK_RT(dgrad || a->op_type == CB2_CONV_FORWARD, "unknown op type %d", a->op_type);
+  RowConvParams p;
+  memset(&p, 0, sizeof(p));
+  p.a = a->ptr_A;
+  p.out = a->ptr_C;
+  p.indices = a->indice_ptr;
+  p.mask = a->mask_ptr;
+  p.argsort = a->mask_argsort_ptr;
+  p.mask_out = dgrad ? nullptr : a->mask_out_ptr;
+  p.n_rows = a->N;
+  p.a_rows = a->rows_A;
+  p.red = dgrad ? a->K : a->C;
+  p.nn = dgrad ? a->C : a->K;
+  p.lda = p.red;
+  p.ldo = p.nn;
+  p.kv = a->kernel_volume;
+  p.mode = kModeMaskConv;
+  p.skip_empty_tiles = dgrad ? 1 : 0;
+  p.reverse_mask = (dgrad && a->reverse_mask) ? 1 : 0;
+  p.mask_filter = a->mask_filter;
+  p.alpha = a->alpha;
+  p.beta = a->beta;
+  p.act_alpha = a->act_alpha;
+  p.act_type = a->act_type;
+  if (kind == 1) {
+    p.scale = reinterpret_cast<const float *>(a->scale_pointer);
+    p.bias = reinterpret_cast<const float *>(a->bias_pointer);
+    if (a->beta != 0.f) {
+      p.src = a->ptr_D ? a->ptr_D : a->ptr_C;
+      p.src_mode = kSrcRows;
+      p.lds = p.nn;
+    }
+  } else if (a->beta != 0.f) {
+    p.src = a->ptr_D ? a->ptr_D : a->ptr_C;
+    p.src_mode = a->d_is_bias ? kSrcVector : kSrcRows;
+    p.lds = p.nn;
+  }
+  // weight [K, kv, C]: forward reduces over C (K-major B), backward input over K (MN-major B)
+  return run_rowconv(dev, p, kind, dgrad, a->ptr_B, a->C, a->kernel_volume, a->K, a->C,
+                     (uint64_t)a->kernel_volume * a->C, stream);
+}
+
+} // extern "C"

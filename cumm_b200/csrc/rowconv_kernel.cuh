@@ -1,0 +1,595 @@
+// Row-gather implicit-GEMM kernel for sm_100a: forward and input-gradient of the
+// mask-based sparse convolution, and the gather-GEMM-scatter GEMM (one filter offset with
+// explicit row lists).  One persistent CTA per SM walks 128-row tiles of the (sorted)
+// output rows; for every filter offset present in the tile's OR-ed neighbour mask it
+// gathers the 128 operand rows into a 128-byte-swizzled shared-memory tile with 16-byte
+// cp.async (missing neighbours are zero-filled), brings the matching weight slice in by
+// TMA, and one thread issues tcgen05.mma into a TMEM accumulator.  Four epilogue warps
+// read the accumulator back, apply alpha/beta/bias/activation (or the int8
+// requantisation), stage the tile through shared memory and write whole rows to their
+// scattered destinations.  No atomics: every output row is owned by exactly one tile.
+//
+// What it computes follows the reference kernel's control flow
+// (cumm/conv/kernel.py:825-920, cumm/conv/sparse_iters.py:317-356,
+// cumm/gemm/mask_iters.py:971-988, cumm/gemm/out_iters.py:541-553); how it computes it
+// does not: the reference stages everything through registers and mma.sync.
+#pragma once
+#include "ptx.cuh"
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+namespace cb2 {
+
+enum : int { kModeMaskConv = 0, kModeGatherGemm = 1 };
+enum : int { kSrcNone = 0, kSrcRows = 1, kSrcVector = 2 };
+enum : int { kStatusOk = 0, kStatusWaitTimeout = 1, kStatusBadIndex = 2 };
+
+struct RowConvParams {
+  const void *a;      // operand rows to gather  [a_rows, red]
+  void *out;          // destination rows        [*, nn]
+  const void *src;    // source rows for beta (same indexing as out) or a length-nn vector
+  const float *scale; // int8 requantisation, per output channel
+  const float *bias;  //   "
+  const int32_t *indices;  // [kv, n_rows] (mask-conv mode)
+  const uint32_t *mask;    // [n_rows] sorted order
+  const int32_t *argsort;  // [n_rows]
+  uint32_t *mask_out;      // [tiles] or null
+  const int32_t *a_inds;   // gather-GEMM mode (null = identity)
+  const int32_t *c_inds;   //   "
+  int *status;             // device status word (0 = ok)
+  long long lda, ldo, lds; // row strides in elements
+  int n_rows;              // rows to produce (sorted positions, or m)
+  int a_rows;              // rows available in `a`
+  int red;                 // reduction width per filter offset
+  int nn;                  // output width
+  int kv;
+  int mode;
+  int src_mode;
+  int skip_empty_tiles;    // input-gradient: a tile whose mask is 0 is left untouched
+  int reverse_mask;
+  uint32_t mask_filter;
+  float alpha, beta, act_alpha;
+  int act_type;
+  uint32_t b_lbo, b_sbo;   // weight-tile descriptor offsets (bytes)
+};
+
+template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN> struct RowConvCfg {
+  static constexpr int ES = KIND == 0 ? 2 : 1;            // operand element bytes
+  static constexpr int OES = KIND == 0 ? 2 : 1;           // output element bytes
+  static constexpr int ATOM_ELEMS = 128 / ES;             // elements per 128-byte swizzle row
+  static constexpr int UMMA_K = 32 / ES;
+  static constexpr int KRED = NATOM_K * ATOM_ELEMS;       // reduction elements per stage
+  static constexpr int TILE_M = 128;
+  static constexpr int SA = 3;                            // A stages == producer groups
+  static constexpr int SB = 2;                            // weight slots
+  static constexpr int A_STAGE_BYTES = TILE_M * 128 * NATOM_K;
+  static constexpr int B_SLOT_BYTES = BLOCK_N * 128 * NATOM_K;
+  static constexpr int OUT_ROW_BYTES = BLOCK_N * OES;
+  static constexpr int STAGING_BYTES = TILE_M * OUT_ROW_BYTES;
+  static constexpr int NUM_ACC = 2;
+  static constexpr int TMEM_COLS = NUM_ACC * BLOCK_N;     // 128 or 256: power of two >= 32
+  static constexpr int EPI_THREADS = 128;
+  static constexpr int GROUP_THREADS = 128;
+  static constexpr int THREADS = EPI_THREADS + 64 + SA * GROUP_THREADS;  // 576
+  // shared memory map (offsets from a 1024-byte aligned base)
+  static constexpr int OFF_A = 0;
+  static constexpr int OFF_B = OFF_A + SA * A_STAGE_BYTES;
+  static constexpr int OFF_STAGING = OFF_B + SB * B_SLOT_BYTES;
+  static constexpr int OFF_ROWIDX = OFF_STAGING + STAGING_BYTES;     // SA * 2 * 128 ints
+  static constexpr int OFF_OUTROW = OFF_ROWIDX + SA * 2 * 128 * 4;   // 128 ints
+  static constexpr int OFF_SCALE = OFF_OUTROW + 128 * 4;             // 2 * BLOCK_N floats
+  static constexpr int OFF_BARS = OFF_SCALE + 2 * BLOCK_N * 4;       // 16 mbarriers
+  static constexpr int OFF_MISC = OFF_BARS + 16 * 8;                 // tmem ptr, abort, flags
+  static constexpr int SMEM_BYTES = OFF_MISC + 64 + 1024;            // + alignment slack
+};
+
+// ---- tile mask helpers (all 32 lanes of the calling warp take part) -------------------
+__device__ __forceinline__ uint32_t tile_mask_partial(const RowConvParams &p, int tile, int ntiles) {
+  if (p.mode != kModeMaskConv || tile >= ntiles)
+    return 0;
+  uint32_t v = 0;
+  int base = tile * 128 + (int)lane_id();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int r = base + i * 32;
+    if (r < p.n_rows)
+      v |= __ldg(p.mask + r);
+  }
+  return v;
+}
+
+__device__ __forceinline__ float apply_act(float x, int act_type, float act_alpha) {
+  switch (act_type) {
+  case 1:
+    return fmaxf(x, 0.f);
+  case 2:
+    return 1.f / (1.f + expf(-x));
+  case 3:
+    return x >= 0.f ? x : x * act_alpha;
+  default:
+    return x;
+  }
+}
+
+__device__ __forceinline__ uint32_t cvt_sat_s8(float t) {
+  int r;
+  asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(t));
+  return static_cast<uint32_t>(r) & 0xffu;
+}
+
+// Walks this CTA's tiles and, inside each, the (filter offset, reduction pass) steps.
+// on_tile(tile, kmask_for_store, has_work) -> bool ; on_step(tile, f, kp, first, last) -> bool;
+// a false return aborts the walk.  Every role of the CTA runs the identical walk so that
+// their ring counters agree.
+template <class TileFn, class StepFn>
+__device__ __forceinline__ void walk_steps(const RowConvParams &p, int ntiles, int kpasses, TileFn on_tile,
+                                           StepFn on_step) {
+  int tile = blockIdx.x;
+  uint32_t part_next = tile_mask_partial(p, tile, ntiles);
+  for (; tile < ntiles; tile += gridDim.x) {
+    uint32_t part = part_next;
+    part_next = tile_mask_partial(p, tile + gridDim.x, ntiles);
+    uint32_t kmask;
+    if (p.mode == kModeMaskConv) {
+      kmask = __reduce_or_sync(0xffffffffu, part) & p.mask_filter;
+      if (p.kv < 32)
+        kmask &= (1u << p.kv) - 1u;
+    } else {
+      kmask = 1u;
+    }
+    uint32_t kmask_store = kmask;
+    if (p.skip_empty_tiles && kmask == 0)
+      continue;
+    if (p.reverse_mask)
+      kmask = __brev(kmask) >> (32 - p.kv);
+    if (!on_tile(tile, kmask_store, kmask != 0))
+      return;
+    uint32_t bits = kmask;
+    bool first = true;
+    while (bits) {
+      int f = __ffs(bits) - 1;
+      bits &= bits - 1;
+      for (int kp = 0; kp < kpasses; ++kp) {
+        bool last = (bits == 0) && (kp == kpasses - 1);
+        if (!on_step(tile, f, kp, first, last))
+          return;
+        first = false;
+      }
+    }
+  }
+}
+
+template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN>
+__global__ void __launch_bounds__(RowConvCfg<KIND, NATOM_K, BLOCK_N, B_MN>::THREADS, 1)
+rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p) {
+  using Cfg = RowConvCfg<KIND, NATOM_K, BLOCK_N, B_MN>;
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: required by the 128-byte swizzle atoms of TMA and tcgen05.
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  uint8_t *smem = smem_raw + pad;
+  const uint32_t sbase = raw_addr + pad;
+
+  int *rowidx = reinterpret_cast<int *>(smem + Cfg::OFF_ROWIDX);
+  int *outrow = reinterpret_cast<int *>(smem + Cfg::OFF_OUTROW);
+  float *s_scale = reinterpret_cast<float *>(smem + Cfg::OFF_SCALE);
+  float *s_bias = s_scale + BLOCK_N;
+  volatile int *misc = reinterpret_cast<volatile int *>(smem + Cfg::OFF_MISC);
+  // misc[0] tmem base, misc[1] abort flag, misc[2..5] per-group wait results
+  volatile int *abort_flag = misc + 1;
+
+  const uint32_t bars = sbase + Cfg::OFF_BARS;
+  auto full_a = [&](int s) { return bars + 8u * s; };
+  auto empty_a = [&](int s) { return bars + 8u * (3 + s); };
+  auto full_b = [&](int s) { return bars + 8u * (6 + s); };
+  auto empty_b = [&](int s) { return bars + 8u * (8 + s); };
+  auto acc_full = [&](int s) { return bars + 8u * (10 + s); };
+  auto acc_empty = [&](int s) { return bars + 8u * (12 + s); };
+  const uint32_t final_bar = bars + 8u * 14;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int ntiles = (p.n_rows + 127) / 128;
+  const int kpasses = (p.red + Cfg::KRED - 1) / Cfg::KRED;
+  const int n0 = blockIdx.y * BLOCK_N;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::SA; ++s) {
+      mbar_init(full_a(s), Cfg::GROUP_THREADS);
+      mbar_init(empty_a(s), 1);
+    }
+    for (int s = 0; s < Cfg::SB; ++s) {
+      mbar_init(full_b(s), 1);
+      mbar_init(empty_b(s), 1);
+    }
+    for (int s = 0; s < Cfg::NUM_ACC; ++s) {
+      mbar_init(acc_full(s), 1);
+      mbar_init(acc_empty(s), Cfg::EPI_THREADS);
+    }
+    mbar_init(final_bar, 1);
+    mbar_init_fence();
+    misc[1] = 0;
+    misc[2] = misc[3] = misc[4] = misc[5] = 1;
+  }
+  if (KIND == 1) {
+    for (int i = threadIdx.x; i < BLOCK_N; i += blockDim.x) {
+      int n = n0 + i;
+      s_scale[i] = (n < p.nn && p.scale) ? p.scale[n] : 0.f;
+      s_bias[i] = (n < p.nn && p.bias) ? p.bias[n] : 0.f;
+    }
+  }
+  if (warp == 4) {
+    tmem_alloc(sbase + Cfg::OFF_MISC, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = static_cast<uint32_t>(misc[0]);
+
+  auto fail = [&](int code) {
+    *abort_flag = 1;
+    if (p.status)
+      atomicCAS(p.status, 0, code);
+  };
+
+  if (warp < 4) {
+    // ======================= epilogue: TMEM -> registers -> staging -> scattered rows
+    const int et = threadIdx.x;  // 0..127, also the tile row this thread reads from TMEM
+    uint8_t *staging = smem + Cfg::OFF_STAGING;
+    constexpr int CPR = Cfg::OUT_ROW_BYTES / 16;       // 16-byte chunks per output row
+    constexpr int SWZ = (CPR >= 8 ? 8 : CPR) - 1;
+    constexpr int CH_PER_ROUND = 32 * Cfg::OES / 16;   // chunks produced per 32 columns
+    int acc_use = 0;
+    walk_steps(
+        p, ntiles, kpasses,
+        [&](int tile, uint32_t kmask_store, bool has_work) -> bool {
+          const int r = tile * 128 + et;
+          int o = -1;
+          if (r < p.n_rows) {
+            if (p.mode == kModeMaskConv)
+              o = __ldg(p.argsort + r);
+            else
+              o = p.c_inds ? __ldg(p.c_inds + r) : r;
+          }
+          if (et == 0 && p.mask_out && blockIdx.y == 0)
+            p.mask_out[tile] = kmask_store;
+          const int buf = acc_use % Cfg::NUM_ACC;
+          if (has_work) {
+            if (et == 0) {
+              bool ok = mbar_wait(acc_full(buf), (acc_use / Cfg::NUM_ACC) & 1, abort_flag);
+              misc[2] = ok ? 1 : 0;
+              if (!ok)
+                fail(kStatusWaitTimeout);
+            }
+          }
+          named_bar_sync(1, Cfg::EPI_THREADS);  // wait result visible; staging free again
+          if (has_work && misc[2] == 0)
+            return false;
+          outrow[et] = o;
+          tc_fence_after();
+          const uint32_t trow = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
+                                static_cast<uint32_t>(buf * BLOCK_N);
+          const bool use_src = (p.src_mode != kSrcNone) && (p.beta != 0.f);
+#pragma unroll 1
+          for (int round = 0; round < BLOCK_N / 32; ++round) {
+            uint32_t v[32];
+            if (has_work) {
+              tmem_ld32(trow + round * 32, v);
+              tmem_ld_wait();
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                v[i] = 0u;
+            }
+            const int ncol0 = n0 + round * 32;
+            if constexpr (KIND == 0) {
+              uint32_t packed[16];
+              uint4 srcv[4];
+              if (use_src && p.src_mode == kSrcRows && o >= 0) {
+                const uint4 *sp = reinterpret_cast<const uint4 *>(
+                    reinterpret_cast<const __half *>(p.src) + (long long)o * p.lds + ncol0);
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                  srcv[q] = (ncol0 + q * 8 < p.nn) ? __ldg(sp + q) : make_uint4(0, 0, 0, 0);
+              }
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                float x0 = __uint_as_float(v[i]), x1 = __uint_as_float(v[i + 1]);
+                float t0, t1;
+                if (use_src) {
+                  float s0 = 0.f, s1 = 0.f;
+                  if (p.src_mode == kSrcRows) {
+                    if (o >= 0) {
+                      const __half2 h = reinterpret_cast<const __half2 *>(srcv)[i / 2];
+                      s0 = __low2float(h);
+                      s1 = __high2float(h);
+                    }
+                  } else {
+                    const __half *bv = reinterpret_cast<const __half *>(p.src);
+                    if (ncol0 + i < p.nn)
+                      s0 = __half2float(__ldg(bv + ncol0 + i));
+                    if (ncol0 + i + 1 < p.nn)
+                      s1 = __half2float(__ldg(bv + ncol0 + i + 1));
+                  }
+                  t0 = __fmaf_rn(p.alpha, x0, __fmul_rn(p.beta, s0));
+                  t1 = __fmaf_rn(p.alpha, x1, __fmul_rn(p.beta, s1));
+                } else {
+                  t0 = __fmul_rn(p.alpha, x0);
+                  t1 = __fmul_rn(p.alpha, x1);
+                }
+                t0 = apply_act(t0, p.act_type, p.act_alpha);
+                t1 = apply_act(t1, p.act_type, p.act_alpha);
+                __half2 h2 = __halves2half2(__float2half_rn(t0), __float2half_rn(t1));
+                packed[i / 2] = *reinterpret_cast<uint32_t *>(&h2);
+              }
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const int c = round * CH_PER_ROUND + q;
+                const int pc = (c & ~SWZ) | ((c ^ et) & SWZ);
+                *reinterpret_cast<uint4 *>(staging + et * Cfg::OUT_ROW_BYTES + pc * 16) =
+                    make_uint4(packed[q * 4], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
+              }
+            } else {
+              uint32_t packed[8];
+              uint4 srcv[2];
+              if (use_src && o >= 0) {
+                const uint4 *sp = reinterpret_cast<const uint4 *>(
+                    reinterpret_cast<const int8_t *>(p.src) + (long long)o * p.lds + ncol0);
+#pragma unroll
+                for (int q = 0; q < 2; ++q)
+                  srcv[q] = (ncol0 + q * 16 < p.nn) ? __ldg(sp + q) : make_uint4(0, 0, 0, 0);
+              }
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                uint32_t w = 0;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const int col = round * 32 + i + j;
+                  float acc = __int2float_rn(static_cast<int>(v[i + j]));
+                  float t = __fmaf_rn(s_scale[col], acc, s_bias[col]);
+                  if (use_src) {
+                    float s = 0.f;
+                    if (o >= 0)
+                      s = static_cast<float>(reinterpret_cast<const int8_t *>(srcv)[i + j]);
+                    t = __fmaf_rn(p.beta, s, t);
+                  }
+                  t = apply_act(t, p.act_type, p.act_alpha);
+                  w |= cvt_sat_s8(t) << (8 * j);
+                }
+                packed[i / 4] = w;
+              }
+#pragma unroll
+              for (int q = 0; q < 2; ++q) {
+                const int c = round * CH_PER_ROUND + q;
+                const int pc = (c & ~SWZ) | ((c ^ et) & SWZ);
+                *reinterpret_cast<uint4 *>(staging + et * Cfg::OUT_ROW_BYTES + pc * 16) =
+                    make_uint4(packed[q * 4], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
+              }
+            }
+          }
+          if (has_work) {
+            tc_fence_before();
+            mbar_arrive(acc_empty(buf));
+            ++acc_use;
+          }
+          named_bar_sync(1, Cfg::EPI_THREADS);  // staging complete
+          // phase 2: CPR threads per row write whole rows
+          {
+            const int c = et % CPR;
+            const int row0 = et / CPR;
+            constexpr int RSTEP = 128 / CPR;
+            const int ncol = n0 + c * (16 / Cfg::OES);
+            if (ncol < p.nn) {
+#pragma unroll 4
+              for (int i = 0; i < CPR; ++i) {
+                const int row = row0 + i * RSTEP;
+                const int orow = outrow[row];
+                if (orow >= 0) {
+                  const int pc = (c & ~SWZ) | ((c ^ row) & SWZ);
+                  uint4 val = *reinterpret_cast<const uint4 *>(staging + row * Cfg::OUT_ROW_BYTES + pc * 16);
+                  uint8_t *dst = reinterpret_cast<uint8_t *>(p.out) +
+                                 ((long long)orow * p.ldo + ncol) * Cfg::OES;
+                  *reinterpret_cast<uint4 *>(dst) = val;
+                }
+              }
+            }
+          }
+          return true;
+        },
+        [&](int, int, int, bool, bool) -> bool { return true; });
+  } else if (warp == 4) {
+    // ======================= MMA issuer (lane 0 issues; the warp walks together)
+    constexpr uint32_t idesc = make_idesc(KIND, false, B_MN, 128, BLOCK_N);
+    int step = 0, acc_use = 0, bcount = 0, last_key = -1, cur_slot = 0;
+    bool ok_all = true;
+    walk_steps(
+        p, ntiles, kpasses, [&](int, uint32_t, bool) -> bool { return true; },
+        [&](int tile, int f, int kp, bool first, bool last) -> bool {
+          const int buf = acc_use % Cfg::NUM_ACC;
+          int ok = 1;
+          if (lane == 0) {
+            if (first)
+              ok = mbar_wait(acc_empty(buf), ((acc_use / Cfg::NUM_ACC) & 1) ^ 1, abort_flag);
+            const int key = f * kpasses + kp;
+            if (ok && key != last_key) {
+              if (bcount > 0)
+                tc_commit(empty_b(cur_slot));
+              cur_slot = bcount % Cfg::SB;
+              ok = mbar_wait(full_b(cur_slot), (bcount / Cfg::SB) & 1, abort_flag);
+              ++bcount;
+              last_key = key;
+            }
+            const int stage = step % Cfg::SA;
+            if (ok)
+              ok = mbar_wait(full_a(stage), (step / Cfg::SA) & 1, abort_flag);
+            if (ok) {
+              tc_fence_after();
+              const uint32_t a_base = sbase + Cfg::OFF_A + stage * Cfg::A_STAGE_BYTES;
+              const uint32_t b_base = sbase + Cfg::OFF_B + cur_slot * Cfg::B_SLOT_BYTES;
+              const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BLOCK_N);
+              const int red_left = p.red - kp * Cfg::KRED;
+              const int ksteps_total = (min(red_left, Cfg::KRED) + Cfg::UMMA_K - 1) / Cfg::UMMA_K;
+              for (int ks = 0; ks < ksteps_total; ++ks) {
+                const int ka = ks >> 2, kk = ks & 3;
+                const uint64_t adesc =
+                    make_smem_desc(a_base + ka * (Cfg::TILE_M * 128) + kk * 32, 16, 1024);
+                uint64_t bdesc;
+                if constexpr (!B_MN) {
+                  bdesc = make_smem_desc(b_base + ka * (BLOCK_N * 128) + kk * 32, 16, 1024);
+                } else {
+                  // weight slot holds BLOCK_N/ATOM_ELEMS blocks of [KRED rows x 128 B]
+                  bdesc = make_smem_desc(b_base + (ka * 4 + kk) * (Cfg::UMMA_K * 128), p.b_lbo, p.b_sbo);
+                }
+                tc_mma<KIND>(d_tmem, adesc, bdesc, idesc, (first && ks == 0) ? 0u : 1u);
+              }
+              tc_commit(empty_a(stage));
+              if (last)
+                tc_commit(acc_full(buf));
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          ++step;
+          if (last)
+            ++acc_use;
+          if (!ok) {
+            if (lane == 0)
+              fail(kStatusWaitTimeout);
+            ok_all = false;
+            return false;
+          }
+          return true;
+        });
+    // make sure every MMA has retired before TMEM is released
+    if (lane == 0 && ok_all) {
+      tc_commit(final_bar);
+      if (!mbar_wait(final_bar, 0, abort_flag))
+        fail(kStatusWaitTimeout);
+    }
+    __syncwarp();
+  } else if (warp == 5) {
+    // ======================= weight tiles by TMA (lane 0 issues)
+    if (lane == 0)
+      tma_prefetch_desc(&tmap_b);
+    int bcount = 0, last_key = -1;
+    walk_steps(
+        p, ntiles, kpasses, [&](int, uint32_t, bool) -> bool { return true; },
+        [&](int tile, int f, int kp, bool, bool) -> bool {
+          int ok = 1;
+          const int key = f * kpasses + kp;
+          if (key != last_key) {
+            if (lane == 0) {
+              const int slot = bcount % Cfg::SB;
+              ok = mbar_wait(empty_b(slot), ((bcount / Cfg::SB) & 1) ^ 1, abort_flag);
+              if (ok) {
+                const uint32_t dst = sbase + Cfg::OFF_B + slot * Cfg::B_SLOT_BYTES;
+                mbar_arrive_expect_tx(full_b(slot), Cfg::B_SLOT_BYTES);
+                if constexpr (!B_MN) {
+                  // [BLOCK_N rows x 128 B] per reduction atom; rows = output channels
+#pragma unroll
+                  for (int ka = 0; ka < NATOM_K; ++ka)
+                    tma_load_3d(dst + ka * (BLOCK_N * 128), &tmap_b, full_b(slot),
+                                kp * Cfg::KRED + ka * Cfg::ATOM_ELEMS, f, n0);
+                } else {
+                  // [KRED rows x 128 B] per block of ATOM_ELEMS output channels; rows = reduction
+#pragma unroll
+                  for (int na = 0; na < BLOCK_N / Cfg::ATOM_ELEMS; ++na)
+                    tma_load_3d(dst + na * (Cfg::KRED * 128), &tmap_b, full_b(slot),
+                                n0 + na * Cfg::ATOM_ELEMS, f, kp * Cfg::KRED);
+                }
+              }
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            ++bcount;
+            last_key = key;
+          }
+          if (!ok) {
+            if (lane == 0)
+              fail(kStatusWaitTimeout);
+            return false;
+          }
+          return true;
+        });
+  } else {
+    // ======================= operand-row gather: group g owns stage g
+    const int g = (warp - 6) >> 2;                    // 0..2
+    const int gt = threadIdx.x - (6 * 32 + g * Cfg::GROUP_THREADS);  // 0..127
+    constexpr int CPR = NATOM_K * 8;                  // 16-byte chunks per operand row
+    constexpr int RSTEP = 128 / CPR;
+    const int c = gt % CPR;
+    const int row0 = gt / CPR;
+    int *group_rowidx = rowidx + g * 256;  // two buffers, alternating per use of the stage
+    volatile int *my_flag = misc + 3 + g;
+    int step = 0;
+    int o = -1;
+    const uint8_t *a_bytes = reinterpret_cast<const uint8_t *>(p.a);
+    walk_steps(
+        p, ntiles, kpasses,
+        [&](int tile, uint32_t, bool) -> bool {
+          const int r = tile * 128 + gt;
+          o = -1;
+          if (r < p.n_rows)
+            o = (p.mode == kModeMaskConv) ? __ldg(p.argsort + r) : r;
+          return true;
+        },
+        [&](int tile, int f, int kp, bool, bool) -> bool {
+          const bool mine = (step % Cfg::SA) == g;
+          const int use = step / Cfg::SA;
+          ++step;
+          if (!mine)
+            return true;
+          int idx = -1;
+          if (o >= 0) {
+            if (p.mode == kModeMaskConv)
+              idx = __ldg(p.indices + (long long)f * p.n_rows + o);
+            else
+              idx = p.a_inds ? __ldg(p.a_inds + o) : o;
+            if (idx >= p.a_rows) {  // never dereference a row the caller did not provide
+              fail(kStatusBadIndex);
+              idx = -1;
+            }
+          }
+          if (gt == 0) {
+            bool ok = mbar_wait(empty_a(g), (use & 1) ^ 1, abort_flag);
+            *my_flag = ok ? 1 : 0;
+            if (!ok)
+              fail(kStatusWaitTimeout);
+          }
+          // Double-buffered: a thread that runs ahead writes the other buffer than the one
+          // slower threads of the group may still be reading for the previous use.
+          int *my_rowidx = group_rowidx + (use & 1) * 128;
+          my_rowidx[gt] = idx;
+          named_bar_sync(2 + g, Cfg::GROUP_THREADS);
+          if (*my_flag == 0)
+            return false;
+          const uint32_t a_stage = sbase + Cfg::OFF_A + g * Cfg::A_STAGE_BYTES;
+          const int byte_off = kp * Cfg::KRED * Cfg::ES + c * 16;
+          const bool col_ok = byte_off < p.red * Cfg::ES;
+          const uint32_t dst_c = a_stage + (c >> 3) * (Cfg::TILE_M * 128);
+#pragma unroll
+          for (int i = 0; i < CPR; ++i) {
+            const int row = row0 + i * RSTEP;
+            const int ridx = my_rowidx[row];
+            const uint32_t dst = dst_c + (row >> 3) * 1024 + (row & 7) * 128 + (((c & 7) ^ (row & 7)) << 4);
+            const bool valid = col_ok && ridx >= 0;
+            const uint8_t *srcp = valid ? a_bytes + ((long long)ridx * p.lda) * Cfg::ES + byte_off : a_bytes;
+            cp_async_16(dst, srcp, valid ? 16u : 0u);
+          }
+          cp_async_commit();
+          cp_async_wait<0>();
+          fence_proxy_async_smem();
+          mbar_arrive(full_a(g));
+          return true;
+        });
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+} // namespace cb2

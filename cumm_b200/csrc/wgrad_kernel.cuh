@@ -1,0 +1,467 @@
+// Weight-gradient kernel of the mask-based sparse convolution (and the gather-gather
+// "ShuffleAB" GEMM) for sm_100a.
+//
+//   dW[k, f, c] = alpha * sum_r dout[o_r, k] * X[idx[f, o_r], c] + beta * dW_prev[k, f, c]
+//
+// The reduction runs over (sorted) rows, so both tcgen05 operands are gathered rows held
+// "MN-major": a gathered row is 128-byte-swizzled along its channels and the 128 rows of a
+// tile are the K dimension of the MMA.  Work is cut into units (filter offset f, range of
+// row tiles); a unit accumulates in TMEM and leaves one fp32 partial [128 x BLOCK_N] in
+// the workspace.  A second kernel adds the partials of each f in a fixed order, applies
+// alpha/beta and converts: no atomics and no inter-CTA waits (the reference serialises
+// split-K slices through a spinning semaphore, cumm/conv/kernel.py:960-1083).
+//
+// Semantics follow cumm/gemm/blockmma/mma.py:608-648,722-740 (a row takes part for
+// offset f iff the reduced-mask word covering it has bit f), cumm/conv/sparse_iters.py
+// :284-316 (A = dout[mask_argsort[r]], B = X[indices[f, mask_argsort[r]]], -1 -> zeros)
+// and cumm/conv/kernel.py:890-897 (offsets outside mask_filter are left untouched).
+#pragma once
+#include "ptx.cuh"
+#include "rowconv_kernel.cuh"
+
+namespace cb2 {
+
+enum : int { kWgradMaskConv = 0, kWgradPairList = 1 };
+
+struct WgradParams {
+  const void *dout;        // A rows [*, m_total]  (fp16)
+  const void *x;           // B rows [*, n_total]  (fp16)
+  const int32_t *indices;  // [kv, n_rows]
+  const uint32_t *rmask;   // reduced masks, one word per mask_width sorted rows
+  const int32_t *argsort;  // [n_rows]
+  const int32_t *a_inds;   // pair-list mode
+  const int32_t *b_inds;   //   "
+  float *partials;         // workspace: [unit][m_tile][n_tile][128][BLOCK_N] fp32
+  int *sched;              // workspace header: [0,32) units per f, [32,64) first unit of f, [64] total units
+  int *unit_flags;         // workspace: [unit] 1 when the unit produced a partial
+  int *status;
+  long long ld_dout, ld_x;
+  int n_rows;
+  int a_rows, b_rows;
+  int m_total, n_total;
+  int kv;
+  int mask_width;
+  int rmask_words;
+  uint32_t mask_filter;
+  int mode;
+};
+
+template <int BLOCK_N> struct WgradCfg {
+  static constexpr int SA = 3;
+  static constexpr int A_BYTES = 128 * 256;                 // 128 rows x (2 x 128 B): M = 128 channels
+  static constexpr int B_BYTES = 128 * 2 * BLOCK_N;         // 128 rows x BLOCK_N fp16
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TMEM_COLS = 2 * BLOCK_N;
+  static constexpr int THREADS = 128 + 64 + SA * 128;       // epilogue, mma + spare, 3 gather groups
+  static constexpr int OFF_STAGES = 0;
+  static constexpr int OFF_ROWIDX = SA * STAGE_BYTES;       // SA x 2 buffers x 2 operands x 128 ints
+  static constexpr int OFF_SCHED = OFF_ROWIDX + SA * 2 * 2 * 128 * 4;  // 96 ints
+  static constexpr int OFF_BARS = OFF_SCHED + 96 * 4;
+  static constexpr int OFF_MISC = OFF_BARS + 16 * 8;
+  static constexpr int SMEM_BYTES = OFF_MISC + 64 + 1024;
+};
+
+// OR of the reduced-mask words that cover sorted rows [128*tile, 128*tile + 128).
+__device__ __forceinline__ uint32_t wgrad_tile_mask(const WgradParams &p, int tile) {
+  if (p.mode != kWgradMaskConv)
+    return 1u;
+  const int r0 = tile * 128;
+  int r1 = r0 + 127;
+  if (r1 >= p.n_rows)
+    r1 = p.n_rows - 1;
+  int w0 = r0 / p.mask_width, w1 = r1 / p.mask_width;
+  uint32_t v = 0;
+  for (int w = w0; w <= w1; ++w)
+    if (w < p.rmask_words)
+      v |= __ldg(p.rmask + w);
+  return v & p.mask_filter;
+}
+
+// Unit schedule, identical in every CTA: S_f units for offset f, proportional to the
+// number of row tiles that carry f; unit (f, s) covers tiles [T*s/S_f, T*(s+1)/S_f).
+__device__ __forceinline__ void wgrad_build_schedule(const WgradParams &p, int ntiles, int *s_sched) {
+  // s_sched[0..31] counts -> S_f, [32..63] base, [64] total
+  for (int i = threadIdx.x; i < 96; i += blockDim.x)
+    s_sched[i] = 0;
+  __syncthreads();
+  for (int t = threadIdx.x; t < ntiles; t += blockDim.x) {
+    uint32_t m = wgrad_tile_mask(p, t);
+    while (m) {
+      int f = __ffs(m) - 1;
+      m &= m - 1;
+      atomicAdd(&s_sched[f], 1);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    long long total = 0;
+    for (int f = 0; f < p.kv && f < 32; ++f)
+      total += s_sched[f];
+    const int G = gridDim.x;
+    int base = 0;
+    for (int f = 0; f < 32; ++f) {
+      int cnt = (f < p.kv) ? s_sched[f] : 0;
+      int S = 0;
+      if (cnt > 0) {
+        S = (int)(((long long)cnt * G + total / 2) / total);
+        if (S < 1)
+          S = 1;
+        if (S > cnt)
+          S = cnt;
+        if (S > G)
+          S = G;
+      }
+      s_sched[f] = S;
+      s_sched[32 + f] = base;
+      base += S;
+    }
+    s_sched[64] = base;
+  }
+  __syncthreads();
+}
+
+// Walk the active tiles of this CTA's units.  on_unit(u, f) at unit start, on_tile(tile, f,
+// first_of_unit) for each tile carrying f, on_unit_end(u, f, n_active).
+template <class UnitFn, class TileFn, class EndFn>
+__device__ __forceinline__ void wgrad_walk(const WgradParams &p, int ntiles, const int *s_sched, UnitFn on_unit,
+                                           TileFn on_tile, EndFn on_unit_end) {
+  const int total = s_sched[64];
+  for (int u = blockIdx.x; u < total; u += gridDim.x) {
+    int f = 0;
+    while (f < 31 && !(u >= s_sched[32 + f] && u < s_sched[32 + f] + s_sched[f]))
+      ++f;
+    const int S = s_sched[f];
+    const int s = u - s_sched[32 + f];
+    const int t0 = (int)(((long long)ntiles * s) / S);
+    const int t1 = (int)(((long long)ntiles * (s + 1)) / S);
+    if (!on_unit(u, f))
+      return;
+    int active = 0;
+    for (int tb = t0; tb < t1; tb += 32) {
+      const int t = tb + (int)lane_id();
+      uint32_t m = (t < t1) ? wgrad_tile_mask(p, t) : 0u;
+      uint32_t ball = __ballot_sync(0xffffffffu, (m >> f) & 1u);
+      while (ball) {
+        const int j = __ffs(ball) - 1;
+        ball &= ball - 1;
+        if (!on_tile(tb + j, f, active == 0))
+          return;
+        ++active;
+      }
+    }
+    if (!on_unit_end(u, f, active))
+      return;
+  }
+}
+
+template <int BLOCK_N>
+__global__ void __launch_bounds__(WgradCfg<BLOCK_N>::THREADS, 1) wgrad_kernel(const WgradParams p) {
+  using Cfg = WgradCfg<BLOCK_N>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  uint8_t *smem = smem_raw + pad;
+  const uint32_t sbase = raw_addr + pad;
+  int *rowidx = reinterpret_cast<int *>(smem + Cfg::OFF_ROWIDX);
+  int *s_sched = reinterpret_cast<int *>(smem + Cfg::OFF_SCHED);
+  volatile int *misc = reinterpret_cast<volatile int *>(smem + Cfg::OFF_MISC);
+  volatile int *abort_flag = misc + 1;
+  const uint32_t bars = sbase + Cfg::OFF_BARS;
+  auto full_s = [&](int s) { return bars + 8u * s; };
+  auto empty_s = [&](int s) { return bars + 8u * (3 + s); };
+  auto acc_full = [&](int s) { return bars + 8u * (6 + s); };
+  auto acc_empty = [&](int s) { return bars + 8u * (8 + s); };
+  const uint32_t final_bar = bars + 8u * 10;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int ntiles = (p.n_rows + 127) / 128;
+  const int n_tiles_n = (p.n_total + BLOCK_N - 1) / BLOCK_N;
+  const int mt = blockIdx.y / n_tiles_n, nt = blockIdx.y % n_tiles_n;
+  const int m0 = mt * 128, n0 = nt * BLOCK_N;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::SA; ++s) {
+      mbar_init(full_s(s), 128);
+      mbar_init(empty_s(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(acc_full(s), 1);
+      mbar_init(acc_empty(s), 128);
+    }
+    mbar_init(final_bar, 1);
+    mbar_init_fence();
+    misc[1] = 0;
+    misc[2] = misc[3] = misc[4] = misc[5] = 1;
+  }
+  if (warp == 4) {
+    tmem_alloc(sbase + Cfg::OFF_MISC, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  wgrad_build_schedule(p, ntiles, s_sched);  // contains __syncthreads
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = static_cast<uint32_t>(misc[0]);
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x < 96)
+    p.sched[threadIdx.x] = s_sched[threadIdx.x];
+
+  auto fail = [&](int code) {
+    *abort_flag = 1;
+    if (p.status)
+      atomicCAS(p.status, 0, code);
+  };
+  const int gy = gridDim.y;
+
+  if (warp < 4) {
+    // ======================= epilogue: one fp32 partial per unit
+    const int et = threadIdx.x;
+    int acc_use = 0;
+    wgrad_walk(
+        p, ntiles, s_sched, [&](int, int) -> bool { return true; },
+        [&](int, int, bool) -> bool { return true; },
+        [&](int u, int f, int active) -> bool {
+          if (et == 0)
+            p.unit_flags[(long long)u * gy + blockIdx.y] = active > 0 ? 1 : 0;
+          if (active == 0)
+            return true;
+          const int buf = acc_use & 1;
+          if (et == 0) {
+            bool ok = mbar_wait(acc_full(buf), (acc_use >> 1) & 1, abort_flag);
+            misc[2] = ok ? 1 : 0;
+            if (!ok)
+              fail(kStatusWaitTimeout);
+          }
+          named_bar_sync(1, 128);
+          if (misc[2] == 0)
+            return false;
+          tc_fence_after();
+          const uint32_t trow = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
+                                static_cast<uint32_t>(buf * BLOCK_N);
+          float *dst = p.partials + (((long long)u * gy + blockIdx.y) * 128 + et) * BLOCK_N;
+#pragma unroll 1
+          for (int round = 0; round < BLOCK_N / 32; ++round) {
+            uint32_t v[32];
+            tmem_ld32(trow + round * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<uint4 *>(dst + round * 32 + q * 4) =
+                  make_uint4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+          }
+          tc_fence_before();
+          mbar_arrive(acc_empty(buf));
+          ++acc_use;
+          return true;
+        });
+  } else if (warp == 4) {
+    // ======================= MMA issuer
+    constexpr uint32_t idesc = make_idesc(0, true, true, 128, BLOCK_N);
+    int step = 0, acc_use = 0;
+    bool ok_all = true;
+    wgrad_walk(
+        p, ntiles, s_sched, [&](int, int) -> bool { return true; },
+        [&](int tile, int f, bool first) -> bool {
+          const int buf = acc_use & 1;
+          int ok = 1;
+          if (lane == 0) {
+            if (first)
+              ok = mbar_wait(acc_empty(buf), ((acc_use >> 1) & 1) ^ 1, abort_flag);
+            const int stage = step % Cfg::SA;
+            if (ok)
+              ok = mbar_wait(full_s(stage), (step / Cfg::SA) & 1, abort_flag);
+            if (ok) {
+              tc_fence_after();
+              const uint32_t a_base = sbase + Cfg::OFF_STAGES + stage * Cfg::STAGE_BYTES;
+              const uint32_t b_base = a_base + Cfg::A_BYTES;
+              const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BLOCK_N);
+              int rows = p.n_rows - tile * 128;
+              if (rows > 128)
+                rows = 128;
+              const int ksteps = (rows + 15) / 16;
+              for (int ks = 0; ks < ksteps; ++ks) {
+                const uint64_t adesc = make_smem_desc(a_base + ks * 2048, 128 * 128, 1024);
+                const uint64_t bdesc = make_smem_desc(b_base + ks * 2048, 128 * 128, 1024);
+                tc_mma<0>(d_tmem, adesc, bdesc, idesc, (first && ks == 0) ? 0u : 1u);
+              }
+              tc_commit(empty_s(stage));
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          ++step;
+          if (!ok) {
+            if (lane == 0)
+              fail(kStatusWaitTimeout);
+            ok_all = false;
+            return false;
+          }
+          return true;
+        },
+        [&](int, int, int active) -> bool {
+          if (active > 0) {
+            if (lane == 0)
+              tc_commit(acc_full(acc_use & 1));
+            __syncwarp();
+            ++acc_use;
+          }
+          return true;
+        });
+    if (lane == 0 && ok_all) {
+      tc_commit(final_bar);
+      if (!mbar_wait(final_bar, 0, abort_flag))
+        fail(kStatusWaitTimeout);
+    }
+    __syncwarp();
+  } else if (warp == 5) {
+    // spare warp (keeps the role layout aligned with the row-conv kernel)
+  } else {
+    // ======================= gather both operands: group g owns stage g
+    const int g = (warp - 6) >> 2;
+    const int gt = threadIdx.x - (6 * 32 + g * 128);
+    int *group_rowidx = rowidx + g * 512;
+    volatile int *my_flag = misc + 3 + g;
+    int step = 0;
+    const uint8_t *a_bytes = reinterpret_cast<const uint8_t *>(p.dout);
+    const uint8_t *b_bytes = reinterpret_cast<const uint8_t *>(p.x);
+    constexpr int CPR_B = BLOCK_N / 8;  // 16-byte chunks per B row (fp16)
+    wgrad_walk(
+        p, ntiles, s_sched, [&](int, int) -> bool { return true; },
+        [&](int tile, int f, bool) -> bool {
+          const bool mine = (step % Cfg::SA) == g;
+          const int use = step / Cfg::SA;
+          ++step;
+          if (!mine)
+            return true;
+          const int r = tile * 128 + gt;
+          int ia = -1, ib = -1;
+          if (r < p.n_rows) {
+            if (p.mode == kWgradMaskConv) {
+              const uint32_t word = __ldg(p.rmask + r / p.mask_width);
+              if ((word >> f) & 1u) {
+                const int o = __ldg(p.argsort + r);
+                ib = __ldg(p.indices + (long long)f * p.n_rows + o);
+                ia = (ib >= 0) ? o : -1;  // a zero B row makes the A row irrelevant
+              }
+            } else {
+              ia = __ldg(p.a_inds + r);
+              ib = __ldg(p.b_inds + r);
+            }
+            if (ia >= p.a_rows || ib >= p.b_rows) {
+              fail(kStatusBadIndex);
+              ia = ib = -1;
+            }
+          }
+          if (gt == 0) {
+            bool ok = mbar_wait(empty_s(g), (use & 1) ^ 1, abort_flag);
+            *my_flag = ok ? 1 : 0;
+            if (!ok)
+              fail(kStatusWaitTimeout);
+          }
+          int *ridx_a = group_rowidx + (use & 1) * 256;
+          int *ridx_b = ridx_a + 128;
+          ridx_a[gt] = ia;
+          ridx_b[gt] = ib;
+          named_bar_sync(2 + g, 128);
+          if (*my_flag == 0)
+            return false;
+          const uint32_t a_stage = sbase + Cfg::OFF_STAGES + g * Cfg::STAGE_BYTES;
+          const uint32_t b_stage = a_stage + Cfg::A_BYTES;
+          {
+            // A rows: 256 B (128 channels of dout starting at m0), 16 chunks per row
+            const int c = gt & 15, row0 = gt >> 4;
+            const bool col_ok = (m0 + c * 8) < p.m_total;
+            const uint32_t dst_c = a_stage + (c >> 3) * (128 * 128);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int row = row0 + i * 8;
+              const int ridx = ridx_a[row];
+              const uint32_t dst = dst_c + (row >> 3) * 1024 + (row & 7) * 128 + (((c & 7) ^ (row & 7)) << 4);
+              const bool valid = col_ok && ridx >= 0;
+              const uint8_t *srcp = valid ? a_bytes + ((long long)ridx * p.ld_dout + m0 + c * 8) * 2 : a_bytes;
+              cp_async_16(dst, srcp, valid ? 16u : 0u);
+            }
+          }
+          {
+            const int c = gt % CPR_B, row0 = gt / CPR_B;
+            constexpr int RSTEP = 128 / CPR_B;
+            const bool col_ok = (n0 + c * 8) < p.n_total;
+            const uint32_t dst_c = b_stage + (c >> 3) * (128 * 128);
+#pragma unroll
+            for (int i = 0; i < CPR_B; ++i) {
+              const int row = row0 + i * RSTEP;
+              const int ridx = ridx_b[row];
+              const uint32_t dst = dst_c + (row >> 3) * 1024 + (row & 7) * 128 + (((c & 7) ^ (row & 7)) << 4);
+              const bool valid = col_ok && ridx >= 0;
+              const uint8_t *srcp = valid ? b_bytes + ((long long)ridx * p.ld_x + n0 + c * 8) * 2 : b_bytes;
+              cp_async_16(dst, srcp, valid ? 16u : 0u);
+            }
+          }
+          cp_async_commit();
+          cp_async_wait<0>();
+          fence_proxy_async_smem();
+          mbar_arrive(full_s(g));
+          return true;
+        },
+        [&](int, int, int) -> bool { return true; });
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// Second stage: out[m, f, n] = alpha * sum_units partial + beta * prev, fixed unit order.
+// OUT_F32 selects fp32 output (multi-GPU partial sums) instead of fp16.
+struct WgradReduceParams {
+  const float *partials;
+  const int *sched;
+  const int *unit_flags;
+  void *out;
+  const void *src;
+  long long ldo;       // elements between consecutive m rows of out
+  long long f_stride;  // elements between consecutive f slices
+  int m_total, n_total, kv;
+  int block_n;
+  int gy;              // m_tiles * n_tiles of the first stage
+  uint32_t mask_filter;
+  float alpha, beta;
+  int out_f32;
+};
+
+__global__ void wgrad_reduce_kernel(const WgradReduceParams p) {
+  const int f = blockIdx.y;
+  if (!((p.mask_filter >> f) & 1u))
+    return;
+  const int S = p.sched[f], base = p.sched[32 + f];
+  const long long total = (long long)p.m_total * p.n_total;
+  const int n_tiles_n = (p.n_total + p.block_n - 1) / p.block_n;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+       e += (long long)gridDim.x * blockDim.x) {
+    const int m = (int)(e / p.n_total), n = (int)(e % p.n_total);
+    const int mt = m >> 7, ntile = n / p.block_n;
+    const int by = mt * n_tiles_n + ntile;
+    const long long in_tile = (long long)(m & 127) * p.block_n + (n - ntile * p.block_n);
+    float acc = 0.f;
+    for (int s = 0; s < S; ++s) {
+      const long long u = base + s;
+      if (p.unit_flags[u * p.gy + by])
+        acc += p.partials[(u * p.gy + by) * 128 * p.block_n + in_tile];
+    }
+    const long long off = (long long)m * p.ldo + (long long)f * p.f_stride + n;
+    if (p.out_f32) {
+      float *o = reinterpret_cast<float *>(p.out);
+      float prev = (p.beta != 0.f) ? reinterpret_cast<const float *>(p.src)[off] : 0.f;
+      o[off] = (p.beta != 0.f) ? __fmaf_rn(p.alpha, acc, __fmul_rn(p.beta, prev)) : __fmul_rn(p.alpha, acc);
+    } else {
+      __half *o = reinterpret_cast<__half *>(p.out);
+      float prev = (p.beta != 0.f) ? __half2float(reinterpret_cast<const __half *>(p.src)[off]) : 0.f;
+      float t = (p.beta != 0.f) ? __fmaf_rn(p.alpha, acc, __fmul_rn(p.beta, prev)) : __fmul_rn(p.alpha, acc);
+      o[off] = __float2half_rn(t);
+    }
+  }
+}
+
+} // namespace cb2

@@ -1,0 +1,168 @@
+/*
+ * cumm_b200 -- C ABI of the B200 (sm_100a) sparse-convolution hot path.
+ *
+ * Plain pointers and sizes only; every pointer is a CUDA device pointer unless said
+ * otherwise.  All entry points are asynchronous on the given stream, keep no reference
+ * to caller memory after the launches they enqueue, and are safe to call from several
+ * host threads.  They return 0 on success, or a negative CB2_ERR_* code with a message
+ * retrievable through cb2_last_error() (thread-local).
+ *
+ * The two argument structs are the flat kernel-parameter records the reference already
+ * passes to its own kernels, extended by the few descriptor fields its dispatcher keys on:
+ *   cb2_gemm_args  <->  tv::gemm::GemmNVRTCParams        include/tensorview/gemm/core/nvrtc_params.h:23-36
+ *   cb2_conv_args  <->  tv::gemm::SparseConvNVRTCParams  include/tensorview/gemm/core/nvrtc_params.h:38-65
+ * dtype codes are tv::DType values (include/tensorview/dtypes.h:39-55): f32 0, i32 1,
+ * i8 3, f16 7.
+ */
+#ifndef CUMM_B200_H_
+#define CUMM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CB2_OK 0
+#define CB2_ERR_INVALID_ARG (-1) /* maps to std::invalid_argument / ValueError in the reference */
+#define CB2_ERR_RUNTIME (-2)     /* maps to std::runtime_error / RuntimeError */
+#define CB2_ERR_UNSUPPORTED (-3) /* no kernel for this descriptor ("can't find algo", cumm/gemm/main.py:1323-1333) */
+#define CB2_ERR_CUDA (-4)        /* a CUDA call failed (TV_CHECK_CUDA_ERR_V2, include/tensorview/core/common.h:170-175) */
+
+#define CB2_DTYPE_F32 0
+#define CB2_DTYPE_I32 1
+#define CB2_DTYPE_I8 3
+#define CB2_DTYPE_F16 7
+
+/* tv::gemm::ShuffleStrideType, include/tensorview/gemm/core/constants.h:30 */
+#define CB2_SHUFFLE_NONE 0
+#define CB2_SHUFFLE_AC 1
+#define CB2_SHUFFLE_AB 2
+
+/* tv::gemm::ConvOpType, include/tensorview/gemm/core/constants.h:18 */
+#define CB2_CONV_FORWARD 0
+#define CB2_CONV_BACKWARD_INPUT 1
+#define CB2_CONV_BACKWARD_WEIGHT 2
+
+/* tv::gemm::Activation, include/tensorview/gemm/core/constants.h:40-56 */
+#define CB2_ACT_NONE 0
+#define CB2_ACT_RELU 1
+#define CB2_ACT_SIGMOID 2
+#define CB2_ACT_LEAKY_RELU 3
+
+/*
+ * Gather-GEMM-scatter GEMM.  Replaces the launch made by GemmMainUnitTest::matmul2
+ * (cumm/gemm/main.py:1178-1335) after its host prologue (cumm/gemm/nvrtc_code.py:34-146).
+ *
+ *   ShuffleAC (and NoShuffle, with null index lists):
+ *     for i < m:  C[ic(i), :] = act(alpha * A[ia(i), :] * op(B) + beta * D[ic(i), :])
+ *     ia = indiceA, ic = indiceBorC; A is [*, k] row-major; B is [n, k] when trans_b
+ *     else [k, n].
+ *   ShuffleAB (requires trans_a and !trans_b):
+ *     C[i, j] = alpha * sum_p A[indiceA[p], i] * B[indiceBorC[p], j] + beta * D[i, j],
+ *     p < k.
+ * D defaults to C when null.  d_is_vector: D is a length-n vector added to every row
+ * (cumm/gemm/nvrtc_code.py:126-128,160-161).  Strides are in elements.
+ */
+typedef struct cb2_gemm_args {
+  int m, n, k;
+  const void *ptr_A, *ptr_B, *ptr_D;
+  void *ptr_C;
+  int64_t stride_A, stride_B, stride_C, stride_D;
+  const int32_t *indiceA, *indiceBorC, *indiceD;
+  float alpha, beta, act_alpha, act_beta;
+  int act_type;
+  int split_k_slices; /* accepted for interface parity; the split is chosen internally */
+  void *workspace;    /* ShuffleAB only: at least cb2_gemm_workspace_size() bytes */
+  size_t workspace_bytes;
+  /* descriptor fields (tv::gemm::GemmAlgoDesp, include/tensorview/gemm/core/params.h:24-45) */
+  int dtype_a, dtype_b, dtype_c;
+  int trans_a, trans_b, trans_c;
+  int shuffle_type;
+  int d_is_vector;
+  int rows_A; /* rows addressable in A (bounds for indiceA); rows_B likewise for ShuffleAB */
+  int rows_B;
+} cb2_gemm_args;
+
+/*
+ * Mask-based implicit-GEMM sparse convolution.  Replaces the launch made by
+ * ConvMainUnitTest::implicit_gemm2 (cumm/conv/main.py:485-745) after its host prologue
+ * (cumm/conv/nvrtc_code.py:20-260).  ptr_A/B/C follow the reference's role mapping
+ * (include/tensorview/gemm/core/utils.h:108-122):
+ *   forward          A = input  [*, C],  B = weight [K, kv, C], C = output [N, K]
+ *   backward input   A = dout   [*, K],  B = weight [K, kv, C], C = din    [N, C]
+ *   backward weight  A = dout   [N, K],  B = input  [*, C],     C = dW     [K, kv, C]
+ * N = number of (sorted) rows = second dimension of the neighbour table.
+ * indice_ptr [kv, N] int32 in original row order, -1 = no neighbour; mask_ptr: forward /
+ * backward input: per-row masks in sorted order [N]; backward weight: reduced masks, one
+ * word per mask_width sorted rows (the forward pass's mask_out_ptr).
+ * ptr_D: source rows for beta (default C); with d_is_bias a length-(output width) vector.
+ * int8 inference (dtype_a == i8, forward only): scale_pointer / bias_pointer fp32 per
+ * output channel; ptr_D (if beta != 0) are int8 rows added after scaling
+ * (cumm/gemm/output_op/linear.py:279-360).
+ */
+typedef struct cb2_conv_args {
+  const void *ptr_A, *ptr_B, *ptr_D;
+  void *ptr_C;
+  float alpha, beta, act_alpha, act_beta;
+  int act_type;
+  int split_k_slices; /* accepted for interface parity; the split is chosen internally */
+  void *workspace;    /* backward weight only: at least cb2_conv_workspace_size() bytes */
+  size_t workspace_bytes;
+  const uint32_t *mask_ptr;
+  uint32_t *mask_out_ptr; /* forward only, may be null: [ceil(N / 128)] tile masks */
+  const int32_t *indice_ptr;
+  const int32_t *mask_argsort_ptr;
+  uint32_t mask_filter;
+  int reverse_mask;
+  int mask_width;
+  int ndim, N, C, K;
+  int kernel_volume;
+  int mode;   /* 1 = cross-correlation (the only mode the reference launches, cumm/conv/nvrtc_code.py:204) */
+  int groups; /* 1 */
+  int d_is_bias;
+  const void *bias_pointer;
+  const void *scale_pointer;
+  /* descriptor fields (tv::gemm::ConvAlgoDesp, include/tensorview/gemm/core/params.h:166-190) */
+  int op_type;
+  int dtype_a, dtype_b, dtype_c; /* dtype_c = CB2_DTYPE_F32 is accepted for backward weight */
+  int is_int8_inference;
+  int rows_A; /* rows addressable in A; rows_B likewise for backward weight */
+  int rows_B;
+  int mask_words; /* backward weight: number of reduced-mask words available */
+} cb2_conv_args;
+
+/* Launches.  `stream` is a cudaStream_t (the reference passes it as uintptr_t,
+ * include/tensorview/gemm/core/params.h:346,420). */
+int cb2_gemm_run(const cb2_gemm_args *args, void *stream);
+int cb2_conv_run(const cb2_conv_args *args, void *stream);
+
+/* Bytes of scratch the call needs in args->workspace (0 when none).  Replaces
+ * GemmAlgoDesp::query_workspace_size / ConvAlgoDesp::query_conv_workspace_size
+ * (include/tensorview/gemm/core/params.h:115-132,286-307); unlike the reference the
+ * callee never allocates. */
+size_t cb2_gemm_workspace_size(const cb2_gemm_args *args);
+size_t cb2_conv_workspace_size(const cb2_conv_args *args);
+
+/* Rows of one output tile, i.e. the granularity of mask_out_ptr and the mask_width to
+ * hand to backward weight (the reference uses the forward kernel's tile_shape[0],
+ * cumm/conv/main_real_spconv.py:176-177). */
+int cb2_tile_m(void);
+
+/* Message of the last failing call on this host thread. */
+const char *cb2_last_error(void);
+
+/* Kernels never spin without bound: a wait that runs out, or a row index outside
+ * rows_A / rows_B, sets a per-device status word instead.  This call synchronises the
+ * current device, returns the word (0 = ok, 1 = wait timed out, 2 = row index out of
+ * range) in *status and clears it. */
+int cb2_device_status(int *status);
+
+/* Number of kernels this library has launched from the calling process (all threads). */
+uint64_t cb2_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CUMM_B200_H_ */
