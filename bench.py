@@ -1,0 +1,481 @@
+#!/usr/bin/env python
+"""Benchmark of the sparse-convolution hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W          (N > 1: launched by torch.distributed.run)
+    python bench.py --impl reference ...                    (the CPU arm: numpy statement on host cores)
+
+Workload ("scale-out" configuration): 8 scenes x 120 000 unique voxels sampled uniformly in
+a [41,1600,1408] grid (seed 4, one generator stream per scene), 3x3x3 submanifold conv,
+C_in = C_out = 128, fp16 with fp32 accumulation.  A step is forward + input gradient +
+weight gradient over the batch.  Scenes are sharded over the ranks (weights replicated, no
+collective for forward / input gradient); the fp32 weight-gradient partials [128,27,128]
+are summed by one NCCL all-reduce and cast to fp16.  Total work is fixed: strong scaling.
+
+The timed loop replays CUDA graphs of the step over rotating buffer sets whose footprint
+exceeds the 126 MB L2, so HBM figures are cold-cache.  One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+N_SCENES = 8
+VOXELS_PER_SCENE = 120000
+C_IN = C_OUT = 128
+KV = 27
+METRIC = "sparse-conv effective TFLOP/s (fwd+dgrad+wgrad, fp16, C=K=128, 3x3x3 subm)"
+WORKLOAD = "scale-out: 8 scenes x 120k voxels, grid [41,1600,1408], seed 4, fwd+dgrad+wgrad fp16 C=K=128"
+L2_BYTES = 126 * 1024 * 1024
+
+
+def scene_tables(scene_ids):
+    from cumm_b200 import workloads as W
+    tabs = [W.build_tables(W.sample_coords(VOXELS_PER_SCENE, [4, b], batch=b)) for b in scene_ids]
+    return W.concat_scenes(tabs) if len(tabs) > 1 else tabs[0]
+
+
+def host_features(n_in, n_out, seed):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((n_in, C_IN), dtype=np.float32).astype(np.float16)
+    dout = rng.standard_normal((n_out, C_OUT), dtype=np.float32).astype(np.float16)
+    w = (rng.standard_normal((KV, C_IN, C_OUT), dtype=np.float32) / np.sqrt(KV * C_IN)).astype(np.float16)
+    return x, dout, np.ascontiguousarray(w.transpose(2, 0, 1))  # weight in the [K, kv, C] layout
+
+
+def op_bytes(n_rows, num_tiles, C=C_IN, K=C_OUT, es=2):
+    """Algorithmic bytes of one launch: features in + out, weights, neighbour table, mask + sort."""
+    fwd = n_rows * C * es + n_rows * K * es + KV * C * K * es + 4 * KV * n_rows + 8 * n_rows
+    wgrad = n_rows * C * es + n_rows * K * es + KV * C * K * es + 4 * KV * n_rows + 4 * n_rows + 4 * num_tiles
+    return fwd, wgrad
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index = index
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._halt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._halt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def finish(self):
+        self._halt.set()
+        self.join(timeout=1.0)
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def physical_gpu_index(local_rank):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except Exception:
+            return local_rank
+    return local_rank
+
+
+# ----------------------------------------------------------------------------------------
+# CPU arm: the reference's numpy statement of the op on the host cores
+# ----------------------------------------------------------------------------------------
+def cpu_sample_step(O, x, dout, w, indices):
+    t = time.perf_counter()
+    O.np_forward(x, w, indices)
+    O.np_dgrad(dout, w, indices, x.shape[0])
+    O.np_wgrad(dout, x, indices)
+    return time.perf_counter() - t
+
+
+def cpu_setup(voxels):
+    from cumm_b200 import workloads as W
+    from oracle import oracle as O
+    tb = W.build_tables(W.sample_coords(voxels, [4, 0]))
+    x, dout, w = host_features(tb.n_in, tb.n_out, [4, 100])
+    return O, tb, x, dout, w
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    voxels = VOXELS_PER_SCENE
+    O, tb, x, dout, w = cpu_setup(voxels)
+    flops = 3 * 2 * tb.num_pairs * C_IN * C_OUT
+    for _ in range(max(args.warmup, 1)):
+        cpu_sample_step(O, x, dout, w, tb.indices)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_sample_step(O, x, dout, w, tb.indices)
+    dt = (time.perf_counter() - t0) / args.steps
+    val = flops / dt / 1e12
+    cores = os.cpu_count()
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                         "sample": f"one scene of {voxels} voxels per step (1/8 of the batch), numpy gather-"
+                                   "matmul-scatter with the BLAS thread pool; the reference's own kernels and CPU "
+                                   "simulator need its code generator, which is not installable offline"},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "voxels_per_s": 3 * tb.n_out / dt,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the single-scene configurations and CPU baseline")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from cumm_b200 import _lib
+    from cumm_b200.layer import DeviceTables, SparseConvLayer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+
+    # ---- shard scenes over ranks
+    per = N_SCENES // world if N_SCENES % world == 0 else None
+    if per is None:
+        ids = [b for b in range(N_SCENES) if b % world == rank]
+    else:
+        ids = list(range(rank * per, (rank + 1) * per))
+    tb = scene_tables(ids)
+    x_h, dout_h, w_h = host_features(tb.n_in, tb.n_out, [4, 100, rank])
+    _, _, w_h = host_features(8, 8, [4, 100])  # identical weights on every rank
+    num_tiles = (tb.n_out + 127) // 128
+    fwd_bytes, wgrad_bytes = op_bytes(tb.n_out, num_tiles)
+    step_bytes = 2 * fwd_bytes + wgrad_bytes
+    nsets = max(2, int(np.ceil(2.2 * L2_BYTES / step_bytes)))
+    nsets = min(nsets, 12)
+
+    stream = torch.cuda.Stream(device=dev)
+    sets = []
+    with torch.cuda.stream(stream):
+        w_d = torch.from_numpy(w_h).to(dev)
+        for i in range(nsets):
+            t = DeviceTables.from_host(tb, dev)
+            x = torch.from_numpy(x_h).to(dev)
+            dout = torch.from_numpy(dout_h).to(dev)
+            out = torch.zeros((tb.n_out, C_OUT), dtype=torch.float16, device=dev)
+            din = torch.zeros((tb.n_in, C_IN), dtype=torch.float16, device=dev)
+            dw32 = torch.zeros((C_OUT, KV, C_IN), dtype=torch.float32, device=dev)
+            dw16 = torch.zeros((C_OUT, KV, C_IN), dtype=torch.float16, device=dev)
+            layer = SparseConvLayer(t, w_d, x, out, dout, din, dw32, stream=stream.cuda_stream)
+            sets.append(dict(t=t, x=x, dout=dout, out=out, din=din, dw32=dw32, dw16=dw16, layer=layer))
+    stream.synchronize()
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def step_ops(s, events=None):
+        L = s["layer"]
+        if events:
+            events[0].record(stream)
+        L.fwd.launch()
+        if events:
+            events[1].record(stream)
+        L.dgrad.launch()
+        if events:
+            events[2].record(stream)
+        L.wgrad.launch()
+        if events:
+            events[3].record(stream)
+        if world > 1:
+            dist.all_reduce(s["dw32"])
+        s["dw16"].copy_(s["dw32"])
+        if events:
+            events[4].record(stream)
+
+    # warm-up outside graphs (first-call set-up: attributes, status buffer, NCCL channels)
+    with torch.cuda.stream(stream):
+        for s in sets:
+            step_ops(s)
+    stream.synchronize()
+    assert _lib.device_status() == 0, "kernel status word set during warm-up"
+
+    graphs = []
+    with torch.cuda.stream(stream):
+        for s in sets:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                step_ops(s)
+            graphs.append(g)
+    stream.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.cuda.stream(stream):
+        for i in range(args.warmup):
+            graphs[i % nsets].replay()
+    barrier()
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    launches0 = _lib.launch_count()
+    e0, e1 = ev(), ev()
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        for i in range(args.steps):
+            graphs[i % nsets].replay()
+        e1.record(stream)
+    barrier()
+    clocks = sampler.finish()
+    ms_total = e0.elapsed_time(e1)
+    # graph replays do not pass through the library's launch counter: 4 kernels per step
+    gpu_launches = 4 * args.steps
+    del launches0
+
+    # per-op durations, live, events between the launches (not graph-captured)
+    op_ms = np.zeros(4)
+    reps = max(5, min(args.steps, 20))
+    with torch.cuda.stream(stream):
+        for i in range(reps):
+            evs = [ev() for _ in range(5)]
+            step_ops(sets[i % nsets], evs)
+            stream.synchronize()
+            op_ms += [evs[j].elapsed_time(evs[j + 1]) for j in range(4)]
+    op_ms /= reps
+    status = _lib.device_status()
+
+    ms_step = ms_total / args.steps
+    t = torch.tensor([ms_step, float(tb.num_pairs), float(tb.n_out), float(status)], dtype=torch.float64, device=dev)
+    if world > 1:
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        tsum = t.clone()
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        ms_step, pairs_total, rows_total, status = float(tmax[0]), float(tsum[1]), float(tsum[2]), int(tmax[3])
+    else:
+        pairs_total, rows_total = float(tb.num_pairs), float(tb.n_out)
+    flops_step = 3 * 2 * pairs_total * C_IN * C_OUT
+    value = flops_step / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end through the public API with host buffers (features in, weight gradient out)
+    s0 = sets[0]
+    x_pin = torch.from_numpy(x_h).pin_memory()
+    dout_pin = torch.from_numpy(dout_h).pin_memory()
+    dw_pin = torch.empty((C_OUT, KV, C_IN), dtype=torch.float16).pin_memory()
+    e2e_steps = max(3, min(args.steps, 10))
+
+    def e2e_step():
+        s0["x"].copy_(x_pin, non_blocking=True)
+        s0["dout"].copy_(dout_pin, non_blocking=True)
+        step_ops(s0)
+        dw_pin.copy_(s0["dw16"], non_blocking=True)
+
+    with torch.cuda.stream(stream):
+        e2e_step()
+    barrier()
+    a0, a1 = ev(), ev()
+    with torch.cuda.stream(stream):
+        a0.record(stream)
+        for _ in range(e2e_steps):
+            e2e_step()
+        a1.record(stream)
+    barrier()
+    e2e_ms = a0.elapsed_time(a1) / e2e_steps
+    if world > 1:
+        tt = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e_ms = float(tt[0])
+    e2e_value = flops_step / (e2e_ms * 1e-3) / 1e12
+    h2d = x_pin.numel() * 2 + dout_pin.numel() * 2
+    d2h = dw_pin.numel() * 2
+
+    line = None
+    if rank == 0:
+        peaks = {}
+        pk = ROOT / "MEASURED_PEAKS.json"
+        if pk.exists():
+            peaks = json.loads(pk.read_text())
+        hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+        peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
+        names = ["forward", "backward_input", "backward_weight(+reduce)", "allreduce+cast"]
+        dom = int(np.argmax(op_ms[:3]))
+        dom_bytes = [fwd_bytes, fwd_bytes, wgrad_bytes][dom]
+        achieved = dom_bytes / (op_ms[dom] * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "scenes_per_rank": len(ids), "rows_per_rank": tb.n_out,
+                       "pairs_total": pairs_total, "parallelism": f"scene-sharded x{world}, wgrad fp32 all-reduce",
+                       "l2": f"rotating {nsets} buffer sets ({nsets * step_bytes / 1e6:.0f} MB touched) > 126 MB L2",
+                       "timed_region": "CUDA-graph replays of fwd+dgrad+wgrad(+allreduce)+cast"},
+            "voxels_per_s": 3 * rows_total / (ms_step * 1e-3),
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms},
+            "gpu_launches": gpu_launches,
+            "roofline": {"bound": "hbm", "kernel": names[dom], "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": achieved / hbm_peak, "peak_source": peak_src, "traffic": None,
+                         "algorithmic_bytes_per_launch": dom_bytes, "us_per_launch": op_ms[dom] * 1e3},
+            "per_op_us": {names[i]: op_ms[i] * 1e3 for i in range(4)},
+            "per_op_gbs": {names[i]: [fwd_bytes, fwd_bytes, wgrad_bytes][i] / (op_ms[i] * 1e-3) / 1e9 for i in range(3)},
+            "status_word": status,
+        }
+
+    if rank == 0 and world == 1 and not args.no_extras:
+        line["single_scene"] = single_scene_configs(torch, dev, stream)
+        line["cpu_baseline"] = cpu_baseline()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def single_scene_configs(torch, dev, stream):
+    """The 150 000-voxel single-scene configurations, each op timed alone with an L2 flush
+    (a 256 MB write) before every launch: fp16 C=K=128 fwd/dgrad/wgrad and int8 stride-2 fwd."""
+    from cumm_b200 import _lib
+    from cumm_b200 import workloads as W
+    from cumm_b200.layer import DeviceTables, SparseConvLayer
+    res = {}
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    coords = W.sample_coords(150000, 1)
+    hbm_peak = 6531.0
+    pk = ROOT / "MEASURED_PEAKS.json"
+    if pk.exists():
+        hbm_peak = float(json.loads(pk.read_text()).get("hbm_gbs", hbm_peak))
+
+    def time_call(call, reps=20):
+        ts = []
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                call.launch()
+            for _ in range(reps):
+                flush.fill_(1)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                call.launch()
+                b.record(stream)
+                stream.synchronize()
+                ts.append(a.elapsed_time(b))
+        return float(np.median(ts)) * 1e3  # us
+
+    with torch.cuda.stream(stream):
+        tb = W.build_tables(coords)
+        rng = np.random.default_rng(2)
+        x = torch.from_numpy(rng.standard_normal((tb.n_in, 128), dtype=np.float32).astype(np.float16)).to(dev)
+        dout = torch.from_numpy(rng.standard_normal((tb.n_out, 128), dtype=np.float32).astype(np.float16)).to(dev)
+        w = torch.from_numpy((rng.standard_normal((128, 27, 128), dtype=np.float32) / 58.8).astype(np.float16)).to(dev)
+        out = torch.zeros((tb.n_out, 128), dtype=torch.float16, device=dev)
+        din = torch.zeros_like(x)
+        dw = torch.zeros((128, 27, 128), dtype=torch.float16, device=dev)
+        t = DeviceTables.from_host(tb, dev)
+        L = SparseConvLayer(t, w, x, out, dout, din, dw, stream=stream.cuda_stream)
+    stream.synchronize()
+    fb, wb = op_bytes(tb.n_out, (tb.n_out + 127) // 128)
+    flops = 2 * tb.num_pairs * 128 * 128
+    for name, call, nbytes in (("fp16_forward", L.fwd, fb), ("fp16_backward_input", L.dgrad, fb),
+                               ("fp16_backward_weight", L.wgrad, wb)):
+        us = time_call(call)
+        res[name] = {"us": us, "eff_tflops": flops / us / 1e6, "gbs": nbytes / us / 1e3,
+                     "frac_hbm_measured": nbytes / us / 1e3 / hbm_peak, "gvoxels_per_s": tb.n_out / us / 1e3}
+    # int8 stride-2 regular conv, k=3, pad=1
+    with torch.cuda.stream(stream):
+        tb3 = W.build_tables(coords, stride=(2, 2, 2), subm=False)
+        rng = np.random.default_rng(3)
+        x8 = torch.from_numpy(rng.integers(-127, 128, (tb3.n_in, 128)).astype(np.int8)).to(dev)
+        w8 = torch.from_numpy(rng.integers(-127, 128, (128, 27, 128)).astype(np.int8)).to(dev)
+        sc = torch.from_numpy(rng.uniform(1e-3, 1e-2, 128).astype(np.float32)).to(dev)
+        bi = torch.from_numpy(rng.standard_normal(128).astype(np.float32)).to(dev)
+        o8 = torch.zeros((tb3.n_out, 128), dtype=torch.int8, device=dev)
+        t3 = DeviceTables.from_host(tb3, dev)
+        L3 = SparseConvLayer(t3, w8, x8, o8, stream=stream.cuda_stream)
+        L3.prepare_int8(sc, bi)
+    stream.synchronize()
+    b3 = tb3.n_in * 128 + tb3.n_out * 128 + 27 * 128 * 128 + 4 * 27 * tb3.n_out + 8 * tb3.n_out + 2 * 128 * 4
+    us = time_call(L3.fwd)
+    ops = 2 * tb3.num_pairs * 128 * 128
+    res["int8_forward_stride2"] = {"us": us, "eff_tops": ops / us / 1e6, "gbs": b3 / us / 1e3,
+                                   "frac_hbm_measured": b3 / us / 1e3 / hbm_peak, "gvoxels_per_s": tb3.n_out / us / 1e3}
+    res["status_word"] = _lib.device_status()
+    return res
+
+
+def cpu_baseline():
+    """The numpy statement of one scene's step on the host cores, a bounded sample."""
+    O, tb, x, dout, w = cpu_setup(VOXELS_PER_SCENE)
+    cpu_sample_step(O, x, dout, w, tb.indices)
+    n, t_total = 0, 0.0
+    while t_total < 10.0 and n < 20:
+        t_total += cpu_sample_step(O, x, dout, w, tb.indices)
+        n += 1
+    dt = t_total / n
+    flops = 3 * 2 * tb.num_pairs * C_IN * C_OUT
+    return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"{n} steps over one scene of {VOXELS_PER_SCENE} voxels (1/8 of the batch), numpy "
+                      "gather-matmul-scatter, BLAS thread pool", "ms_per_sample_step": dt * 1e3}
+
+
+if __name__ == "__main__":
+    main()

@@ -724,3 +724,62 @@ def run_nvrtc_gemm_kernel(params: GemmParams) -> None:
 def run_nvrtc_conv_kernel(params: ConvParams) -> None:
     """cumm/tensorview_bind.py:152-167; see :func:`run_nvrtc_gemm_kernel`."""
     run_conv(params)
+
+
+class PreparedCall:
+    """A validated call with its flat argument record built once, for launch-bound loops
+    (replays, CUDA-graph capture): ``launch()`` only crosses the C ABI."""
+
+    def __init__(self, kind: str, args, device: int, stream: int, keep):
+        self._kind = kind
+        self._args = args
+        self._device = device
+        self._stream = int(stream)
+        self._keep = keep  # tensors whose memory the record points at
+        L = _lib.load()
+        self._fn = L.cb2_conv_run if kind == "conv" else L.cb2_gemm_run
+
+    def launch(self, stream: Optional[int] = None) -> None:
+        s = self._stream if stream is None else int(stream)
+        rc = self._fn(ctypes.byref(self._args), ctypes.c_void_p(s))
+        if rc:
+            _lib.raise_for(rc)
+
+
+def prepare_conv(params: ConvParams) -> PreparedCall:
+    """Validate ``params`` like :func:`run_conv` and return a replayable call.  The tensors
+    in ``params`` must stay alive and in place while the call is in use."""
+    L = _lib.load()
+    args = _conv_args(params)
+    need = L.cb2_conv_workspace_size(ctypes.byref(args))
+    keep = [params.input, params.weight, params.output, params.indices, params.mask, params.mask_argsort,
+            params.mask_output, params.bias, params.scale, params.output_add]
+    if need:
+        t = as_view(params.workspace)
+        if t is None or t.nbytes() < need:
+            import torch
+            ws = torch.empty(need, dtype=torch.uint8, device=f"cuda:{args._device}")
+            keep.append(ws)
+            args.workspace, args.workspace_bytes = ws.data_ptr(), need
+        else:
+            keep.append(params.workspace)
+            args.workspace, args.workspace_bytes = t.data_ptr(), t.nbytes()
+    return PreparedCall("conv", args, args._device, params.stream, keep)
+
+
+def prepare_gemm(params: GemmParams) -> PreparedCall:
+    L = _lib.load()
+    args = _gemm_args(params)
+    need = L.cb2_gemm_workspace_size(ctypes.byref(args))
+    keep = [params.a, params.b, params.c, params.d, params.a_inds, params.b_inds, params.c_inds]
+    if need:
+        t = as_view(params.workspace)
+        if t is None or t.nbytes() < need:
+            import torch
+            ws = torch.empty(need, dtype=torch.uint8, device=f"cuda:{args._device}")
+            keep.append(ws)
+            args.workspace, args.workspace_bytes = ws.data_ptr(), need
+        else:
+            keep.append(params.workspace)
+            args.workspace, args.workspace_bytes = t.data_ptr(), t.nbytes()
+    return PreparedCall("gemm", args, args._device, params.stream, keep)

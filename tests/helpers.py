@@ -105,8 +105,8 @@ def run_conv_dgrad(torch, dout, w, tb, *, din_init=None, beta=0.0, use_reverse=F
     p.weight = dev(w, torch)
     p.output = dev(dout, torch)
     if use_reverse:
-        # submanifold: the forward tables serve, with the filter order reversed
-        p.indices = dev(tb.indices, torch)
+        # submanifold: the forward masks and sort serve, with the tile mask bit-reversed
+        p.indices = dev(tb.indices_bwd, torch)
         p.mask = mask_to_torch(tb.mask, torch)
         p.mask_argsort = dev(tb.mask_argsort, torch)
         p.reverse_mask = True
