@@ -178,6 +178,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the single-scene configurations and CPU baseline")
+    ap.add_argument("--single-scene-only", action="store_true",
+                    help="run only the 150k-voxel single-scene configurations (few launches: the profiling case)")
+    ap.add_argument("--reps", type=int, default=20, help="timed launches per op in the single-scene configurations")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
@@ -198,6 +201,10 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
     _lib.load()
+    if args.single_scene_only:
+        st = torch.cuda.Stream(device=dev)
+        print(json.dumps({"single_scene": single_scene_configs(torch, dev, st, reps=args.reps, warm=1)}), flush=True)
+        return
 
     # ---- shard scenes over ranks
     per = N_SCENES // world if N_SCENES % world == 0 else None
@@ -392,7 +399,7 @@ def main():
         dist.destroy_process_group()
 
 
-def single_scene_configs(torch, dev, stream):
+def single_scene_configs(torch, dev, stream, reps=20, warm=3):
     """The 150 000-voxel single-scene configurations, each op timed alone with an L2 flush
     (a 256 MB write) before every launch: fp16 C=K=128 fwd/dgrad/wgrad and int8 stride-2 fwd."""
     from cumm_b200 import _lib
@@ -406,10 +413,10 @@ def single_scene_configs(torch, dev, stream):
     if pk.exists():
         hbm_peak = float(json.loads(pk.read_text()).get("hbm_gbs", hbm_peak))
 
-    def time_call(call, reps=20):
+    def time_call(call):
         ts = []
         with torch.cuda.stream(stream):
-            for _ in range(3):
+            for _ in range(warm):
                 call.launch()
             for _ in range(reps):
                 flush.fill_(1)

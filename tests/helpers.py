@@ -135,6 +135,8 @@ def run_conv_wgrad(torch, dout, x, tb, reduced_mask, *, kv=27, dw_init=None, bet
     p.mask = mask_to_torch(reduced_mask, torch)
     p.mask_argsort = dev(tb.mask_argsort, torch)
     p.mask_width = mask_width
+    if mask_width < 128:
+        p.conv_algo_desp.tile_shape[2] = mask_width  # the reference requires mask_width % tile_k == 0
     p.mask_filter = mask_filter
     p.alpha, p.beta = alpha, beta
     p.split_k_slices = 32

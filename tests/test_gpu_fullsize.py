@@ -39,7 +39,8 @@ def test_mask_igemm_fp16_all_three_ops(torch, oracle, scene):
     H.check_status()
     # linearity: conv(2x) == 2 conv(x) exactly in fp16 (power-of-two scaling)
     out2, _ = H.run_conv_fwd(torch, (x * np.float16(2)).astype(np.float16), w, tb)
-    assert (out2.astype(np.float32) == 2 * out.astype(np.float32)).all()
+    normal = np.abs(out.astype(np.float32)) >= 2.0 ** -13  # fp16 subnormals do not scale exactly
+    assert (out2.astype(np.float32)[normal] == 2 * out.astype(np.float32)[normal]).all()
 
 
 def test_int8_stride2_bit_exact(torch, oracle, scene):

@@ -104,9 +104,12 @@ def test_native_sparse_conv_as_27_gemm_calls(torch, oracle):
     w = (rng.standard_normal((K, 27, C)) / np.sqrt(27 * C) * 4).astype(np.float16)
     xd, wd = H.dev(x, torch), H.dev(w, torch)
     out = torch.zeros((tb.n_out, K), dtype=torch.float16, device="cuda")
+    want = np.zeros((tb.n_out, K), np.float16)  # same call sequence on the oracle: fp16 round trip per offset
     for f, (i_idx, o_idx) in enumerate(oracle.np_pairs(tb.indices)):
         if len(o_idx) == 0:
             continue
+        oracle.gemm_shuffle_ac(x, np.ascontiguousarray(w[:, f, :]), want, i_idx.astype(np.int32),
+                               o_idx.astype(np.int32), beta=1.0)
         p = GemmParams()
         p.algo_desp = H.gemm_desp(ShuffleStrideType.ShuffleAC, trans_b=True)
         p.a = xd
@@ -117,7 +120,10 @@ def test_native_sparse_conv_as_27_gemm_calls(torch, oracle):
         GemmMainUnitTest.matmul2(p)
     torch.cuda.synchronize()
     H.check_status()
-    H.assert_close_f16(out.cpu().numpy(), oracle.np_forward(x, w, tb.indices), "27-call native conv")
+    H.assert_close_f16(out.cpu().numpy(), want, "27-call native conv")
+    # and close to the single-rounding result (looser: up to 27 fp16 roundings per element)
+    np.testing.assert_allclose(out.cpu().numpy().astype(np.float32), oracle.np_forward(x, w, tb.indices),
+                               rtol=3e-2, atol=3e-2)
 
 
 @pytest.mark.parametrize("kk,m,n", [(1, 64, 64), (200, 64, 64), (5000, 64, 64), (5000, 128, 128), (3000, 128, 64),
