@@ -290,10 +290,8 @@ int run_wgrad(DeviceState *dev, WgradParams &p, void *workspace, size_t workspac
   r.alpha = alpha;
   r.beta = beta;
   r.out_f32 = out_f32;
-  const long long total = (long long)p.m_total * p.n_total;
-  int bx = (int)((total + 255) / 256);
-  if (bx > 64)
-    bx = 64;
+  const long long total4 = (long long)p.m_total * (p.n_total / 4);
+  const int bx = (int)((total4 + 31) / 32);
   wgrad_reduce_kernel<<<dim3(bx, p.kv), 256, 0, stream>>>(r);
   CB2_CUDA(cudaGetLastError());
   g_launches.fetch_add(1);

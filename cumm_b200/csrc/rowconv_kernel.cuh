@@ -271,6 +271,8 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
           const uint32_t trow = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
                                 static_cast<uint32_t>(buf * BLOCK_N);
           const bool use_src = (p.src_mode != kSrcNone) && (p.beta != 0.f);
+          // fast path: out = cvt(acc); everything else goes through the general epilogue
+          const bool plain = !use_src && p.act_type == 0 && p.alpha == 1.f;
 #pragma unroll 1
           for (int round = 0; round < BLOCK_N / 32; ++round) {
             uint32_t v[32];
@@ -285,43 +287,61 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
             const int ncol0 = n0 + round * 32;
             if constexpr (KIND == 0) {
               uint32_t packed[16];
-              uint4 srcv[4];
-              if (use_src && p.src_mode == kSrcRows && o >= 0) {
-                const uint4 *sp = reinterpret_cast<const uint4 *>(
-                    reinterpret_cast<const __half *>(p.src) + (long long)o * p.lds + ncol0);
+              if (plain) {
 #pragma unroll
-                for (int q = 0; q < 4; ++q)
-                  srcv[q] = (ncol0 + q * 8 < p.nn) ? __ldg(sp + q) : make_uint4(0, 0, 0, 0);
-              }
-#pragma unroll
-              for (int i = 0; i < 32; i += 2) {
-                float x0 = __uint_as_float(v[i]), x1 = __uint_as_float(v[i + 1]);
-                float t0, t1;
+                for (int i = 0; i < 32; i += 2) {
+                  __half2 h2 = __floats2half2_rn(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+                  packed[i / 2] = *reinterpret_cast<uint32_t *>(&h2);
+                }
+              } else {
+                float t[32];
                 if (use_src) {
-                  float s0 = 0.f, s1 = 0.f;
                   if (p.src_mode == kSrcRows) {
+                    uint4 srcv[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                      srcv[q] = make_uint4(0, 0, 0, 0);
                     if (o >= 0) {
+                      const uint4 *sp = reinterpret_cast<const uint4 *>(
+                          reinterpret_cast<const __half *>(p.src) + (long long)o * p.lds + ncol0);
+#pragma unroll
+                      for (int q = 0; q < 4; ++q)
+                        if (ncol0 + q * 8 < p.nn)
+                          srcv[q] = __ldg(sp + q);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
                       const __half2 h = reinterpret_cast<const __half2 *>(srcv)[i / 2];
-                      s0 = __low2float(h);
-                      s1 = __high2float(h);
+                      t[i] = __fmaf_rn(p.alpha, __uint_as_float(v[i]), __fmul_rn(p.beta, __low2float(h)));
+                      t[i + 1] = __fmaf_rn(p.alpha, __uint_as_float(v[i + 1]), __fmul_rn(p.beta, __high2float(h)));
                     }
                   } else {
                     const __half *bv = reinterpret_cast<const __half *>(p.src);
-                    if (ncol0 + i < p.nn)
-                      s0 = __half2float(__ldg(bv + ncol0 + i));
-                    if (ncol0 + i + 1 < p.nn)
-                      s1 = __half2float(__ldg(bv + ncol0 + i + 1));
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                      const float sv = (ncol0 + i < p.nn) ? __half2float(__ldg(bv + ncol0 + i)) : 0.f;
+                      t[i] = __fmaf_rn(p.alpha, __uint_as_float(v[i]), __fmul_rn(p.beta, sv));
+                    }
                   }
-                  t0 = __fmaf_rn(p.alpha, x0, __fmul_rn(p.beta, s0));
-                  t1 = __fmaf_rn(p.alpha, x1, __fmul_rn(p.beta, s1));
                 } else {
-                  t0 = __fmul_rn(p.alpha, x0);
-                  t1 = __fmul_rn(p.alpha, x1);
+#pragma unroll
+                  for (int i = 0; i < 32; ++i)
+                    t[i] = __fmul_rn(p.alpha, __uint_as_float(v[i]));
                 }
-                t0 = apply_act(t0, p.act_type, p.act_alpha);
-                t1 = apply_act(t1, p.act_type, p.act_alpha);
-                __half2 h2 = __halves2half2(__float2half_rn(t0), __float2half_rn(t1));
-                packed[i / 2] = *reinterpret_cast<uint32_t *>(&h2);
+                if (p.act_type == 1) {
+#pragma unroll
+                  for (int i = 0; i < 32; ++i)
+                    t[i] = fmaxf(t[i], 0.f);
+                } else if (p.act_type != 0) {
+#pragma unroll
+                  for (int i = 0; i < 32; ++i)
+                    t[i] = apply_act(t[i], p.act_type, p.act_alpha);
+                }
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                  __half2 h2 = __floats2half2_rn(t[i], t[i + 1]);
+                  packed[i / 2] = *reinterpret_cast<uint32_t *>(&h2);
+                }
               }
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
@@ -332,33 +352,40 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
               }
             } else {
               uint32_t packed[8];
-              uint4 srcv[2];
-              if (use_src && o >= 0) {
-                const uint4 *sp = reinterpret_cast<const uint4 *>(
-                    reinterpret_cast<const int8_t *>(p.src) + (long long)o * p.lds + ncol0);
+              float t[32];
 #pragma unroll
-                for (int q = 0; q < 2; ++q)
-                  srcv[q] = (ncol0 + q * 16 < p.nn) ? __ldg(sp + q) : make_uint4(0, 0, 0, 0);
+              for (int i = 0; i < 32; ++i) {
+                const int col = round * 32 + i;
+                t[i] = __fmaf_rn(s_scale[col], __int2float_rn(static_cast<int>(v[i])), s_bias[col]);
               }
+              if (use_src) {
+                uint4 srcv[2];
+                srcv[0] = srcv[1] = make_uint4(0, 0, 0, 0);
+                if (o >= 0) {
+                  const uint4 *sp = reinterpret_cast<const uint4 *>(
+                      reinterpret_cast<const int8_t *>(p.src) + (long long)o * p.lds + ncol0);
 #pragma unroll
-              for (int i = 0; i < 32; i += 4) {
-                uint32_t w = 0;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const int col = round * 32 + i + j;
-                  float acc = __int2float_rn(static_cast<int>(v[i + j]));
-                  float t = __fmaf_rn(s_scale[col], acc, s_bias[col]);
-                  if (use_src) {
-                    float s = 0.f;
-                    if (o >= 0)
-                      s = static_cast<float>(reinterpret_cast<const int8_t *>(srcv)[i + j]);
-                    t = __fmaf_rn(p.beta, s, t);
-                  }
-                  t = apply_act(t, p.act_type, p.act_alpha);
-                  w |= cvt_sat_s8(t) << (8 * j);
+                  for (int q = 0; q < 2; ++q)
+                    if (ncol0 + q * 16 < p.nn)
+                      srcv[q] = __ldg(sp + q);
                 }
-                packed[i / 4] = w;
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  t[i] = __fmaf_rn(p.beta, static_cast<float>(reinterpret_cast<const int8_t *>(srcv)[i]), t[i]);
               }
+              if (p.act_type == 1) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  t[i] = fmaxf(t[i], 0.f);
+              } else if (p.act_type != 0) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  t[i] = apply_act(t[i], p.act_type, p.act_alpha);
+              }
+#pragma unroll
+              for (int i = 0; i < 32; i += 4)
+                packed[i / 4] = cvt_sat_s8(t[i]) | (cvt_sat_s8(t[i + 1]) << 8) | (cvt_sat_s8(t[i + 2]) << 16) |
+                                (cvt_sat_s8(t[i + 3]) << 24);
 #pragma unroll
               for (int q = 0; q < 2; ++q) {
                 const int c = round * CH_PER_ROUND + q;
@@ -424,6 +451,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
             if (ok)
               ok = mbar_wait(full_a(stage), (step / Cfg::SA) & 1, abort_flag);
             if (ok) {
+              fence_proxy_async_smem();  // gathered rows were written through the generic proxy
               tc_fence_after();
               const uint32_t a_base = sbase + Cfg::OFF_A + stage * Cfg::A_STAGE_BYTES;
               const uint32_t b_base = sbase + Cfg::OFF_B + cur_slot * Cfg::B_SLOT_BYTES;
@@ -523,13 +551,21 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
     int step = 0;
     int o = -1;
     const uint8_t *a_bytes = reinterpret_cast<const uint8_t *>(p.a);
+    auto load_o = [&](int tile) -> int {
+      const int r = tile * 128 + gt;
+      if (tile >= ntiles || r >= p.n_rows)
+        return -1;
+      return (p.mode == kModeMaskConv) ? __ldg(p.argsort + r) : r;
+    };
+    int o_next_tile = blockIdx.x;
+    int o_next = load_o(o_next_tile);
     walk_steps(
         p, ntiles, kpasses,
         [&](int tile, uint32_t, bool) -> bool {
-          const int r = tile * 128 + gt;
-          o = -1;
-          if (r < p.n_rows)
-            o = (p.mode == kModeMaskConv) ? __ldg(p.argsort + r) : r;
+          // the sort index of this thread's row, fetched one tile ahead of its use
+          o = (tile == o_next_tile) ? o_next : load_o(tile);
+          o_next_tile = tile + gridDim.x;
+          o_next = load_o(o_next_tile);
           return true;
         },
         [&](int tile, int f, int kp, bool, bool) -> bool {
@@ -575,12 +611,13 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
             const uint8_t *srcp = valid ? a_bytes + ((long long)ridx * p.lda) * Cfg::ES + byte_off : a_bytes;
             cp_async_16(dst, srcp, valid ? 16u : 0u);
           }
-          cp_async_commit();
-          cp_async_wait<0>();
-          fence_proxy_async_smem();
-          mbar_arrive(full_a(g));
+          // The barrier is signalled by the copy engine when this thread's copies have landed;
+          // the thread itself runs on to its next step.  The consumer makes the data visible
+          // to the tensor core with a proxy fence after its wait.
+          cp_async_mbar_arrive_noinc(full_a(g));
           return true;
         });
+    cp_async_wait_all();
   }
 
   // ---------------------------------------------------------------- teardown

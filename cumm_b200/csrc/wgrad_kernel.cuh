@@ -271,6 +271,7 @@ __global__ void __launch_bounds__(WgradCfg<BLOCK_N>::THREADS, 1) wgrad_kernel(co
             if (ok)
               ok = mbar_wait(full_s(stage), (step / Cfg::SA) & 1, abort_flag);
             if (ok) {
+              fence_proxy_async_smem();
               tc_fence_after();
               const uint32_t a_base = sbase + Cfg::OFF_STAGES + stage * Cfg::STAGE_BYTES;
               const uint32_t b_base = a_base + Cfg::A_BYTES;
@@ -396,13 +397,12 @@ __global__ void __launch_bounds__(WgradCfg<BLOCK_N>::THREADS, 1) wgrad_kernel(co
               cp_async_16(dst, srcp, valid ? 16u : 0u);
             }
           }
-          cp_async_commit();
-          cp_async_wait<0>();
-          fence_proxy_async_smem();
-          mbar_arrive(full_s(g));
+          // async arrive when this thread's copies land; the consumer fences (see rowconv kernel)
+          cp_async_mbar_arrive_noinc(full_s(g));
           return true;
         },
         [&](int, int, int) -> bool { return true; });
+    cp_async_wait_all();
   }
 
   tc_fence_before();
@@ -431,35 +431,86 @@ struct WgradReduceParams {
   int out_f32;
 };
 
-__global__ void wgrad_reduce_kernel(const WgradReduceParams p) {
+// One block per (f, group of 32 float4 columns of the [m_total x n_total] slice); the 8 warps
+// of a block each add every 8th unit, then the 8 warp sums are combined in a fixed order.
+__global__ void __launch_bounds__(256) wgrad_reduce_kernel(const WgradReduceParams p) {
+  __shared__ float4 s_part[8][32];
+  __shared__ int s_flags[256];
   const int f = blockIdx.y;
   if (!((p.mask_filter >> f) & 1u))
     return;
   const int S = p.sched[f], base = p.sched[32 + f];
-  const long long total = (long long)p.m_total * p.n_total;
+  const int n4 = p.n_total >> 2;                     // float4 per row (n_total is a multiple of 8)
+  const long long total4 = (long long)p.m_total * n4;
   const int n_tiles_n = (p.n_total + p.block_n - 1) / p.block_n;
-  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
-       e += (long long)gridDim.x * blockDim.x) {
-    const int m = (int)(e / p.n_total), n = (int)(e % p.n_total);
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const long long e4 = (long long)blockIdx.x * 32 + lane;
+  const bool in_range = e4 < total4;
+  int m = 0, n = 0, by = 0;
+  long long in_tile = 0;
+  if (in_range) {
+    m = (int)(e4 / n4);
+    n = (int)(e4 % n4) * 4;
     const int mt = m >> 7, ntile = n / p.block_n;
-    const int by = mt * n_tiles_n + ntile;
-    const long long in_tile = (long long)(m & 127) * p.block_n + (n - ntile * p.block_n);
-    float acc = 0.f;
-    for (int s = 0; s < S; ++s) {
-      const long long u = base + s;
-      if (p.unit_flags[u * p.gy + by])
-        acc += p.partials[(u * p.gy + by) * 128 * p.block_n + in_tile];
+    by = mt * n_tiles_n + ntile;
+    in_tile = (long long)(m & 127) * p.block_n + (n - ntile * p.block_n);
+  }
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s0 = 0; s0 < S; s0 += 256) {
+    __syncthreads();
+    if (s0 + (int)threadIdx.x < S)
+      s_flags[threadIdx.x] = 0;
+    __syncthreads();
+    const int cnt = min(256, S - s0);
+    // flags depend on the (m-tile, n-tile) of the element; with one tile pair per block row this is
+    // uniform across the block, so the flags of `by` of lane 0's element are shared
+    const int by0 = __shfl_sync(0xffffffffu, by, 0);
+    if ((int)threadIdx.x < cnt)
+      s_flags[threadIdx.x] = p.unit_flags[(long long)(base + s0 + threadIdx.x) * p.gy + by0];
+    __syncthreads();
+    if (in_range) {
+#pragma unroll 4
+      for (int s = wid; s < cnt; s += 8) {
+        const long long u = base + s0 + s;
+        const bool on = (by == by0) ? (s_flags[s] != 0) : (p.unit_flags[u * p.gy + by] != 0);
+        if (on) {
+          const float4 v = *reinterpret_cast<const float4 *>(p.partials + (u * p.gy + by) * 128 * p.block_n + in_tile);
+          acc.x += v.x;
+          acc.y += v.y;
+          acc.z += v.z;
+          acc.w += v.w;
+        }
+      }
     }
-    const long long off = (long long)m * p.ldo + (long long)f * p.f_stride + n;
-    if (p.out_f32) {
-      float *o = reinterpret_cast<float *>(p.out);
-      float prev = (p.beta != 0.f) ? reinterpret_cast<const float *>(p.src)[off] : 0.f;
-      o[off] = (p.beta != 0.f) ? __fmaf_rn(p.alpha, acc, __fmul_rn(p.beta, prev)) : __fmul_rn(p.alpha, acc);
-    } else {
-      __half *o = reinterpret_cast<__half *>(p.out);
-      float prev = (p.beta != 0.f) ? __half2float(reinterpret_cast<const __half *>(p.src)[off]) : 0.f;
-      float t = (p.beta != 0.f) ? __fmaf_rn(p.alpha, acc, __fmul_rn(p.beta, prev)) : __fmul_rn(p.alpha, acc);
-      o[off] = __float2half_rn(t);
+  }
+  s_part[wid][lane] = acc;
+  __syncthreads();
+  if (wid != 0 || !in_range)
+    return;
+  float r[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int w = 0; w < 8; ++w) {
+    const float4 v = s_part[w][lane];
+    r[0] += v.x;
+    r[1] += v.y;
+    r[2] += v.z;
+    r[3] += v.w;
+  }
+  const long long off = (long long)m * p.ldo + (long long)f * p.f_stride + n;
+  if (p.out_f32) {
+    float *o = reinterpret_cast<float *>(p.out);
+    const float *sp = reinterpret_cast<const float *>(p.src);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      o[off + j] = (p.beta != 0.f) ? __fmaf_rn(p.alpha, r[j], __fmul_rn(p.beta, sp[off + j])) : __fmul_rn(p.alpha, r[j]);
+  } else {
+    __half *o = reinterpret_cast<__half *>(p.out);
+    const __half *sp = reinterpret_cast<const __half *>(p.src);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float t = (p.beta != 0.f) ? __fmaf_rn(p.alpha, r[j], __fmul_rn(p.beta, __half2float(sp[off + j])))
+                                      : __fmul_rn(p.alpha, r[j]);
+      o[off + j] = __float2half_rn(t);
     }
   }
 }
