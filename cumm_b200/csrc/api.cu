@@ -13,6 +13,10 @@
 #include <mutex>
 #include <string>
 
+#ifndef CB2_DEFAULT_GATHER
+#define CB2_DEFAULT_GATHER 0
+#endif
+
 namespace {
 
 using namespace cb2;
@@ -108,6 +112,35 @@ int make_weight_map(CUtensorMap *map, const void *ptr, int es, uint64_t inner, u
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   CB2_CHECK_RT(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code %d", (int)r);
   return CB2_OK;
+}
+
+// 2-D tensor map over gathered operand rows [rows, width] (row stride ld elements); the box is
+// one row of 128 bytes, so a gather is one request per (row, column block).
+int make_rows_map(CUtensorMap *map, const void *ptr, int es, uint64_t width, uint64_t rows, uint64_t ld) {
+  cuuint64_t dims[2] = {width, rows > 0 ? rows : 1};
+  cuuint64_t strides[1] = {ld * es};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / es), 1};
+  cuuint32_t estr[2] = {1, 1};
+  CB2_CHECK_ARG(aligned16(ptr), "operand pointer must be 16-byte aligned");
+  CB2_CHECK_ARG(strides[0] % 16 == 0, "operand row stride must be a multiple of 16 bytes");
+  CUresult r = g_encode(map, es == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                        const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CB2_CHECK_RT(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (rows) failed with code %d", (int)r);
+  return CB2_OK;
+}
+
+// Which row-gather implementation the kernels use: 0 cp.async, 1 TMA row loads, 2 TMA gather4.
+int gather_mode() {
+  static int mode = -1;
+  if (mode < 0) {
+    int m = CB2_DEFAULT_GATHER;
+    if (const char *v = getenv("CUMM_B200_GATHER"))
+      m = atoi(v);
+    mode = (m >= 0 && m <= 2) ? m : CB2_DEFAULT_GATHER;
+  }
+  return mode;
 }
 
 template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN>
@@ -232,9 +265,11 @@ void wgrad_layout(int num_sms, int m_total, int n_total, WgradLayout *L) {
   L->total = L->off_partials + (size_t)L->slots * L->gy * 128 * L->block_n * 4;
 }
 
-template <int BLOCK_N> int launch_wgrad_inst(const WgradParams &p, int gx, int gy, cudaStream_t stream) {
-  using Cfg = WgradCfg<BLOCK_N>;
-  auto kern = wgrad_kernel<BLOCK_N>;
+template <int BLOCK_N, int GATHER>
+int launch_wgrad_inst(const CUtensorMap &ma, const CUtensorMap &mb, const WgradParams &p, int gx, int gy,
+                      cudaStream_t stream) {
+  using Cfg = WgradCfg<BLOCK_N, GATHER>;
+  auto kern = wgrad_kernel<BLOCK_N, GATHER>;
   static std::atomic<uint64_t> configured{0};
   int dev = 0;
   CB2_CUDA(cudaGetDevice(&dev));
@@ -242,7 +277,7 @@ template <int BLOCK_N> int launch_wgrad_inst(const WgradParams &p, int gx, int g
     CB2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     configured.fetch_or(1ull << dev);
   }
-  kern<<<dim3(gx, gy), Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(p);
+  kern<<<dim3(gx, gy), Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, p);
   CB2_CUDA(cudaGetLastError());
   g_launches.fetch_add(1);
   return CB2_OK;
@@ -266,8 +301,22 @@ int run_wgrad(DeviceState *dev, WgradParams &p, void *workspace, size_t workspac
   const int ntiles = (p.n_rows + 127) / 128;
   int rc;
   if (ntiles > 0) {
-    rc = (L.block_n == 64) ? launch_wgrad_inst<64>(p, L.G, L.gy, stream)
-                           : launch_wgrad_inst<128>(p, L.G, L.gy, stream);
+    CUtensorMap ma, mb;
+    rc = make_rows_map(&ma, p.dout, 2, p.m_total, p.a_rows, p.ld_dout);
+    if (rc)
+      return rc;
+    rc = make_rows_map(&mb, p.x, 2, p.n_total, p.b_rows, p.ld_x);
+    if (rc)
+      return rc;
+    const int gm = gather_mode();
+    if (L.block_n == 64)
+      rc = gm == 0 ? launch_wgrad_inst<64, 0>(ma, mb, p, L.G, L.gy, stream)
+                   : gm == 1 ? launch_wgrad_inst<64, 1>(ma, mb, p, L.G, L.gy, stream)
+                             : launch_wgrad_inst<64, 2>(ma, mb, p, L.G, L.gy, stream);
+    else
+      rc = gm == 0 ? launch_wgrad_inst<128, 0>(ma, mb, p, L.G, L.gy, stream)
+                   : gm == 1 ? launch_wgrad_inst<128, 1>(ma, mb, p, L.G, L.gy, stream)
+                             : launch_wgrad_inst<128, 2>(ma, mb, p, L.G, L.gy, stream);
     if (rc)
       return rc;
   } else {
@@ -290,8 +339,8 @@ int run_wgrad(DeviceState *dev, WgradParams &p, void *workspace, size_t workspac
   r.alpha = alpha;
   r.beta = beta;
   r.out_f32 = out_f32;
-  const long long total4 = (long long)p.m_total * (p.n_total / 4);
-  const int bx = (int)((total4 + 31) / 32);
+  const long long e4 = (long long)L.gy * (L.block_n / 4) * 128;
+  const int bx = (int)((e4 + 31) / 32);
   wgrad_reduce_kernel<<<dim3(bx, p.kv), 256, 0, stream>>>(r);
   CB2_CUDA(cudaGetLastError());
   g_launches.fetch_add(1);
@@ -310,6 +359,19 @@ int kind_of(int da, int db, int dc, int is_int8, bool allow_f32_out) {
 } // namespace
 
 extern "C" {
+
+#ifdef CB2_TRACE
+// Debug builds only: copy the device trace buffer to the host and reset it.
+int cb2_debug_read_trace(void *host_dst, size_t bytes) {
+  if (bytes != sizeof(cb2::TraceBuf))
+    return set_err(CB2_ERR_INVALID_ARG, "trace buffer is %zu bytes", sizeof(cb2::TraceBuf));
+  CB2_CUDA(cudaDeviceSynchronize());
+  CB2_CUDA(cudaMemcpyFromSymbol(host_dst, cb2::g_trace, bytes));
+  static cb2::TraceBuf zero;
+  CB2_CUDA(cudaMemcpyToSymbol(cb2::g_trace, &zero, bytes));
+  return CB2_OK;
+}
+#endif
 
 const char *cb2_last_error(void) { return g_err.c_str(); }
 

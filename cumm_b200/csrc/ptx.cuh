@@ -14,6 +14,32 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) {
 
 __device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31; }
 
+// ---------------------------------------------------------------- optional event trace
+// Built only with -DCB2_TRACE (a debugging aid): CTA 0 records (global timer, code, step)
+// triples per role into a device buffer so a pipeline timeline can be read back.
+#ifdef CB2_TRACE
+struct TraceBuf {
+  unsigned long long ev[8][512][2];  // [role][event][time, (code << 32) | step]
+  int count[8];
+};
+__device__ TraceBuf g_trace;
+__device__ __forceinline__ void trace_event(int role, int code, int step) {
+  if (blockIdx.x != 0 || blockIdx.y != 0)
+    return;
+  int n = g_trace.count[role];
+  if (n >= 512)
+    return;
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  g_trace.ev[role][n][0] = t;
+  g_trace.ev[role][n][1] = (static_cast<unsigned long long>(code) << 32) | static_cast<unsigned>(step);
+  g_trace.count[role] = n + 1;
+}
+#define CB2_TRACE_EVENT(role, code, step) ::cb2::trace_event(role, code, step)
+#else
+#define CB2_TRACE_EVENT(role, code, step) ((void)0)
+#endif
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -54,11 +80,20 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 
 // Bounded wait.  `abort_flag` (shared memory) is polled so that once any thread of the
 // CTA has given up, everybody else leaves quickly too.  Returns false on give-up.
+// A waiter that does not get through at once sleeps between polls (20 ns growing to
+// 160 ns): a CTA has a dozen waiters most of the time, and pollers that spin take issue
+// slots away from the warps that do the work.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+  if (mbar_test(bar, parity))
+    return true;
   unsigned long long t0 = 0;
+  uint32_t backoff = 20;
   for (uint32_t i = 0;; ++i) {
+    __nanosleep(backoff);
     if (mbar_test(bar, parity))
       return true;
+    if (backoff < 160)
+      backoff += backoff;
     if ((i & 63u) == 63u) {
       if (*abort_flag)
         return false;
@@ -67,11 +102,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         t0 = now;
       else if (now - t0 > kWaitLimitNs)
         break;
-      __nanosleep(32);
     }
   }
   *abort_flag = 1;
   return false;
+}
+
+// Warp-collective wait: lane 0 polls, the other lanes sleep at the shuffle.  Keeps the
+// number of spinning threads per SM small (one per warp), which matters because pollers
+// compete for issue slots with the warps that do the work.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+  int ok = 1;
+  if (lane_id() == 0)
+    ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 // ---------------------------------------------------------------- named barriers
@@ -113,6 +157,21 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void *tmap, uint
                : "memory");
 }
 
+// One row of a 2-D tensor (box {128 bytes, 1 row}); rows outside the tensor read as zeros.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, uint32_t bar, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+               "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+               "l"(tmap), "r"(bar), "r"(c0), "r"(c1)
+               : "memory");
+}
+// Four rows r0..r3 of a 2-D tensor, gathered into four consecutive 128-byte rows of `dst`.
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const void *tmap, uint32_t bar, int c0, int r0, int r1,
+                                            int r2, int r3) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes "
+               "[%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(dst),
+               "l"(tmap), "r"(bar), "r"(c0), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+               : "memory");
+}
 // ---------------------------------------------------------------- tcgen05 / TMEM
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
@@ -172,6 +231,36 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
+}
+// 16 consecutive 32-bit columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+                 "=r"(r[15])
+               : "r"(taddr)
+               : "memory");
+}
+// Wait for outstanding tcgen05.ld; the registers are named as operands so that no use of
+// them can be scheduled ahead of the wait.
+__device__ __forceinline__ void tmem_ld_wait_regs16(uint32_t (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+                 "+r"(r[15])
+               :
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait_regs(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+                 "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
+                 "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
+                 "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 

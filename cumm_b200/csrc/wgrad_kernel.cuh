@@ -22,6 +22,10 @@
 namespace cb2 {
 
 enum : int { kWgradMaskConv = 0, kWgradPairList = 1 };
+// Row-gather implementations: 16-byte cp.async per chunk; one TMA tile load per (row, 128-byte
+// column block) where a row coordinate of -1 is out of bounds and reads as zeros; TMA
+// tile::gather4, four rows per request.
+enum : int { kGatherCpAsync = 0, kGatherTmaRow = 1, kGatherTma4 = 2 };
 
 struct WgradParams {
   const void *dout;        // A rows [*, m_total]  (fp16)
@@ -46,17 +50,21 @@ struct WgradParams {
   int mode;
 };
 
-template <int BLOCK_N> struct WgradCfg {
+template <int BLOCK_N, int GATHER> struct WgradCfg {
   static constexpr int SA = 3;
   static constexpr int A_BYTES = 128 * 256;                 // 128 rows x (2 x 128 B): M = 128 channels
   static constexpr int B_BYTES = 128 * 2 * BLOCK_N;         // 128 rows x BLOCK_N fp16
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TMEM_COLS = 2 * BLOCK_N;
   static constexpr int THREADS = 128 + 64 + SA * 128;       // epilogue, mma + spare, 3 gather groups
+  static constexpr int FULL_COUNT = GATHER == kGatherCpAsync ? 128 : 1;
   static constexpr int OFF_STAGES = 0;
   static constexpr int OFF_ROWIDX = SA * STAGE_BYTES;       // SA x 2 buffers x 2 operands x 128 ints
-  static constexpr int OFF_SCHED = OFF_ROWIDX + SA * 2 * 2 * 128 * 4;  // 96 ints
-  static constexpr int OFF_BARS = OFF_SCHED + 96 * 4;
+  static constexpr int OFF_SCHED = OFF_ROWIDX + SA * 2 * 2 * 128 * 4;  // 96 ints + unit table
+  static constexpr int MAX_UNITS = 4;                        // units of one CTA with a bitmap
+  static constexpr int BITMAP_WORDS = 2048;                  // 32 tiles per word
+  static constexpr int OFF_BITMAP = OFF_SCHED + 128 * 4;
+  static constexpr int OFF_BARS = OFF_BITMAP + BITMAP_WORDS * 4;
   static constexpr int OFF_MISC = OFF_BARS + 16 * 8;
   static constexpr int SMEM_BYTES = OFF_MISC + 64 + 1024;
 };
@@ -79,74 +87,188 @@ __device__ __forceinline__ uint32_t wgrad_tile_mask(const WgradParams &p, int ti
 
 // Unit schedule, identical in every CTA: S_f units for offset f, proportional to the
 // number of row tiles that carry f; unit (f, s) covers tiles [T*s/S_f, T*(s+1)/S_f).
-__device__ __forceinline__ void wgrad_build_schedule(const WgradParams &p, int ntiles, int *s_sched) {
-  // s_sched[0..31] counts -> S_f, [32..63] base, [64] total
-  for (int i = threadIdx.x; i < 96; i += blockDim.x)
+// s_sched: [0,32) S_f, [32,64) first unit of f, [64] total units,
+//          [96 + 4k .. 96 + 4k + 3] for this CTA's k-th unit: f, first bitmap word index
+//          (absolute tile / 32), offset of its words in the bitmap, number of words (0 = the
+//          unit has no bitmap and is scanned from global memory).
+// bitmap: for each of the CTA's first MAX_UNITS units, one bit per tile of its range that
+// carries f, so that every role can enumerate the unit's tiles without touching memory.
+template <int MAX_UNITS, int BITMAP_WORDS>
+__device__ __forceinline__ void wgrad_build_schedule(const WgradParams &p, int ntiles, int *s_sched,
+                                                     uint32_t *bitmap) {
+  constexpr int MAXK = 16;  // tile masks kept in registers per thread
+  for (int i = threadIdx.x; i < 128; i += blockDim.x)
     s_sched[i] = 0;
   __syncthreads();
-  for (int t = threadIdx.x; t < ntiles; t += blockDim.x) {
-    uint32_t m = wgrad_tile_mask(p, t);
-    while (m) {
-      int f = __ffs(m) - 1;
-      m &= m - 1;
-      atomicAdd(&s_sched[f], 1);
+  uint32_t mk[MAXK];
+#pragma unroll
+  for (int k = 0; k < MAXK; ++k) {
+    const int t = k * blockDim.x + threadIdx.x;
+    mk[k] = (t < ntiles) ? wgrad_tile_mask(p, t) : 0u;
+  }
+  // per-offset tile counts: one ballot per (offset, 32 tiles), one shared-memory add per warp
+  {
+    const int ln = threadIdx.x & 31;
+    int mine = 0;  // lane f accumulates the count of offset f
+#pragma unroll
+    for (int k = 0; k < MAXK; ++k) {
+      if (k * (int)blockDim.x < ntiles) {  // uniform
+        const uint32_t any = __reduce_or_sync(0xffffffffu, mk[k]);
+        for (uint32_t rest = any; rest;) {
+          const int f = __ffs(rest) - 1;
+          rest &= rest - 1;
+          const int c = __popc(__ballot_sync(0xffffffffu, (mk[k] >> f) & 1u));
+          if (ln == f)
+            mine += c;
+        }
+      }
     }
+    for (int t0 = MAXK * blockDim.x; t0 < ntiles; t0 += blockDim.x) {  // uniform trip count
+      const int t = t0 + threadIdx.x;
+      const uint32_t m = (t < ntiles) ? wgrad_tile_mask(p, t) : 0u;
+      const uint32_t any = __reduce_or_sync(0xffffffffu, m);
+      for (uint32_t rest = any; rest;) {
+        const int f = __ffs(rest) - 1;
+        rest &= rest - 1;
+        const int c = __popc(__ballot_sync(0xffffffffu, (m >> f) & 1u));
+        if (ln == f)
+          mine += c;
+      }
+    }
+    if (mine)
+      atomicAdd(&s_sched[ln], mine);
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    long long total = 0;
-    for (int f = 0; f < p.kv && f < 32; ++f)
-      total += s_sched[f];
-    const int G = gridDim.x;
-    int base = 0;
-    for (int f = 0; f < 32; ++f) {
-      int cnt = (f < p.kv) ? s_sched[f] : 0;
-      int S = 0;
-      if (cnt > 0) {
-        S = (int)(((long long)cnt * G + total / 2) / total);
-        if (S < 1)
-          S = 1;
-        if (S > cnt)
-          S = cnt;
-        if (S > G)
-          S = G;
-      }
-      s_sched[f] = S;
-      s_sched[32 + f] = base;
-      base += S;
+  if (threadIdx.x < 32) {
+    const int f = threadIdx.x;
+    const int cnt = (f < p.kv) ? s_sched[f] : 0;
+    int total = cnt, nf = cnt > 0 ? 1 : 0;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+      total += __shfl_xor_sync(0xffffffffu, total, d);
+      nf += __shfl_xor_sync(0xffffffffu, nf, d);
     }
-    s_sched[64] = base;
+    // S_f ~ cnt_f / total of the CTAs left after every present offset got one; the sum stays
+    // within the grid so that no CTA gets a second unit (unless there are more offsets than CTAs)
+    const int G = gridDim.x;
+    const int spare = max(G - nf, 0);
+    int S = 0;
+    if (cnt > 0) {
+      S = 1 + (int)(((float)cnt * (float)spare) / (float)total);
+      S = max(1, min(S, min(cnt, G)));
+    }
+    int incl = S;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, d);
+      if (f >= d)
+        incl += v;
+    }
+    __syncwarp();
+    s_sched[f] = S;
+    s_sched[32 + f] = incl - S;
+    if (f == 31)
+      s_sched[64] = incl;
+  }
+  __syncthreads();
+  // unit table and bitmaps of this CTA's first MAX_UNITS units
+  const int total_units = s_sched[64];
+  int word_off = 0;
+  for (int k = 0; k < MAX_UNITS; ++k) {
+    const int u = blockIdx.x + k * gridDim.x;
+    if (u >= total_units)
+      break;
+    int f = 0;
+    while (f < 31 && !(u >= s_sched[32 + f] && u < s_sched[32 + f] + s_sched[f]))
+      ++f;
+    const int S = s_sched[f], si = u - s_sched[32 + f];
+    const int t0 = (int)(((long long)ntiles * si) / S);
+    const int t1 = (int)(((long long)ntiles * (si + 1)) / S);
+    const int w0 = t0 >> 5, w1 = (t1 + 31) >> 5;
+    const int nwords = (t1 > t0 && word_off + (w1 - w0) <= BITMAP_WORDS) ? (w1 - w0) : 0;
+    if (threadIdx.x == 0) {
+      s_sched[96 + 4 * k] = f;
+      s_sched[96 + 4 * k + 1] = w0;
+      s_sched[96 + 4 * k + 2] = word_off;
+      s_sched[96 + 4 * k + 3] = nwords;
+    }
+    if (nwords > 0) {
+      // warp-per-word: lane l tests tile 32*w + l
+      const int nwarps = blockDim.x >> 5, wid = threadIdx.x >> 5, ln = threadIdx.x & 31;
+#pragma unroll
+      for (int kk = 0; kk < MAXK; ++kk) {
+        const int w = kk * nwarps + wid;  // word that mk[kk] belongs to (tile = kk*blockDim + tid)
+        const int t = w * 32 + ln;
+        const bool on = t >= t0 && t < t1 && ((mk[kk] >> f) & 1u);
+        const uint32_t bal = __ballot_sync(0xffffffffu, on);
+        if (ln == 0 && w >= w0 && w < w1)
+          bitmap[word_off + w - w0] = bal;
+      }
+      for (int w = MAXK * nwarps + wid; w < w1; w += nwarps) {
+        const int t = w * 32 + ln;
+        const uint32_t m = (t < ntiles) ? wgrad_tile_mask(p, t) : 0u;
+        const bool on = t >= t0 && t < t1 && ((m >> f) & 1u);
+        const uint32_t bal = __ballot_sync(0xffffffffu, on);
+        if (ln == 0 && w >= w0)
+          bitmap[word_off + w - w0] = bal;
+      }
+      word_off += nwords;
+    }
   }
   __syncthreads();
 }
 
 // Walk the active tiles of this CTA's units.  on_unit(u, f) at unit start, on_tile(tile, f,
 // first_of_unit) for each tile carrying f, on_unit_end(u, f, n_active).
-template <class UnitFn, class TileFn, class EndFn>
-__device__ __forceinline__ void wgrad_walk(const WgradParams &p, int ntiles, const int *s_sched, UnitFn on_unit,
-                                           TileFn on_tile, EndFn on_unit_end) {
+template <int MAX_UNITS, class UnitFn, class TileFn, class EndFn>
+__device__ __forceinline__ void wgrad_walk(const WgradParams &p, int ntiles, const int *s_sched,
+                                           const uint32_t *bitmap, UnitFn on_unit, TileFn on_tile,
+                                           EndFn on_unit_end) {
   const int total = s_sched[64];
-  for (int u = blockIdx.x; u < total; u += gridDim.x) {
-    int f = 0;
-    while (f < 31 && !(u >= s_sched[32 + f] && u < s_sched[32 + f] + s_sched[f]))
-      ++f;
-    const int S = s_sched[f];
-    const int s = u - s_sched[32 + f];
-    const int t0 = (int)(((long long)ntiles * s) / S);
-    const int t1 = (int)(((long long)ntiles * (s + 1)) / S);
+  int k = 0;
+  for (int u = blockIdx.x; u < total; u += gridDim.x, ++k) {
+    int f, w0 = 0, woff = 0, nwords = 0;
+    if (k < MAX_UNITS) {
+      f = s_sched[96 + 4 * k];
+      w0 = s_sched[96 + 4 * k + 1];
+      woff = s_sched[96 + 4 * k + 2];
+      nwords = s_sched[96 + 4 * k + 3];
+    } else {
+      f = 0;
+      while (f < 31 && !(u >= s_sched[32 + f] && u < s_sched[32 + f] + s_sched[f]))
+        ++f;
+    }
     if (!on_unit(u, f))
       return;
     int active = 0;
-    for (int tb = t0; tb < t1; tb += 32) {
-      const int t = tb + (int)lane_id();
-      uint32_t m = (t < t1) ? wgrad_tile_mask(p, t) : 0u;
-      uint32_t ball = __ballot_sync(0xffffffffu, (m >> f) & 1u);
-      while (ball) {
-        const int j = __ffs(ball) - 1;
-        ball &= ball - 1;
-        if (!on_tile(tb + j, f, active == 0))
-          return;
-        ++active;
+    if (nwords > 0) {
+      for (int w = 0; w < nwords; ++w) {
+        uint32_t bits = bitmap[woff + w];
+        while (bits) {
+          const int j = __ffs(bits) - 1;
+          bits &= bits - 1;
+          if (!on_tile((w0 + w) * 32 + j, f, active == 0))
+            return;
+          ++active;
+        }
+      }
+    } else {
+      // no bitmap (more units or tiles than the bitmap holds): scan the masks in global memory
+      const int S = s_sched[f];
+      const int si = u - s_sched[32 + f];
+      const int t0 = (int)(((long long)ntiles * si) / S);
+      const int t1 = (int)(((long long)ntiles * (si + 1)) / S);
+      for (int tb = t0; tb < t1; tb += 32) {
+        const int t = tb + (int)lane_id();
+        uint32_t m = (t < t1) ? wgrad_tile_mask(p, t) : 0u;
+        uint32_t ball = __ballot_sync(0xffffffffu, (m >> f) & 1u);
+        while (ball) {
+          const int j = __ffs(ball) - 1;
+          ball &= ball - 1;
+          if (!on_tile(tb + j, f, active == 0))
+            return;
+          ++active;
+        }
       }
     }
     if (!on_unit_end(u, f, active))
@@ -154,9 +276,11 @@ __device__ __forceinline__ void wgrad_walk(const WgradParams &p, int ntiles, con
   }
 }
 
-template <int BLOCK_N>
-__global__ void __launch_bounds__(WgradCfg<BLOCK_N>::THREADS, 1) wgrad_kernel(const WgradParams p) {
-  using Cfg = WgradCfg<BLOCK_N>;
+template <int BLOCK_N, int GATHER>
+__global__ void __launch_bounds__(WgradCfg<BLOCK_N, GATHER>::THREADS, 1)
+wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constant__ CUtensorMap tmap_x,
+             const WgradParams p) {
+  using Cfg = WgradCfg<BLOCK_N, GATHER>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -164,6 +288,7 @@ __global__ void __launch_bounds__(WgradCfg<BLOCK_N>::THREADS, 1) wgrad_kernel(co
   const uint32_t sbase = raw_addr + pad;
   int *rowidx = reinterpret_cast<int *>(smem + Cfg::OFF_ROWIDX);
   int *s_sched = reinterpret_cast<int *>(smem + Cfg::OFF_SCHED);
+  uint32_t *bitmap = reinterpret_cast<uint32_t *>(smem + Cfg::OFF_BITMAP);
   volatile int *misc = reinterpret_cast<volatile int *>(smem + Cfg::OFF_MISC);
   volatile int *abort_flag = misc + 1;
   const uint32_t bars = sbase + Cfg::OFF_BARS;
@@ -182,7 +307,7 @@ __global__ void __launch_bounds__(WgradCfg<BLOCK_N>::THREADS, 1) wgrad_kernel(co
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::SA; ++s) {
-      mbar_init(full_s(s), 128);
+      mbar_init(full_s(s), Cfg::FULL_COUNT);
       mbar_init(empty_s(s), 1);
     }
     for (int s = 0; s < 2; ++s) {
@@ -198,7 +323,11 @@ __global__ void __launch_bounds__(WgradCfg<BLOCK_N>::THREADS, 1) wgrad_kernel(co
     tmem_alloc(sbase + Cfg::OFF_MISC, Cfg::TMEM_COLS);
     tmem_relinquish();
   }
-  wgrad_build_schedule(p, ntiles, s_sched);  // contains __syncthreads
+  if (threadIdx.x == 0)
+    CB2_TRACE_EVENT(5, 10, 0);
+  wgrad_build_schedule<Cfg::MAX_UNITS, Cfg::BITMAP_WORDS>(p, ntiles, s_sched, bitmap);  // contains __syncthreads
+  if (threadIdx.x == 0)
+    CB2_TRACE_EVENT(5, 11, 0);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -217,8 +346,8 @@ __global__ void __launch_bounds__(WgradCfg<BLOCK_N>::THREADS, 1) wgrad_kernel(co
     // ======================= epilogue: one fp32 partial per unit
     const int et = threadIdx.x;
     int acc_use = 0;
-    wgrad_walk(
-        p, ntiles, s_sched, [&](int, int) -> bool { return true; },
+    wgrad_walk<Cfg::MAX_UNITS>(
+        p, ntiles, s_sched, bitmap, [&](int, int) -> bool { return true; },
         [&](int, int, bool) -> bool { return true; },
         [&](int u, int f, int active) -> bool {
           if (et == 0)
@@ -227,7 +356,9 @@ __global__ void __launch_bounds__(WgradCfg<BLOCK_N>::THREADS, 1) wgrad_kernel(co
             return true;
           const int buf = acc_use & 1;
           if (et == 0) {
+            CB2_TRACE_EVENT(4, 7, u);
             bool ok = mbar_wait(acc_full(buf), (acc_use >> 1) & 1, abort_flag);
+            CB2_TRACE_EVENT(4, 8, u);  // accumulator complete
             misc[2] = ok ? 1 : 0;
             if (!ok)
               fail(kStatusWaitTimeout);
@@ -238,7 +369,9 @@ __global__ void __launch_bounds__(WgradCfg<BLOCK_N>::THREADS, 1) wgrad_kernel(co
           tc_fence_after();
           const uint32_t trow = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
                                 static_cast<uint32_t>(buf * BLOCK_N);
-          float *dst = p.partials + (((long long)u * gy + blockIdx.y) * 128 + et) * BLOCK_N;
+          // partial layout: float4 (col/4, row) at index (col/4) * 128 + row, so that the 32
+          // rows of a warp store 512 contiguous bytes
+          uint4 *dst = reinterpret_cast<uint4 *>(p.partials + ((long long)u * gy + blockIdx.y) * 128 * BLOCK_N) + et;
 #pragma unroll 1
           for (int round = 0; round < BLOCK_N / 32; ++round) {
             uint32_t v[32];
@@ -246,12 +379,13 @@ __global__ void __launch_bounds__(WgradCfg<BLOCK_N>::THREADS, 1) wgrad_kernel(co
             tmem_ld_wait();
 #pragma unroll
             for (int q = 0; q < 8; ++q)
-              *reinterpret_cast<uint4 *>(dst + round * 32 + q * 4) =
-                  make_uint4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+              dst[(round * 8 + q) * 128] = make_uint4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
           }
           tc_fence_before();
           mbar_arrive(acc_empty(buf));
           ++acc_use;
+          if (et == 0)
+            CB2_TRACE_EVENT(4, 9, u);  // partial written
           return true;
         });
   } else if (warp == 4) {
@@ -259,8 +393,8 @@ __global__ void __launch_bounds__(WgradCfg<BLOCK_N>::THREADS, 1) wgrad_kernel(co
     constexpr uint32_t idesc = make_idesc(0, true, true, 128, BLOCK_N);
     int step = 0, acc_use = 0;
     bool ok_all = true;
-    wgrad_walk(
-        p, ntiles, s_sched, [&](int, int) -> bool { return true; },
+    wgrad_walk<Cfg::MAX_UNITS>(
+        p, ntiles, s_sched, bitmap, [&](int, int) -> bool { return true; },
         [&](int tile, int f, bool first) -> bool {
           const int buf = acc_use & 1;
           int ok = 1;
@@ -268,10 +402,13 @@ __global__ void __launch_bounds__(WgradCfg<BLOCK_N>::THREADS, 1) wgrad_kernel(co
             if (first)
               ok = mbar_wait(acc_empty(buf), ((acc_use >> 1) & 1) ^ 1, abort_flag);
             const int stage = step % Cfg::SA;
+            CB2_TRACE_EVENT(3, 4, step);  // waiting for data
             if (ok)
               ok = mbar_wait(full_s(stage), (step / Cfg::SA) & 1, abort_flag);
+            CB2_TRACE_EVENT(3, 5, step);  // data landed
             if (ok) {
-              fence_proxy_async_smem();
+              if constexpr (GATHER == kGatherCpAsync)
+                fence_proxy_async_smem();
               tc_fence_after();
               const uint32_t a_base = sbase + Cfg::OFF_STAGES + stage * Cfg::STAGE_BYTES;
               const uint32_t b_base = a_base + Cfg::A_BYTES;
@@ -286,6 +423,7 @@ __global__ void __launch_bounds__(WgradCfg<BLOCK_N>::THREADS, 1) wgrad_kernel(co
                 tc_mma<0>(d_tmem, adesc, bdesc, idesc, (first && ks == 0) ? 0u : 1u);
               }
               tc_commit(empty_s(stage));
+              CB2_TRACE_EVENT(3, 6, step);  // MMAs issued
             }
           }
           ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -325,8 +463,8 @@ __global__ void __launch_bounds__(WgradCfg<BLOCK_N>::THREADS, 1) wgrad_kernel(co
     const uint8_t *a_bytes = reinterpret_cast<const uint8_t *>(p.dout);
     const uint8_t *b_bytes = reinterpret_cast<const uint8_t *>(p.x);
     constexpr int CPR_B = BLOCK_N / 8;  // 16-byte chunks per B row (fp16)
-    wgrad_walk(
-        p, ntiles, s_sched, [&](int, int) -> bool { return true; },
+    wgrad_walk<Cfg::MAX_UNITS>(
+        p, ntiles, s_sched, bitmap, [&](int, int) -> bool { return true; },
         [&](int tile, int f, bool) -> bool {
           const bool mine = (step % Cfg::SA) == g;
           const int use = step / Cfg::SA;
@@ -338,8 +476,8 @@ __global__ void __launch_bounds__(WgradCfg<BLOCK_N>::THREADS, 1) wgrad_kernel(co
           if (r < p.n_rows) {
             if (p.mode == kWgradMaskConv) {
               const uint32_t word = __ldg(p.rmask + r / p.mask_width);
+              const int o = __ldg(p.argsort + r);  // independent of `word`: both loads are in flight together
               if ((word >> f) & 1u) {
-                const int o = __ldg(p.argsort + r);
                 ib = __ldg(p.indices + (long long)f * p.n_rows + o);
                 ia = (ib >= 0) ? o : -1;  // a zero B row makes the A row irrelevant
               }
@@ -352,57 +490,98 @@ __global__ void __launch_bounds__(WgradCfg<BLOCK_N>::THREADS, 1) wgrad_kernel(co
               ia = ib = -1;
             }
           }
-          if (gt == 0) {
-            bool ok = mbar_wait(empty_s(g), (use & 1) ^ 1, abort_flag);
-            *my_flag = ok ? 1 : 0;
-            if (!ok)
-              fail(kStatusWaitTimeout);
-          }
-          int *ridx_a = group_rowidx + (use & 1) * 256;
-          int *ridx_b = ridx_a + 128;
-          ridx_a[gt] = ia;
-          ridx_b[gt] = ib;
-          named_bar_sync(2 + g, 128);
-          if (*my_flag == 0)
-            return false;
           const uint32_t a_stage = sbase + Cfg::OFF_STAGES + g * Cfg::STAGE_BYTES;
           const uint32_t b_stage = a_stage + Cfg::A_BYTES;
-          {
-            // A rows: 256 B (128 channels of dout starting at m0), 16 chunks per row
-            const int c = gt & 15, row0 = gt >> 4;
-            const bool col_ok = (m0 + c * 8) < p.m_total;
-            const uint32_t dst_c = a_stage + (c >> 3) * (128 * 128);
+          if constexpr (GATHER == kGatherCpAsync) {
+            if (gt == 0) {
+              CB2_TRACE_EVENT(g, 1, step - 1 + (ib == 0x7fffffff));  // indices loaded
+              bool ok = mbar_wait(empty_s(g), (use & 1) ^ 1, abort_flag);
+              CB2_TRACE_EVENT(g, 2, step - 1);             // stage free
+              *my_flag = ok ? 1 : 0;
+              if (!ok)
+                fail(kStatusWaitTimeout);
+            }
+            int *ridx_a = group_rowidx + (use & 1) * 256;
+            int *ridx_b = ridx_a + 128;
+            ridx_a[gt] = ia;
+            ridx_b[gt] = ib;
+            named_bar_sync(2 + g, 128);
+            if (*my_flag == 0)
+              return false;
+            {
+              // A rows: 256 B (128 channels of dout starting at m0), 16 chunks per row
+              const int c = gt & 15, row0 = gt >> 4;
+              const bool col_ok = (m0 + c * 8) < p.m_total;
+              const uint32_t dst_c = a_stage + (c >> 3) * (128 * 128);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int row = row0 + i * 8;
-              const int ridx = ridx_a[row];
-              const uint32_t dst = dst_c + (row >> 3) * 1024 + (row & 7) * 128 + (((c & 7) ^ (row & 7)) << 4);
-              const bool valid = col_ok && ridx >= 0;
-              const uint8_t *srcp = valid ? a_bytes + ((long long)ridx * p.ld_dout + m0 + c * 8) * 2 : a_bytes;
-              cp_async_16(dst, srcp, valid ? 16u : 0u);
+              for (int i = 0; i < 16; ++i) {
+                const int row = row0 + i * 8;
+                const int ridx = ridx_a[row];
+                const uint32_t dst = dst_c + (row >> 3) * 1024 + (row & 7) * 128 + (((c & 7) ^ (row & 7)) << 4);
+                const bool valid = col_ok && ridx >= 0;
+                const uint8_t *srcp = valid ? a_bytes + ((long long)ridx * p.ld_dout + m0 + c * 8) * 2 : a_bytes;
+                cp_async_16(dst, srcp, valid ? 16u : 0u);
+              }
+            }
+            {
+              const int c = gt % CPR_B, row0 = gt / CPR_B;
+              constexpr int RSTEP = 128 / CPR_B;
+              const bool col_ok = (n0 + c * 8) < p.n_total;
+              const uint32_t dst_c = b_stage + (c >> 3) * (128 * 128);
+#pragma unroll
+              for (int i = 0; i < CPR_B; ++i) {
+                const int row = row0 + i * RSTEP;
+                const int ridx = ridx_b[row];
+                const uint32_t dst = dst_c + (row >> 3) * 1024 + (row & 7) * 128 + (((c & 7) ^ (row & 7)) << 4);
+                const bool valid = col_ok && ridx >= 0;
+                const uint8_t *srcp = valid ? b_bytes + ((long long)ridx * p.ld_x + n0 + c * 8) * 2 : b_bytes;
+                cp_async_16(dst, srcp, valid ? 16u : 0u);
+              }
+            }
+            // async arrive when this thread's copies land; the consumer fences (see rowconv kernel)
+            cp_async_mbar_arrive_noinc(full_s(g));
+          } else {
+            if (gt == 0)
+              CB2_TRACE_EVENT(g, 1, step - 1 + (ib == 0x7fffffff));  // indices loaded
+            if (!mbar_wait_warp(empty_s(g), (use & 1) ^ 1, abort_flag)) {
+              if (lane == 0)
+                fail(kStatusWaitTimeout);
+              return false;
+            }
+            if (gt == 0) {
+              CB2_TRACE_EVENT(g, 2, step - 1);  // stage free
+              mbar_arrive_expect_tx(full_s(g), Cfg::STAGE_BYTES);
+            }
+            // one 128-byte row slot per thread and column block; row -1 reads as zeros
+            if constexpr (GATHER == kGatherTmaRow) {
+#pragma unroll
+              for (int ka = 0; ka < 2; ++ka)
+                tma_load_2d(a_stage + ka * (128 * 128) + gt * 128, &tmap_dout, full_s(g), m0 + ka * 64, ia);
+#pragma unroll
+              for (int kb = 0; kb < BLOCK_N / 64; ++kb)
+                tma_load_2d(b_stage + kb * (128 * 128) + gt * 128, &tmap_x, full_s(g), n0 + kb * 64, ib);
+            } else {
+              const int a1 = __shfl_down_sync(0xffffffffu, ia, 1), a2 = __shfl_down_sync(0xffffffffu, ia, 2),
+                        a3 = __shfl_down_sync(0xffffffffu, ia, 3);
+              const int b1 = __shfl_down_sync(0xffffffffu, ib, 1), b2 = __shfl_down_sync(0xffffffffu, ib, 2),
+                        b3 = __shfl_down_sync(0xffffffffu, ib, 3);
+              if ((lane & 3) == 0) {
+#pragma unroll
+                for (int ka = 0; ka < 2; ++ka)
+                  tma_gather4(a_stage + ka * (128 * 128) + gt * 128, &tmap_dout, full_s(g), m0 + ka * 64, ia, a1, a2, a3);
+#pragma unroll
+                for (int kb = 0; kb < BLOCK_N / 64; ++kb)
+                  tma_gather4(b_stage + kb * (128 * 128) + gt * 128, &tmap_x, full_s(g), n0 + kb * 64, ib, b1, b2, b3);
+              }
             }
           }
-          {
-            const int c = gt % CPR_B, row0 = gt / CPR_B;
-            constexpr int RSTEP = 128 / CPR_B;
-            const bool col_ok = (n0 + c * 8) < p.n_total;
-            const uint32_t dst_c = b_stage + (c >> 3) * (128 * 128);
-#pragma unroll
-            for (int i = 0; i < CPR_B; ++i) {
-              const int row = row0 + i * RSTEP;
-              const int ridx = ridx_b[row];
-              const uint32_t dst = dst_c + (row >> 3) * 1024 + (row & 7) * 128 + (((c & 7) ^ (row & 7)) << 4);
-              const bool valid = col_ok && ridx >= 0;
-              const uint8_t *srcp = valid ? b_bytes + ((long long)ridx * p.ld_x + n0 + c * 8) * 2 : b_bytes;
-              cp_async_16(dst, srcp, valid ? 16u : 0u);
-            }
-          }
-          // async arrive when this thread's copies land; the consumer fences (see rowconv kernel)
-          cp_async_mbar_arrive_noinc(full_s(g));
+          if (gt == 0)
+            CB2_TRACE_EVENT(g, 3, step - 1);  // copies issued
           return true;
         },
         [&](int, int, int) -> bool { return true; });
-    cp_async_wait_all();
+    if constexpr (GATHER == kGatherCpAsync)
+      cp_async_wait_all();
   }
 
   tc_fence_before();
@@ -431,71 +610,81 @@ struct WgradReduceParams {
   int out_f32;
 };
 
-// One block per (f, group of 32 float4 columns of the [m_total x n_total] slice); the 8 warps
-// of a block each add every 8th unit, then the 8 warp sums are combined in a fixed order.
+// The partials of a unit are one contiguous array of E4 = gy * (block_n/4) * 128 float4
+// (index e4 = (by * block_n/4 + col/4) * 128 + row), so the reduction is a sum of S_f such
+// arrays.  Offsets with few units: one thread per float4.  Offsets with many (the centre
+// of a submanifold conv has one per CTA): the 8 warps of a block each add every 8th unit
+// for 32 float4, and the 8 sums are combined in a fixed order.  No atomics: deterministic.
 __global__ void __launch_bounds__(256) wgrad_reduce_kernel(const WgradReduceParams p) {
   __shared__ float4 s_part[8][32];
-  __shared__ int s_flags[256];
+  __shared__ int s_flags[512];
   const int f = blockIdx.y;
   if (!((p.mask_filter >> f) & 1u))
     return;
   const int S = p.sched[f], base = p.sched[32 + f];
-  const int n4 = p.n_total >> 2;                     // float4 per row (n_total is a multiple of 8)
-  const long long total4 = (long long)p.m_total * n4;
-  const int n_tiles_n = (p.n_total + p.block_n - 1) / p.block_n;
+  const int bn4 = p.block_n >> 2;
+  const long long E4 = (long long)p.gy * bn4 * 128;
+  const bool split = S > 8;
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  const long long e4 = (long long)blockIdx.x * 32 + lane;
-  const bool in_range = e4 < total4;
-  int m = 0, n = 0, by = 0;
-  long long in_tile = 0;
-  if (in_range) {
-    m = (int)(e4 / n4);
-    n = (int)(e4 % n4) * 4;
-    const int mt = m >> 7, ntile = n / p.block_n;
-    by = mt * n_tiles_n + ntile;
-    in_tile = (long long)(m & 127) * p.block_n + (n - ntile * p.block_n);
+  long long e4;
+  if (split) {
+    e4 = (long long)blockIdx.x * 32 + lane;
+  } else {
+    e4 = (long long)blockIdx.x * 256 + threadIdx.x;
+    if ((long long)blockIdx.x * 256 >= E4)
+      return;
   }
+  const bool in_range = e4 < E4;
+  const int by = in_range ? (int)(e4 / (bn4 * 128)) : 0;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int s0 = 0; s0 < S; s0 += 256) {
+  for (int s0 = 0; s0 < S; s0 += 512) {
+    const int cnt = min(512, S - s0);
     __syncthreads();
-    if (s0 + (int)threadIdx.x < S)
-      s_flags[threadIdx.x] = 0;
-    __syncthreads();
-    const int cnt = min(256, S - s0);
-    // flags depend on the (m-tile, n-tile) of the element; with one tile pair per block row this is
-    // uniform across the block, so the flags of `by` of lane 0's element are shared
-    const int by0 = __shfl_sync(0xffffffffu, by, 0);
-    if ((int)threadIdx.x < cnt)
-      s_flags[threadIdx.x] = p.unit_flags[(long long)(base + s0 + threadIdx.x) * p.gy + by0];
+    // a block's elements share one (m-tile, n-tile) pair `by`: 32 or 256 consecutive e4 never
+    // straddle a multiple of block_n/4 * 128 >= 2048
+    for (int i = threadIdx.x; i < cnt; i += blockDim.x)
+      s_flags[i] = p.unit_flags[(long long)(base + s0 + i) * p.gy + by];
     __syncthreads();
     if (in_range) {
-#pragma unroll 4
-      for (int s = wid; s < cnt; s += 8) {
-        const long long u = base + s0 + s;
-        const bool on = (by == by0) ? (s_flags[s] != 0) : (p.unit_flags[u * p.gy + by] != 0);
-        if (on) {
-          const float4 v = *reinterpret_cast<const float4 *>(p.partials + (u * p.gy + by) * 128 * p.block_n + in_tile);
-          acc.x += v.x;
-          acc.y += v.y;
-          acc.z += v.z;
-          acc.w += v.w;
-        }
+      const float4 *src = reinterpret_cast<const float4 *>(p.partials) + (long long)(base + s0) * E4 + e4;
+      const int first = split ? wid : 0, stride = split ? 8 : 1;
+#pragma unroll 8
+      for (int s = first; s < cnt; s += stride) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (s_flags[s])
+          v = __ldg(src + (long long)s * E4);
+        acc.x += v.x;
+        acc.y += v.y;
+        acc.z += v.z;
+        acc.w += v.w;
       }
     }
   }
-  s_part[wid][lane] = acc;
-  __syncthreads();
-  if (wid != 0 || !in_range)
-    return;
-  float r[4] = {0.f, 0.f, 0.f, 0.f};
+  float r[4] = {acc.x, acc.y, acc.z, acc.w};
+  if (split) {
+    s_part[wid][lane] = acc;
+    __syncthreads();
+    if (wid != 0)
+      return;
+    r[0] = r[1] = r[2] = r[3] = 0.f;
 #pragma unroll
-  for (int w = 0; w < 8; ++w) {
-    const float4 v = s_part[w][lane];
-    r[0] += v.x;
-    r[1] += v.y;
-    r[2] += v.z;
-    r[3] += v.w;
+    for (int w = 0; w < 8; ++w) {
+      const float4 v = s_part[w][lane];
+      r[0] += v.x;
+      r[1] += v.y;
+      r[2] += v.z;
+      r[3] += v.w;
+    }
   }
+  if (!in_range)
+    return;
+  const int n_tiles_n = (p.n_total + p.block_n - 1) / p.block_n;
+  const int rem = (int)(e4 % (bn4 * 128));
+  const int col4 = rem >> 7, row = rem & 127;
+  const int m = (by / n_tiles_n) * 128 + row;
+  const int n = (by % n_tiles_n) * p.block_n + col4 * 4;
+  if (m >= p.m_total || n >= p.n_total)
+    return;
   const long long off = (long long)m * p.ldo + (long long)f * p.f_stride + n;
   if (p.out_f32) {
     float *o = reinterpret_cast<float *>(p.out);
