@@ -14,7 +14,7 @@
 #include <string>
 
 #ifndef CB2_DEFAULT_GATHER
-#define CB2_DEFAULT_GATHER 0
+#define CB2_DEFAULT_GATHER 2
 #endif
 
 namespace {
