@@ -26,6 +26,9 @@ EXPORTED_SYMBOLS = (
     "cb2_last_error",
     "cb2_device_status",
     "cb2_launch_count",
+    "cb2_conv_backward_weight_static",
+    "cb2_static_scratch_bytes",
+    "cb2_static_status",
 )
 
 
@@ -111,6 +114,11 @@ def load() -> ctypes.CDLL:
     L.cb2_device_status.restype = ctypes.c_int
     L.cb2_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
     L.cb2_launch_count.restype = ctypes.c_uint64
+    L.cb2_conv_backward_weight_static.restype = ctypes.c_int
+    L.cb2_conv_backward_weight_static.argtypes = [ctypes.POINTER(ConvArgs), ctypes.c_void_p]
+    L.cb2_static_scratch_bytes.restype = ctypes.c_size_t
+    L.cb2_static_status.restype = ctypes.c_int
+    L.cb2_static_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
     _lib = L
     return L
 

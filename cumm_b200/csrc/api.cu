@@ -347,6 +347,55 @@ int run_wgrad(DeviceState *dev, WgradParams &p, void *workspace, size_t workspac
   return CB2_OK;
 }
 
+// ---------------------------------------------------------------- allocation-free variant
+// Scratch for cb2_conv_backward_weight_static: lives in the library image, one copy per GPU
+// that loads it, for the life of the process.  In host code this name is only a handle for
+// cudaGetSymbolAddress, never a pointer a kernel may be given.
+constexpr size_t kStaticScratchBytes = 16u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+static __device__ int g_static_status[16];
+
+struct StaticState {
+  bool ready = false;
+  DeviceState dev;  // num_sms, and `status` pointing at g_static_status on that device
+  void *scratch = nullptr;
+};
+StaticState g_static[kMaxDevices];
+
+// Per-device set-up of the allocation-free path, with that device current: resolves the
+// device addresses of the two static arrays.  Nothing here allocates.
+int get_device_static(StaticState **out) {
+  int dev = 0;
+  CB2_CUDA(cudaGetDevice(&dev));
+  CB2_CHECK_RT(dev >= 0 && dev < kMaxDevices, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_mu);
+  StaticState &st = g_static[dev];
+  if (!st.ready) {
+    cudaDeviceProp prop;
+    CB2_CUDA(cudaGetDeviceProperties(&prop, dev));
+    CB2_CHECK_RT(prop.major == 10, "cumm_b200 kernels are built for sm_100a only; device %d is sm_%d%d", dev,
+                 prop.major, prop.minor);
+    st.dev.num_sms = prop.multiProcessorCount;
+    void *scratch = nullptr, *status = nullptr;
+    CB2_CUDA(cudaGetSymbolAddress(&scratch, g_static_scratch));
+    CB2_CUDA(cudaGetSymbolAddress(&status, g_static_status));
+    CB2_CHECK_RT(scratch != nullptr && status != nullptr, "could not resolve the static scratch on device %d", dev);
+    st.scratch = scratch;
+    st.dev.status = reinterpret_cast<int *>(status);
+    st.dev.ready = true;
+    st.ready = true;
+  }
+  if (!g_encode) {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    CB2_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+    CB2_CHECK_RT(fn != nullptr && q == cudaDriverEntryPointSuccess, "cuTensorMapEncodeTiled not available");
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  *out = &st;
+  return CB2_OK;
+}
+
 int kind_of(int da, int db, int dc, int is_int8, bool allow_f32_out) {
   if (da == CB2_DTYPE_F16 && db == CB2_DTYPE_F16 &&
       (dc == CB2_DTYPE_F16 || (allow_f32_out && dc == CB2_DTYPE_F32)) && !is_int8)
@@ -414,6 +463,74 @@ size_t cb2_conv_workspace_size(const cb2_conv_args *a) {
   WgradLayout L;
   wgrad_layout(dev->num_sms, a->K, a->C, &L);
   return L.total;
+}
+
+size_t cb2_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+int cb2_conv_backward_weight_static(const cb2_conv_args *a, void *stream_v) {
+  CB2_CHECK_ARG(a != nullptr, "null arguments");
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  StaticState *st;
+  int rc = get_device_static(&st);
+  if (rc)
+    return rc;
+  CB2_CHECK_RT(a->op_type == CB2_CONV_BACKWARD_WEIGHT, "the static-scratch entry point computes the weight gradient only");
+  CB2_CHECK_RT(a->ptr_A && a->ptr_B && a->ptr_C, "input, weight, output must not empty");
+  CB2_CHECK_RT(a->indice_ptr && a->mask_ptr && a->mask_argsort_ptr, "error: indices, mask or mask_argsort empty");
+  CB2_CHECK_RT(a->kernel_volume >= 1 && a->kernel_volume <= 32, "kernel volume %d is not supported", a->kernel_volume);
+  CB2_CHECK_ARG(a->N >= 0 && a->C > 0 && a->K > 0, "bad N,C,K (%d,%d,%d)", a->N, a->C, a->K);
+  CB2_CHECK_RT(kind_of(a->dtype_a, a->dtype_b, a->dtype_c, a->is_int8_inference, true) == 0,
+               "can't find any suitable algo for dtypes (%d,%d,%d)", a->dtype_a, a->dtype_b, a->dtype_c);
+  CB2_CHECK_ARG(a->C % 8 == 0 && a->K % 8 == 0, "fp16 channel counts must be multiples of 8");
+  CB2_CHECK_RT(a->mask_width > 0 && (a->mask_width % 128 == 0 || 128 % a->mask_width == 0),
+               "error: mask_width must be positive and divide or be a multiple of %d", 128);
+  const int need_words = (a->N + a->mask_width - 1) / a->mask_width;
+  CB2_CHECK_RT(a->mask_words >= need_words, "reduced mask has %d words, %d needed", a->mask_words, need_words);
+  WgradLayout L;
+  wgrad_layout(st->dev.num_sms, a->K, a->C, &L);
+  CB2_CHECK_RT(L.total <= kStaticScratchBytes,
+               "this problem (K=%d, C=%d) needs %zu bytes of scratch; the static scratch holds %zu. Use cb2_conv_run "
+               "with a caller-provided workspace instead.",
+               a->K, a->C, L.total, kStaticScratchBytes);
+  WgradParams p;
+  memset(&p, 0, sizeof(p));
+  p.dout = a->ptr_A;
+  p.x = a->ptr_B;
+  p.indices = a->indice_ptr;
+  p.rmask = a->mask_ptr;
+  p.argsort = a->mask_argsort_ptr;
+  p.ld_dout = a->K;
+  p.ld_x = a->C;
+  p.n_rows = a->N;
+  p.a_rows = a->rows_A;
+  p.b_rows = a->rows_B;
+  p.m_total = a->K;
+  p.n_total = a->C;
+  p.kv = a->kernel_volume;
+  p.mask_width = a->mask_width;
+  p.rmask_words = a->mask_words;
+  p.mask_filter = a->mask_filter;
+  p.mode = kWgradMaskConv;
+  // every unit flag and partial the second stage reads is rewritten by the first stage of
+  // the same call, so nothing has to be cleared between calls
+  return run_wgrad(&st->dev, p, st->scratch, kStaticScratchBytes, a->ptr_C, a->ptr_D,
+                   (long long)a->kernel_volume * a->C, a->C, a->alpha, a->beta, a->dtype_c == CB2_DTYPE_F32 ? 1 : 0,
+                   stream);
+}
+
+int cb2_static_status(int *status) {
+  StaticState *st;
+  int rc = get_device_static(&st);
+  if (rc)
+    return rc;
+  CB2_CUDA(cudaDeviceSynchronize());
+  int v = 0;
+  CB2_CUDA(cudaMemcpy(&v, st->dev.status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (v != 0)
+    CB2_CUDA(cudaMemset(st->dev.status, 0, sizeof(int)));
+  if (status)
+    *status = v;
+  return CB2_OK;
 }
 
 int cb2_gemm_run(const cb2_gemm_args *a, void *stream_v) {

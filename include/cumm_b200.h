@@ -145,6 +145,33 @@ int cb2_conv_run(const cb2_conv_args *args, void *stream);
 size_t cb2_gemm_workspace_size(const cb2_gemm_args *args);
 size_t cb2_conv_workspace_size(const cb2_conv_args *args);
 
+/*
+ * Weight gradient without any allocation.  (No counterpart in the reference: its callee
+ * allocates scratch whenever the caller passes none.)
+ *
+ * For callers that may not allocate device memory where they run: code inside a CUDA
+ * stream capture, a real-time or inference-server thread that is forbidden to touch the
+ * allocator, a plugin whose host hands it tensors but no allocator.  It computes exactly
+ * what cb2_conv_run computes for CB2_CONV_BACKWARD_WEIGHT with the same arguments, except
+ * that args->workspace is ignored: the partial sums go to a fixed 16 MiB array that is
+ * part of the library image (cb2_static_scratch_bytes()).  Every GPU that loads the library
+ * holds that array until the process exits.
+ *
+ *  - Problems whose scratch does not fit (roughly K * C > 128 * 128 on a 148-SM part) are
+ *    refused with CB2_ERR_RUNTIME and a message naming both sizes; nothing is launched.
+ *  - The first call on each device resolves the array's device address.  That one call
+ *    should be made before any stream capture begins on that device.
+ *  - All calls share the one array and it keeps the previous call's contents; the kernels
+ *    rewrite every word they later read, so no clearing is needed between calls, but two
+ *    calls that overlap on the same GPU (different streams, no ordering) race on it.
+ *  - Neither this call nor anything it calls uses cudaMalloc, cudaFree or an allocating
+ *    library routine.  Its kernels report through their own status word:
+ *    cb2_static_status() is to this entry point what cb2_device_status() is to the others.
+ */
+int cb2_conv_backward_weight_static(const cb2_conv_args *args, void *stream);
+size_t cb2_static_scratch_bytes(void);
+int cb2_static_status(int *status);
+
 /* Rows of one output tile, i.e. the granularity of mask_out_ptr and the mask_width to
  * hand to backward weight (the reference uses the forward kernel's tile_shape[0],
  * cumm/conv/main_real_spconv.py:176-177). */
