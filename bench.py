@@ -367,6 +367,9 @@ def main():
         names = ["forward", "backward_input", "backward_weight(+reduce)", "allreduce+cast"]
         dom = int(np.argmax(op_ms[:3]))
         dom_bytes = [fwd_bytes, fwd_bytes, wgrad_bytes][dom]
+        # DRAM bytes per output row from the ncu launch list of this command
+        # (profiles/bench_step_launch_list.md): 468.9 MB and 523.6 MB per launch at 960 000 rows
+        traffic = [488.4, 488.4, 545.4][dom] * tb.n_out
         achieved = dom_bytes / (op_ms[dom] * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
@@ -382,7 +385,8 @@ def main():
                     "ms_per_step": e2e_ms},
             "gpu_launches": gpu_launches,
             "roofline": {"bound": "hbm", "kernel": names[dom], "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                         "frac": achieved / hbm_peak, "peak_source": peak_src, "traffic": None,
+                         "frac": achieved / hbm_peak, "peak_source": peak_src, "traffic": traffic,
+                         "traffic_source": "ncu dram__bytes_read+write per row at 960k rows, scaled by rows",
                          "algorithmic_bytes_per_launch": dom_bytes, "us_per_launch": op_ms[dom] * 1e3},
             "per_op_us": {names[i]: op_ms[i] * 1e3 for i in range(4)},
             "per_op_gbs": {names[i]: [fwd_bytes, fwd_bytes, wgrad_bytes][i] / (op_ms[i] * 1e-3) / 1e9 for i in range(3)},
