@@ -272,23 +272,44 @@ def main():
     stream.synchronize()
     assert _lib.device_status() == 0, "kernel status word set during warm-up"
 
-    graphs = []
+    # Single GPU: the whole step is one graph.  Several GPUs: graph A = forward + weight
+    # gradient, then the all-reduce + cast run eagerly on a side stream (NCCL stays out of
+    # capture) while graph B = input gradient runs on the main stream, so the exchange is
+    # hidden behind compute; the step ends when both streams are done.
+    graphs, graphs_b = [], []
+    side = torch.cuda.Stream(device=dev)
     with torch.cuda.stream(stream):
         for s in sets:
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=stream):
-                step_kernels(s)
                 if world == 1:
+                    step_kernels(s)
                     step_tail(s)
+                else:
+                    s["layer"].fwd.launch()
+                    s["layer"].wgrad.launch()
             graphs.append(g)
+            if world > 1:
+                gb = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gb, stream=stream):
+                    s["layer"].dgrad.launch()
+                graphs_b.append(gb)
     stream.synchronize()
+    ev_a = [torch.cuda.Event() for _ in range(nsets)]
+    ev_b = [torch.cuda.Event() for _ in range(nsets)]
 
     def replay(i):
-        # single GPU: the whole step is one graph; several GPUs: the kernels are a graph and
-        # the all-reduce + cast follow eagerly on the same stream (NCCL stays out of capture)
-        graphs[i % nsets].replay()
+        k = i % nsets
+        graphs[k].replay()
         if world > 1:
-            step_tail(sets[i % nsets])
+            ev_a[k].record(stream)
+            with torch.cuda.stream(side):
+                side.wait_event(ev_a[k])
+                dist.all_reduce(sets[k]["dw32"])
+                sets[k]["dw16"].copy_(sets[k]["dw32"])
+                ev_b[k].record(side)
+            graphs_b[k].replay()
+            stream.wait_event(ev_b[k])
 
     def barrier():
         if world > 1:
@@ -394,7 +415,7 @@ def main():
             "config": {"workload": WORKLOAD, "scenes_per_rank": len(ids), "rows_per_rank": tb.n_out,
                        "pairs_total": pairs_total, "parallelism": f"scene-sharded x{world}, wgrad fp32 all-reduce",
                        "l2": f"rotating {nsets} buffer sets ({nsets * step_bytes / 1e6:.0f} MB touched) > 126 MB L2",
-                       "timed_region": "CUDA-graph replays of fwd+dgrad+wgrad, then (N>1: eager NCCL all-reduce +) cast"},
+                       "timed_region": "N=1: one CUDA graph per step; N>1: graph(fwd+wgrad), then NCCL all-reduce + cast on a side stream overlapped with graph(dgrad)"},
             "voxels_per_s": 3 * rows_total / (ms_step * 1e-3),
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

@@ -52,6 +52,8 @@ int set_err(int code, const char *fmt, ...) {
   } while (0)
 
 constexpr int kMaxDevices = 64;
+constexpr int kTicketSlots = 256;
+constexpr size_t kStatusBytes = (16 + 2 * kTicketSlots) * sizeof(int);
 
 struct DeviceState {
   bool ready = false;
@@ -79,8 +81,9 @@ int get_device(DeviceState **out) {
     CB2_CHECK_RT(prop.major == 10, "cumm_b200 kernels are built for sm_100a only; device %d is sm_%d%d",
                  dev, prop.major, prop.minor);
     st.num_sms = prop.multiProcessorCount;
-    CB2_CUDA(cudaMalloc(&st.status, 64));
-    CB2_CUDA(cudaMemset(st.status, 0, 64));
+    // word 0: kernel status; from word 16 on: kTicketSlots pairs of scheduling counters
+    CB2_CUDA(cudaMalloc(&st.status, kStatusBytes));
+    CB2_CUDA(cudaMemset(st.status, 0, kStatusBytes));
     st.ready = true;
   }
   if (!g_encode) {
@@ -235,6 +238,12 @@ int run_rowconv(DeviceState *dev, RowConvParams &p, int kind, bool b_mn, const v
     }
   }
   p.status = dev->status;
+  // Dynamic tile scheduling draws from a pair of device counters that the kernel itself
+  // returns to zero.  Launches take counter pairs round-robin, so two launches that overlap
+  // on different streams use different pairs unless more than kTicketSlots are in flight.
+  static std::atomic<unsigned> next_slot{0};
+  p.tickets = getenv("CUMM_B200_STATIC_TILES") ? nullptr
+                                               : dev->status + 16 + 2 * (next_slot.fetch_add(1) % kTicketSlots);
   const int ntiles = (p.n_rows + 127) / 128;
   const int gy = (p.nn + pl.block_n - 1) / pl.block_n;
   int gx = dev->num_sms / gy;
@@ -436,8 +445,8 @@ int cb2_device_status(int *status) {
   CB2_CUDA(cudaDeviceSynchronize());
   int v = 0;
   CB2_CUDA(cudaMemcpy(&v, dev->status, sizeof(int), cudaMemcpyDeviceToHost));
-  if (v != 0)
-    CB2_CUDA(cudaMemset(dev->status, 0, sizeof(int)));
+  if (v != 0)  // a kernel that gave up may have left its scheduling counters non-zero: clear everything
+    CB2_CUDA(cudaMemset(dev->status, 0, kStatusBytes));
   if (status)
     *status = v;
   return CB2_OK;

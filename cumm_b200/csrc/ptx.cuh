@@ -21,6 +21,7 @@ __device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31; }
 struct TraceBuf {
   unsigned long long ev[8][512][2];  // [role][event][time, (code << 32) | step]
   int count[8];
+  unsigned long long cta[256][3];    // per CTA: start time, end time, steps
 };
 __device__ TraceBuf g_trace;
 __device__ __forceinline__ void trace_event(int role, int code, int step) {
@@ -35,9 +36,19 @@ __device__ __forceinline__ void trace_event(int role, int code, int step) {
   g_trace.ev[role][n][1] = (static_cast<unsigned long long>(code) << 32) | static_cast<unsigned>(step);
   g_trace.count[role] = n + 1;
 }
+__device__ __forceinline__ void trace_cta(int which, unsigned long long value) {
+  if (blockIdx.x >= 256 || blockIdx.y != 0)
+    return;
+  if (which < 2) {
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(value));
+  }
+  g_trace.cta[blockIdx.x][which] = value;
+}
 #define CB2_TRACE_EVENT(role, code, step) ::cb2::trace_event(role, code, step)
+#define CB2_TRACE_CTA(which, value) ::cb2::trace_cta(which, value)
 #else
 #define CB2_TRACE_EVENT(role, code, step) ((void)0)
+#define CB2_TRACE_CTA(which, value) ((void)0)
 #endif
 
 // ---------------------------------------------------------------- mbarrier
@@ -115,6 +126,14 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
   int ok = 1;
   if (lane_id() == 0)
     ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
+// Non-blocking, warp-uniform test (lane 0 tests, the result is broadcast).
+__device__ __forceinline__ bool mbar_test_warp(uint32_t bar, uint32_t parity) {
+  int ok = 0;
+  if (lane_id() == 0)
+    ok = mbar_test(bar, parity) ? 1 : 0;
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 

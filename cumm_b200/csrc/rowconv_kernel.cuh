@@ -37,6 +37,7 @@ struct RowConvParams {
   const int32_t *a_inds;   // gather-GEMM mode (null = identity)
   const int32_t *c_inds;   //   "
   int *status;             // device status word (0 = ok)
+  int *tickets;            // two zero-initialised ints (next ticket, finished CTAs) or null = static round-robin
   long long lda, ldo, lds; // row strides in elements
   int n_rows;              // rows to produce (sorted positions, or m)
   int a_rows;              // rows available in `a`
@@ -70,7 +71,11 @@ template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN> struct RowConvCfg {
   static constexpr int TMEM_COLS = NUM_ACC * BLOCK_N;     // 128 or 256: power of two >= 32
   static constexpr int EPI_THREADS = 128;
   static constexpr int GROUP_THREADS = 128;
-  static constexpr int THREADS = EPI_THREADS + 64 + SA * GROUP_THREADS;  // 576
+  static constexpr int SCHED_WARP = (EPI_THREADS + 64 + SA * GROUP_THREADS) / 32;   // the last warp hands out tiles
+  static constexpr int THREADS = EPI_THREADS + 64 + SA * GROUP_THREADS + 32;  // 608
+  static constexpr int RING = 6;                          // tile ring slots
+  static constexpr int RING_SLOT_INTS = 264;              // tile, mask, pad; 128 gather rows; 128 output rows
+  static constexpr int RING_CONSUMER_WARPS = 4 + 1 + 1 + SA * 4;
   // shared memory map (offsets from a 1024-byte aligned base)
   static constexpr int OFF_A = 0;
   static constexpr int OFF_B = OFF_A + SA * A_STAGE_BYTES;
@@ -78,25 +83,11 @@ template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN> struct RowConvCfg {
   static constexpr int OFF_ROWIDX = OFF_STAGING + STAGING_BYTES;     // SA * 2 * 128 ints
   static constexpr int OFF_OUTROW = OFF_ROWIDX + SA * 2 * 128 * 4;   // 128 ints
   static constexpr int OFF_SCALE = OFF_OUTROW + 128 * 4;             // 2 * BLOCK_N floats
-  static constexpr int OFF_BARS = OFF_SCALE + 2 * BLOCK_N * 4;       // 16 mbarriers
-  static constexpr int OFF_MISC = OFF_BARS + 16 * 8;                 // tmem ptr, abort, flags
+  static constexpr int OFF_RING = OFF_SCALE + 2 * BLOCK_N * 4;       // RING slots
+  static constexpr int OFF_BARS = OFF_RING + RING * RING_SLOT_INTS * 4;  // 16 + 2 * RING mbarriers
+  static constexpr int OFF_MISC = OFF_BARS + (16 + 2 * RING) * 8;                 // tmem ptr, abort, flags
   static constexpr int SMEM_BYTES = OFF_MISC + 64 + 1024;            // + alignment slack
 };
-
-// ---- tile mask helpers (all 32 lanes of the calling warp take part) -------------------
-__device__ __forceinline__ uint32_t tile_mask_partial(const RowConvParams &p, int tile, int ntiles) {
-  if (p.mode != kModeMaskConv || tile >= ntiles)
-    return 0;
-  uint32_t v = 0;
-  int base = tile * 128 + (int)lane_id();
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    int r = base + i * 32;
-    if (r < p.n_rows)
-      v |= __ldg(p.mask + r);
-  }
-  return v;
-}
 
 __device__ __forceinline__ float apply_act(float x, int act_type, float act_alpha) {
   switch (act_type) {
@@ -117,44 +108,194 @@ __device__ __forceinline__ uint32_t cvt_sat_s8(float t) {
   return static_cast<uint32_t>(r) & 0xffu;
 }
 
-// Walks this CTA's tiles and, inside each, the (filter offset, reduction pass) steps.
-// on_tile(tile, kmask_for_store, has_work) -> bool ; on_step(tile, f, kp, first, last) -> bool;
-// a false return aborts the walk.  Every role of the CTA runs the identical walk so that
-// their ring counters agree.
+// Tiles are handed out by one scheduler warp per CTA through a small shared-memory ring.
+// A slot holds {tile, OR-ed neighbour mask of the tile, the 128 rows the gather starts from,
+// the 128 destination rows}.  With `tickets` the scheduler draws tiles from a global counter
+// (dynamic scheduling: a tile whose mask carries many offsets costs many steps, and a static
+// split leaves the CTAs that own such tiles running long after the others), last tiles of
+// the sorted order first because those carry the most offsets.
+struct RingView {
+  int *slots;
+  uint32_t full0, empty0;  // addresses of the first "filled" / "released" barrier
+  int ring, slot_ints;
+  volatile int *abort_flag;
+  __device__ __forceinline__ int *slot(int i) const { return slots + i * slot_ints; }
+};
+
+// Walks the tiles the scheduler publishes and, inside each, the (filter offset, reduction
+// pass) steps.  on_tile(tile, slot, kmask_for_store, has_work) -> bool; on_step(tile, f, kp,
+// first, last) -> bool; a false return aborts the walk.  Every consumer warp of the CTA runs
+// the identical walk, so their step counters agree.  All 32 lanes take part.
 template <class TileFn, class StepFn>
-__device__ __forceinline__ void walk_steps(const RowConvParams &p, int ntiles, int kpasses, TileFn on_tile,
+__device__ __forceinline__ bool walk_steps(const RowConvParams &p, const RingView &rv, int kpasses, TileFn on_tile,
                                            StepFn on_step) {
-  int tile = blockIdx.x;
-  uint32_t part_next = tile_mask_partial(p, tile, ntiles);
-  for (; tile < ntiles; tile += gridDim.x) {
-    uint32_t part = part_next;
-    part_next = tile_mask_partial(p, tile + gridDim.x, ntiles);
-    uint32_t kmask;
-    if (p.mode == kModeMaskConv) {
-      kmask = __reduce_or_sync(0xffffffffu, part) & p.mask_filter;
-      if (p.kv < 32)
-        kmask &= (1u << p.kv) - 1u;
-    } else {
-      kmask = 1u;
-    }
-    uint32_t kmask_store = kmask;
-    if (p.skip_empty_tiles && kmask == 0)
-      continue;
-    if (p.reverse_mask)
-      kmask = __brev(kmask) >> (32 - p.kv);
-    if (!on_tile(tile, kmask_store, kmask != 0))
-      return;
-    uint32_t bits = kmask;
-    bool first = true;
-    while (bits) {
-      int f = __ffs(bits) - 1;
-      bits &= bits - 1;
-      for (int kp = 0; kp < kpasses; ++kp) {
-        bool last = (bits == 0) && (kp == kpasses - 1);
-        if (!on_step(tile, f, kp, first, last))
-          return;
-        first = false;
+  for (int seq = 0;; ++seq) {
+    const int si = seq % rv.ring;
+    if (!mbar_wait_warp(rv.full0 + 8u * si, (seq / rv.ring) & 1, rv.abort_flag))
+      return false;
+    const int *sl = rv.slot(si);
+    const int tile = sl[0];
+    uint32_t kmask = static_cast<uint32_t>(sl[1]);
+    const uint32_t kmask_store = kmask;
+    bool cont = true;
+    if (tile >= 0 && !(p.skip_empty_tiles && kmask == 0)) {
+      if (p.reverse_mask)
+        kmask = __brev(kmask) >> (32 - p.kv);
+      cont = on_tile(tile, sl, kmask_store, kmask != 0);
+      uint32_t bits = kmask;
+      bool first = true;
+      while (cont && bits) {
+        int f = __ffs(bits) - 1;
+        bits &= bits - 1;
+        for (int kp = 0; cont && kp < kpasses; ++kp) {
+          bool last = (bits == 0) && (kp == kpasses - 1);
+          cont = on_step(tile, f, kp, first, last);
+          first = false;
+        }
       }
+    }
+    __syncwarp();
+    if (lane_id() == 0)
+      mbar_arrive(rv.empty0 + 8u * si);
+    if (!cont)
+      return false;
+    if (tile < 0)
+      return true;  // end marker
+  }
+}
+
+// The scheduler warp: draws tiles, fetches their mask words and row numbers straight into
+// the ring slot with 4-byte cp.async (no registers involved, so several tiles can be in
+// flight and a slot is published when ITS copies have landed), then publishes the slot.
+// Slot layout (ints): [0] tile (-1 = no more tiles), [1] OR-ed mask, [8,136) rows the gather
+// starts from, [136,264) destination rows in gather-GEMM mode / raw mask words in conv mode
+// (in conv mode the destination rows are the gather rows).
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void *src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+
+__device__ __forceinline__ void scheduler_run(const RowConvParams &p, const RingView &rv, int ntiles, int kpasses) {
+  constexpr int DEPTH = 2;       // tiles whose words are in flight besides the one being published
+  constexpr int STEP_BUDGET = 6; // steps a CTA may hold (drawn, not finished) before it stops drawing tiles
+  const int lane = (int)lane_id();
+  const bool dynamic = p.tickets != nullptr && gridDim.y == 1;
+  const bool conv = p.mode == kModeMaskConv;
+  int drawn = 0;
+  auto draw = [&]() -> int {
+    int t;
+    if (dynamic) {
+      t = 0;
+      if (lane == 0)
+        t = atomicAdd(p.tickets, 1);
+      t = __shfl_sync(0xffffffffu, t, 0);
+    } else {
+      t = blockIdx.x + drawn * gridDim.x;
+    }
+    ++drawn;
+    return t;
+  };
+  const uint32_t slots_addr = smem_u32(rv.slots);
+  int issued = 0, published = 0, released = 0, held_steps = 0;
+  bool end = false;
+  for (;;) {
+    if (!end) {
+      // Tiles a CTA has drawn but not finished cannot be taken over by an idle CTA, so the
+      // look-ahead is bounded by WORK, not by tiles: a CTA keeps drawing while the steps it
+      // holds (one per offset in a tile's mask; 1 assumed until the mask has arrived) are within
+      // STEP_BUDGET.  Light tiles keep the pipeline deep; after a tile with many offsets the CTA
+      // draws nothing until that tile is finished.
+      auto account_released = [&]() {
+        while (released < published &&
+               mbar_test_warp(rv.empty0 + 8u * (released % rv.ring), (released / rv.ring) & 1)) {
+          held_steps -= rv.slot(released % rv.ring)[2];
+          ++released;
+        }
+      };
+      for (;;) {
+        account_released();
+        if (held_steps <= STEP_BUDGET || released == published)
+          break;
+        if (!mbar_wait_warp(rv.empty0 + 8u * (released % rv.ring), (released / rv.ring) & 1, rv.abort_flag))
+          return;
+      }
+      const int si = issued % rv.ring;
+      if (!mbar_wait_warp(rv.empty0 + 8u * si, ((issued / rv.ring) & 1) ^ 1, rv.abort_flag))
+        return;
+      account_released();  // before the slot's step count is overwritten
+      const int ticket = draw();
+      held_steps += 1;
+      int tile = -1;
+      if (ticket < ntiles)
+        tile = conv ? (ntiles - 1 - ticket) : ticket;  // the last tiles of the sorted order carry the most offsets
+      int *sl = rv.slot(si);
+      const uint32_t sa = slots_addr + static_cast<uint32_t>(si * rv.slot_ints) * 4u;
+      if (lane == 0)
+        sl[0] = tile;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int j = i * 32 + lane;
+        const int r = tile * 128 + j;
+        if (tile >= 0 && r < p.n_rows) {
+          if (conv) {
+            cp_async_4(sa + (8 + j) * 4, p.argsort + r);
+            cp_async_4(sa + (136 + j) * 4, p.mask + r);
+          } else {
+            sl[8 + j] = r;
+            if (p.c_inds)
+              cp_async_4(sa + (136 + j) * 4, p.c_inds + r);
+            else
+              sl[136 + j] = r;
+          }
+        } else {
+          sl[8 + j] = -1;
+          sl[136 + j] = conv ? 0 : -1;
+        }
+      }
+      cp_async_commit();
+      ++issued;
+      end = tile < 0;
+    }
+    while (published < issued && (end || issued - published > DEPTH)) {
+      const int pending = issued - published - 1;  // younger groups that may stay in flight
+      if (pending >= 2)
+        cp_async_wait<2>();
+      else if (pending == 1)
+        cp_async_wait<1>();
+      else
+        cp_async_wait<0>();
+      __syncwarp();
+      const int si = published % rv.ring;
+      int *sl = rv.slot(si);
+      uint32_t kmask = 1u;
+      if (conv) {
+        const uint32_t m = static_cast<uint32_t>(sl[136 + lane]) | static_cast<uint32_t>(sl[136 + 32 + lane]) |
+                           static_cast<uint32_t>(sl[136 + 64 + lane]) | static_cast<uint32_t>(sl[136 + 96 + lane]);
+        kmask = __reduce_or_sync(0xffffffffu, m) & p.mask_filter;
+        if (p.kv < 32)
+          kmask &= (1u << p.kv) - 1u;
+      }
+      const int nsteps = (sl[0] >= 0) ? max(1, __popc(kmask) * kpasses) : 1;
+      held_steps += nsteps - 1;  // the tile was counted as one step when it was drawn
+      __syncwarp();
+      if (lane == 0) {
+        sl[1] = static_cast<int>(kmask);
+        sl[2] = nsteps;
+      }
+      __syncwarp();
+      if (lane == 0)
+        mbar_arrive(rv.full0 + 8u * si);
+      ++published;
+    }
+    if (end && published == issued)
+      break;
+  }
+  // the last CTA to run out of tiles puts the two counters back to zero for the next launch
+  if (dynamic && lane == 0) {
+    const int done = atomicAdd(p.tickets + 1, 1);
+    if (done == (int)(gridDim.x * gridDim.y) - 1) {
+      p.tickets[0] = 0;
+      p.tickets[1] = 0;
+      __threadfence();
     }
   }
 }
@@ -164,6 +305,10 @@ __global__ void __launch_bounds__(RowConvCfg<KIND, NATOM_K, BLOCK_N, B_MN>::THRE
 rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p) {
   using Cfg = RowConvCfg<KIND, NATOM_K, BLOCK_N, B_MN>;
   extern __shared__ uint8_t smem_raw[];
+  if (threadIdx.x == 0) {
+    CB2_TRACE_EVENT(5, 10, 0);  // kernel entered
+    CB2_TRACE_CTA(0, 0);
+  }
   // 1024-byte alignment: required by the 128-byte swizzle atoms of TMA and tcgen05.
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -186,6 +331,13 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
   auto acc_full = [&](int s) { return bars + 8u * (10 + s); };
   auto acc_empty = [&](int s) { return bars + 8u * (12 + s); };
   const uint32_t final_bar = bars + 8u * 14;
+  RingView rv;
+  rv.slots = reinterpret_cast<int *>(smem + Cfg::OFF_RING);
+  rv.full0 = bars + 8u * 16;
+  rv.empty0 = bars + 8u * (16 + Cfg::RING);
+  rv.ring = Cfg::RING;
+  rv.slot_ints = Cfg::RING_SLOT_INTS;
+  rv.abort_flag = abort_flag;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -207,6 +359,10 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
       mbar_init(acc_empty(s), Cfg::EPI_THREADS);
     }
     mbar_init(final_bar, 1);
+    for (int s = 0; s < Cfg::RING; ++s) {
+      mbar_init(rv.full0 + 8u * s, 1);
+      mbar_init(rv.empty0 + 8u * s, Cfg::RING_CONSUMER_WARPS);
+    }
     mbar_init_fence();
     misc[1] = 0;
     misc[2] = misc[3] = misc[4] = misc[5] = 1;
@@ -226,6 +382,8 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = static_cast<uint32_t>(misc[0]);
+  if (threadIdx.x == 0)
+    CB2_TRACE_EVENT(5, 11, 0);  // set-up done
 
   auto fail = [&](int code) {
     *abort_flag = 1;
@@ -242,22 +400,17 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
     constexpr int CH_PER_ROUND = 32 * Cfg::OES / 16;   // chunks produced per 32 columns
     int acc_use = 0;
     walk_steps(
-        p, ntiles, kpasses,
-        [&](int tile, uint32_t kmask_store, bool has_work) -> bool {
-          const int r = tile * 128 + et;
-          int o = -1;
-          if (r < p.n_rows) {
-            if (p.mode == kModeMaskConv)
-              o = __ldg(p.argsort + r);
-            else
-              o = p.c_inds ? __ldg(p.c_inds + r) : r;
-          }
+        p, rv, kpasses,
+        [&](int tile, const int *sl, uint32_t kmask_store, bool has_work) -> bool {
+          const int o = (p.mode == kModeMaskConv) ? sl[8 + et] : sl[136 + et];  // destination row of this thread's tile row
           if (et == 0 && p.mask_out && blockIdx.y == 0)
             p.mask_out[tile] = kmask_store;
           const int buf = acc_use % Cfg::NUM_ACC;
           if (has_work) {
             if (et == 0) {
+              CB2_TRACE_EVENT(4, 7, tile);
               bool ok = mbar_wait(acc_full(buf), (acc_use / Cfg::NUM_ACC) & 1, abort_flag);
+              CB2_TRACE_EVENT(4, 8, tile);  // accumulator complete
               misc[2] = ok ? 1 : 0;
               if (!ok)
                 fail(kStatusWaitTimeout);
@@ -400,6 +553,8 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
             mbar_arrive(acc_empty(buf));
             ++acc_use;
           }
+          if (et == 0)
+            CB2_TRACE_EVENT(4, 12, tile);  // staged
           named_bar_sync(1, Cfg::EPI_THREADS);  // staging complete
           // phase 2: CPR threads per row write whole rows
           {
@@ -422,6 +577,8 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
               }
             }
           }
+          if (et == 0)
+            CB2_TRACE_EVENT(4, 9, tile);  // rows stored
           return true;
         },
         [&](int, int, int, bool, bool) -> bool { return true; });
@@ -431,7 +588,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
     int step = 0, acc_use = 0, bcount = 0, last_key = -1, cur_slot = 0;
     bool ok_all = true;
     walk_steps(
-        p, ntiles, kpasses, [&](int, uint32_t, bool) -> bool { return true; },
+        p, rv, kpasses, [&](int, const int *, uint32_t, bool) -> bool { return true; },
         [&](int tile, int f, int kp, bool first, bool last) -> bool {
           const int buf = acc_use % Cfg::NUM_ACC;
           int ok = 1;
@@ -448,8 +605,10 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
               last_key = key;
             }
             const int stage = step % Cfg::SA;
+            CB2_TRACE_EVENT(3, 4, step);  // waiting for rows
             if (ok)
               ok = mbar_wait(full_a(stage), (step / Cfg::SA) & 1, abort_flag);
+            CB2_TRACE_EVENT(3, 5, step);  // rows landed
             if (ok) {
               fence_proxy_async_smem();  // gathered rows were written through the generic proxy
               tc_fence_after();
@@ -472,6 +631,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
                 tc_mma<KIND>(d_tmem, adesc, bdesc, idesc, (first && ks == 0) ? 0u : 1u);
               }
               tc_commit(empty_a(stage));
+              CB2_TRACE_EVENT(3, 6, step);  // MMAs issued
               if (last)
                 tc_commit(acc_full(buf));
             }
@@ -488,6 +648,8 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
           }
           return true;
         });
+    if (lane == 0)
+      CB2_TRACE_CTA(2, (unsigned long long)step);
     // make sure every MMA has retired before TMEM is released
     if (lane == 0 && ok_all) {
       tc_commit(final_bar);
@@ -501,7 +663,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
       tma_prefetch_desc(&tmap_b);
     int bcount = 0, last_key = -1;
     walk_steps(
-        p, ntiles, kpasses, [&](int, uint32_t, bool) -> bool { return true; },
+        p, rv, kpasses, [&](int, const int *, uint32_t, bool) -> bool { return true; },
         [&](int tile, int f, int kp, bool, bool) -> bool {
           int ok = 1;
           const int key = f * kpasses + kp;
@@ -538,6 +700,9 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
           }
           return true;
         });
+  } else if (warp == Cfg::SCHED_WARP) {
+    // ======================= scheduler: draws tiles, publishes their masks and row numbers
+    scheduler_run(p, rv, ntiles, kpasses);
   } else {
     // ======================= operand-row gather: group g owns stage g
     const int g = (warp - 6) >> 2;                    // 0..2
@@ -551,21 +716,10 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
     int step = 0;
     int o = -1;
     const uint8_t *a_bytes = reinterpret_cast<const uint8_t *>(p.a);
-    auto load_o = [&](int tile) -> int {
-      const int r = tile * 128 + gt;
-      if (tile >= ntiles || r >= p.n_rows)
-        return -1;
-      return (p.mode == kModeMaskConv) ? __ldg(p.argsort + r) : r;
-    };
-    int o_next_tile = blockIdx.x;
-    int o_next = load_o(o_next_tile);
     walk_steps(
-        p, ntiles, kpasses,
-        [&](int tile, uint32_t, bool) -> bool {
-          // the sort index of this thread's row, fetched one tile ahead of its use
-          o = (tile == o_next_tile) ? o_next : load_o(tile);
-          o_next_tile = tile + gridDim.x;
-          o_next = load_o(o_next_tile);
+        p, rv, kpasses,
+        [&](int tile, const int *sl, uint32_t, bool) -> bool {
+          o = sl[8 + gt];  // the row this thread's gather starts from (sort index, or the row itself)
           return true;
         },
         [&](int tile, int f, int kp, bool, bool) -> bool {
@@ -586,7 +740,9 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
             }
           }
           if (gt == 0) {
+            CB2_TRACE_EVENT(g, 1, step - 1 + (idx == 0x7fffffff));  // index loaded
             bool ok = mbar_wait(empty_a(g), (use & 1) ^ 1, abort_flag);
+            CB2_TRACE_EVENT(g, 2, step - 1);  // stage free
             *my_flag = ok ? 1 : 0;
             if (!ok)
               fail(kStatusWaitTimeout);
@@ -615,6 +771,8 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
           // the thread itself runs on to its next step.  The consumer makes the data visible
           // to the tensor core with a proxy fence after its wait.
           cp_async_mbar_arrive_noinc(full_a(g));
+          if (gt == 0)
+            CB2_TRACE_EVENT(g, 3, step - 1);  // copies issued
           return true;
         });
     cp_async_wait_all();
@@ -623,6 +781,8 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
   // ---------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0)
+    CB2_TRACE_CTA(1, 0);
   if (warp == 4) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);

@@ -618,7 +618,9 @@ struct WgradReduceParams {
 __global__ void __launch_bounds__(256) wgrad_reduce_kernel(const WgradReduceParams p) {
   __shared__ float4 s_part[8][32];
   __shared__ int s_flags[512];
-  const int f = blockIdx.y;
+  // blocks are dispatched in blockIdx order: start with the centre offset, which carries by
+  // far the most units in a submanifold convolution, so its blocks are not left for the tail
+  const int f = (blockIdx.y + p.kv / 2) % p.kv;
   if (!((p.mask_filter >> f) & 1u))
     return;
   const int S = p.sched[f], base = p.sched[32 + f];
