@@ -24,8 +24,9 @@ struct TraceBuf {
   unsigned long long cta[256][3];    // per CTA: start time, end time, steps
 };
 __device__ TraceBuf g_trace;
+__device__ int g_trace_cta = 0;  // the CTA whose events are recorded
 __device__ __forceinline__ void trace_event(int role, int code, int step) {
-  if (blockIdx.x != 0 || blockIdx.y != 0)
+  if ((int)blockIdx.x != *(volatile int *)&g_trace_cta || blockIdx.y != 0)
     return;
   int n = g_trace.count[role];
   if (n >= 512)

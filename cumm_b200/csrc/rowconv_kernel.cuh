@@ -223,6 +223,10 @@ __device__ __forceinline__ void scheduler_run(const RowConvParams &p, const Ring
         return;
       account_released();  // before the slot's step count is overwritten
       const int ticket = draw();
+#ifdef CB2_TRACE
+      if (ticket == 0 && lane == 0)
+        g_trace_cta = blockIdx.x;  // follow the CTA that got the heaviest tile
+#endif
       held_steps += 1;
       int tile = -1;
       if (ticket < ntiles)
@@ -587,6 +591,9 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
     constexpr uint32_t idesc = make_idesc(KIND, false, B_MN, 128, BLOCK_N);
     int step = 0, acc_use = 0, bcount = 0, last_key = -1, cur_slot = 0;
     bool ok_all = true;
+    const uint64_t adesc_base = make_smem_desc(sbase + Cfg::OFF_A, 16, 1024);
+    const uint64_t bdesc_base = B_MN ? make_smem_desc(sbase + Cfg::OFF_B, p.b_lbo, p.b_sbo)
+                                     : make_smem_desc(sbase + Cfg::OFF_B, 16, 1024);
     walk_steps(
         p, rv, kpasses, [&](int, const int *, uint32_t, bool) -> bool { return true; },
         [&](int tile, int f, int kp, bool first, bool last) -> bool {
@@ -612,23 +619,30 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
             if (ok) {
               fence_proxy_async_smem();  // gathered rows were written through the generic proxy
               tc_fence_after();
-              const uint32_t a_base = sbase + Cfg::OFF_A + stage * Cfg::A_STAGE_BYTES;
-              const uint32_t b_base = sbase + Cfg::OFF_B + cur_slot * Cfg::B_SLOT_BYTES;
+              // Descriptors differ from the stage's / slot's base descriptor only in the start
+              // address field (bits 0-13, units of 16 bytes), so each one is an add.  This loop is
+              // issued by a single thread: every instruction saved here shortens each step.
+              const uint64_t adesc0 = adesc_base + static_cast<uint64_t>((stage * Cfg::A_STAGE_BYTES) >> 4);
+              const uint64_t bdesc0 = bdesc_base + static_cast<uint64_t>((cur_slot * Cfg::B_SLOT_BYTES) >> 4);
               const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BLOCK_N);
               const int red_left = p.red - kp * Cfg::KRED;
-              const int ksteps_total = (min(red_left, Cfg::KRED) + Cfg::UMMA_K - 1) / Cfg::UMMA_K;
-              for (int ks = 0; ks < ksteps_total; ++ks) {
+              constexpr int KSTEPS_FULL = NATOM_K * 4;
+              auto issue = [&](int ks, uint32_t acc) {
                 const int ka = ks >> 2, kk = ks & 3;
-                const uint64_t adesc =
-                    make_smem_desc(a_base + ka * (Cfg::TILE_M * 128) + kk * 32, 16, 1024);
-                uint64_t bdesc;
-                if constexpr (!B_MN) {
-                  bdesc = make_smem_desc(b_base + ka * (BLOCK_N * 128) + kk * 32, 16, 1024);
-                } else {
-                  // weight slot holds BLOCK_N/ATOM_ELEMS blocks of [KRED rows x 128 B]
-                  bdesc = make_smem_desc(b_base + (ka * 4 + kk) * (Cfg::UMMA_K * 128), p.b_lbo, p.b_sbo);
-                }
-                tc_mma<KIND>(d_tmem, adesc, bdesc, idesc, (first && ks == 0) ? 0u : 1u);
+                const uint64_t adesc = adesc0 + static_cast<uint64_t>((ka * (Cfg::TILE_M * 128) + kk * 32) >> 4);
+                const uint64_t bdesc =
+                    bdesc0 + static_cast<uint64_t>(B_MN ? (((ka * 4 + kk) * (Cfg::UMMA_K * 128)) >> 4)
+                                                        : ((ka * (BLOCK_N * 128) + kk * 32) >> 4));
+                tc_mma<KIND>(d_tmem, adesc, bdesc, idesc, acc);
+              };
+              if (red_left >= Cfg::KRED) {
+#pragma unroll
+                for (int ks = 0; ks < KSTEPS_FULL; ++ks)
+                  issue(ks, (first && ks == 0) ? 0u : 1u);
+              } else {
+                const int ksteps_total = (red_left + Cfg::UMMA_K - 1) / Cfg::UMMA_K;
+                for (int ks = 0; ks < ksteps_total; ++ks)
+                  issue(ks, (first && ks == 0) ? 0u : 1u);
               }
               tc_commit(empty_a(stage));
               CB2_TRACE_EVENT(3, 6, step);  // MMAs issued
