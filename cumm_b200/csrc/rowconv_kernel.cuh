@@ -69,13 +69,17 @@ template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN> struct RowConvCfg {
   static constexpr int STAGING_BYTES = TILE_M * OUT_ROW_BYTES;
   static constexpr int NUM_ACC = 2;
   static constexpr int TMEM_COLS = NUM_ACC * BLOCK_N;     // 128 or 256: power of two >= 32
-  static constexpr int EPI_THREADS = 128;
+  static constexpr int EPI_THREADS = 256;                 // two threads per tile row: each takes half the columns
+  static constexpr int EPI_HALVES = EPI_THREADS / 128;
   static constexpr int GROUP_THREADS = 128;
-  static constexpr int SCHED_WARP = (EPI_THREADS + 64 + SA * GROUP_THREADS) / 32;   // the last warp hands out tiles
-  static constexpr int THREADS = EPI_THREADS + 64 + SA * GROUP_THREADS + 32;  // 608
+  static constexpr int MMA_WARP = EPI_THREADS / 32;
+  static constexpr int TMA_WARP = MMA_WARP + 1;
+  static constexpr int FIRST_GATHER_WARP = TMA_WARP + 1;
+  static constexpr int SCHED_WARP = FIRST_GATHER_WARP + SA * GROUP_THREADS / 32;  // the last warp hands out tiles
+  static constexpr int THREADS = (SCHED_WARP + 1) * 32;   // 544
   static constexpr int RING = 6;                          // tile ring slots
   static constexpr int RING_SLOT_INTS = 264;              // tile, mask, pad; 128 gather rows; 128 output rows
-  static constexpr int RING_CONSUMER_WARPS = 4 + 1 + 1 + SA * 4;
+  static constexpr int RING_CONSUMER_WARPS = SCHED_WARP;   // every warp but the scheduler
   // shared memory map (offsets from a 1024-byte aligned base)
   static constexpr int OFF_A = 0;
   static constexpr int OFF_B = OFF_A + SA * A_STAGE_BYTES;
@@ -378,7 +382,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
       s_bias[i] = (n < p.nn && p.bias) ? p.bias[n] : 0.f;
     }
   }
-  if (warp == 4) {
+  if (warp == Cfg::MMA_WARP) {
     tmem_alloc(sbase + Cfg::OFF_MISC, Cfg::TMEM_COLS);
     tmem_relinquish();
   }
@@ -395,9 +399,12 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
       atomicCAS(p.status, 0, code);
   };
 
-  if (warp < 4) {
+  if (warp < Cfg::MMA_WARP) {
     // ======================= epilogue: TMEM -> registers -> staging -> scattered rows
-    const int et = threadIdx.x;  // 0..127, also the tile row this thread reads from TMEM
+    const int et = threadIdx.x;
+    const int erow = et & 127;   // the tile row this thread reads from TMEM (lane quarter = warp & 3)
+    const int half = et >> 7;    // which share of the columns
+    constexpr int COLS_PER_HALF = BLOCK_N / Cfg::EPI_HALVES;
     uint8_t *staging = smem + Cfg::OFF_STAGING;
     constexpr int CPR = Cfg::OUT_ROW_BYTES / 16;       // 16-byte chunks per output row
     constexpr int SWZ = (CPR >= 8 ? 8 : CPR) - 1;
@@ -406,7 +413,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
     walk_steps(
         p, rv, kpasses,
         [&](int tile, const int *sl, uint32_t kmask_store, bool has_work) -> bool {
-          const int o = (p.mode == kModeMaskConv) ? sl[8 + et] : sl[136 + et];  // destination row of this thread's tile row
+          const int o = (p.mode == kModeMaskConv) ? sl[8 + erow] : sl[136 + erow];  // destination row of this thread's tile row
           if (et == 0 && p.mask_out && blockIdx.y == 0)
             p.mask_out[tile] = kmask_store;
           const int buf = acc_use % Cfg::NUM_ACC;
@@ -423,7 +430,8 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
           named_bar_sync(1, Cfg::EPI_THREADS);  // wait result visible; staging free again
           if (has_work && misc[2] == 0)
             return false;
-          outrow[et] = o;
+          if (half == 0)
+            outrow[erow] = o;
           tc_fence_after();
           const uint32_t trow = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
                                 static_cast<uint32_t>(buf * BLOCK_N);
@@ -431,17 +439,18 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
           // fast path: out = cvt(acc); everything else goes through the general epilogue
           const bool plain = !use_src && p.act_type == 0 && p.alpha == 1.f;
 #pragma unroll 1
-          for (int round = 0; round < BLOCK_N / 32; ++round) {
+          for (int round = 0; round < COLS_PER_HALF / 32; ++round) {
             uint32_t v[32];
+            const int col0 = half * COLS_PER_HALF + round * 32;
             if (has_work) {
-              tmem_ld32(trow + round * 32, v);
+              tmem_ld32(trow + col0, v);
               tmem_ld_wait();
             } else {
 #pragma unroll
               for (int i = 0; i < 32; ++i)
                 v[i] = 0u;
             }
-            const int ncol0 = n0 + round * 32;
+            const int ncol0 = n0 + col0;
             if constexpr (KIND == 0) {
               uint32_t packed[16];
               if (plain) {
@@ -502,9 +511,9 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
               }
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
-                const int c = round * CH_PER_ROUND + q;
-                const int pc = (c & ~SWZ) | ((c ^ et) & SWZ);
-                *reinterpret_cast<uint4 *>(staging + et * Cfg::OUT_ROW_BYTES + pc * 16) =
+                const int c = (col0 / 32) * CH_PER_ROUND + q;
+                const int pc = (c & ~SWZ) | ((c ^ erow) & SWZ);
+                *reinterpret_cast<uint4 *>(staging + erow * Cfg::OUT_ROW_BYTES + pc * 16) =
                     make_uint4(packed[q * 4], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
               }
             } else {
@@ -512,7 +521,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
               float t[32];
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
-                const int col = round * 32 + i;
+                const int col = col0 + i;
                 t[i] = __fmaf_rn(s_scale[col], __int2float_rn(static_cast<int>(v[i])), s_bias[col]);
               }
               if (use_src) {
@@ -545,9 +554,9 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
                                 (cvt_sat_s8(t[i + 3]) << 24);
 #pragma unroll
               for (int q = 0; q < 2; ++q) {
-                const int c = round * CH_PER_ROUND + q;
-                const int pc = (c & ~SWZ) | ((c ^ et) & SWZ);
-                *reinterpret_cast<uint4 *>(staging + et * Cfg::OUT_ROW_BYTES + pc * 16) =
+                const int c = (col0 / 32) * CH_PER_ROUND + q;
+                const int pc = (c & ~SWZ) | ((c ^ erow) & SWZ);
+                *reinterpret_cast<uint4 *>(staging + erow * Cfg::OUT_ROW_BYTES + pc * 16) =
                     make_uint4(packed[q * 4], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
               }
             }
@@ -564,11 +573,11 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
           {
             const int c = et % CPR;
             const int row0 = et / CPR;
-            constexpr int RSTEP = 128 / CPR;
+            constexpr int RSTEP = Cfg::EPI_THREADS / CPR;
             const int ncol = n0 + c * (16 / Cfg::OES);
             if (ncol < p.nn) {
 #pragma unroll 4
-              for (int i = 0; i < CPR; ++i) {
+              for (int i = 0; i < 128 / RSTEP; ++i) {
                 const int row = row0 + i * RSTEP;
                 const int orow = outrow[row];
                 if (orow >= 0) {
@@ -586,7 +595,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
           return true;
         },
         [&](int, int, int, bool, bool) -> bool { return true; });
-  } else if (warp == 4) {
+  } else if (warp == Cfg::MMA_WARP) {
     // ======================= MMA issuer (lane 0 issues; the warp walks together)
     constexpr uint32_t idesc = make_idesc(KIND, false, B_MN, 128, BLOCK_N);
     int step = 0, acc_use = 0, bcount = 0, last_key = -1, cur_slot = 0;
@@ -671,7 +680,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
         fail(kStatusWaitTimeout);
     }
     __syncwarp();
-  } else if (warp == 5) {
+  } else if (warp == Cfg::TMA_WARP) {
     // ======================= weight tiles by TMA (lane 0 issues)
     if (lane == 0)
       tma_prefetch_desc(&tmap_b);
@@ -719,21 +728,29 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
     scheduler_run(p, rv, ntiles, kpasses);
   } else {
     // ======================= operand-row gather: group g owns stage g
-    const int g = (warp - 6) >> 2;                    // 0..2
-    const int gt = threadIdx.x - (6 * 32 + g * Cfg::GROUP_THREADS);  // 0..127
+    constexpr int GT = Cfg::GROUP_THREADS;
+    constexpr int RPT = 128 / GT;                     // tile rows whose index each thread fetches
+    const int g = (warp - Cfg::FIRST_GATHER_WARP) / (GT / 32);  // 0..2
+    const int gt = threadIdx.x - (Cfg::FIRST_GATHER_WARP * 32 + g * GT);
     constexpr int CPR = NATOM_K * 8;                  // 16-byte chunks per operand row
-    constexpr int RSTEP = 128 / CPR;
+    constexpr int RSTEP = GT / CPR;
     const int c = gt % CPR;
     const int row0 = gt / CPR;
     int *group_rowidx = rowidx + g * 256;  // two buffers, alternating per use of the stage
     volatile int *my_flag = misc + 3 + g;
     int step = 0;
-    int o = -1;
+    int o[RPT];
+#pragma unroll
+    for (int r = 0; r < RPT; ++r)
+      o[r] = -1;
     const uint8_t *a_bytes = reinterpret_cast<const uint8_t *>(p.a);
     walk_steps(
         p, rv, kpasses,
         [&](int tile, const int *sl, uint32_t, bool) -> bool {
-          o = sl[8 + gt];  // the row this thread's gather starts from (sort index, or the row itself)
+          // the rows this thread's gathers start from (sort index, or the row itself)
+#pragma unroll
+          for (int r = 0; r < RPT; ++r)
+            o[r] = sl[8 + gt + r * GT];
           return true;
         },
         [&](int tile, int f, int kp, bool, bool) -> bool {
@@ -742,19 +759,25 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
           ++step;
           if (!mine)
             return true;
-          int idx = -1;
-          if (o >= 0) {
-            if (p.mode == kModeMaskConv)
-              idx = __ldg(p.indices + (long long)f * p.n_rows + o);
-            else
-              idx = p.a_inds ? __ldg(p.a_inds + o) : o;
-            if (idx >= p.a_rows) {  // never dereference a row the caller did not provide
-              fail(kStatusBadIndex);
-              idx = -1;
+          int idx[RPT];
+#pragma unroll
+          for (int r = 0; r < RPT; ++r) {
+            idx[r] = -1;
+            if (o[r] >= 0) {
+              if (p.mode == kModeMaskConv)
+                idx[r] = __ldg(p.indices + (long long)f * p.n_rows + o[r]);
+              else
+                idx[r] = p.a_inds ? __ldg(p.a_inds + o[r]) : o[r];
             }
           }
+#pragma unroll
+          for (int r = 0; r < RPT; ++r)
+            if (idx[r] >= p.a_rows) {  // never dereference a row the caller did not provide
+              fail(kStatusBadIndex);
+              idx[r] = -1;
+            }
           if (gt == 0) {
-            CB2_TRACE_EVENT(g, 1, step - 1 + (idx == 0x7fffffff));  // index loaded
+            CB2_TRACE_EVENT(g, 1, step - 1 + (idx[0] == 0x7fffffff));  // index loaded
             bool ok = mbar_wait(empty_a(g), (use & 1) ^ 1, abort_flag);
             CB2_TRACE_EVENT(g, 2, step - 1);  // stage free
             *my_flag = ok ? 1 : 0;
@@ -764,7 +787,9 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
           // Double-buffered: a thread that runs ahead writes the other buffer than the one
           // slower threads of the group may still be reading for the previous use.
           int *my_rowidx = group_rowidx + (use & 1) * 128;
-          my_rowidx[gt] = idx;
+#pragma unroll
+          for (int r = 0; r < RPT; ++r)
+            my_rowidx[gt + r * GT] = idx[r];
           named_bar_sync(2 + g, Cfg::GROUP_THREADS);
           if (*my_flag == 0)
             return false;
@@ -773,7 +798,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
           const bool col_ok = byte_off < p.red * Cfg::ES;
           const uint32_t dst_c = a_stage + (c >> 3) * (Cfg::TILE_M * 128);
 #pragma unroll
-          for (int i = 0; i < CPR; ++i) {
+          for (int i = 0; i < 128 / RSTEP; ++i) {
             const int row = row0 + i * RSTEP;
             const int ridx = my_rowidx[row];
             const uint32_t dst = dst_c + (row >> 3) * 1024 + (row & 7) * 128 + (((c & 7) ^ (row & 7)) << 4);
@@ -797,7 +822,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
   __syncthreads();
   if (threadIdx.x == 0)
     CB2_TRACE_CTA(1, 0);
-  if (warp == 4) {
+  if (warp == Cfg::MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
