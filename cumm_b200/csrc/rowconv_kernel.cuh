@@ -54,6 +54,22 @@ struct RowConvParams {
   uint32_t b_lbo, b_sbo;   // weight-tile descriptor offsets (bytes)
 };
 
+#ifndef CB2_ROWCONV_GROUP_THREADS
+#define CB2_ROWCONV_GROUP_THREADS 128
+#endif
+#ifndef CB2_ROWCONV_RING
+#define CB2_ROWCONV_RING 12
+#endif
+#ifndef CB2_ROWCONV_STEP_BUDGET
+#define CB2_ROWCONV_STEP_BUDGET 12
+#endif
+#ifndef CB2_ROWCONV_DEPTH
+#define CB2_ROWCONV_DEPTH 2
+#endif
+#ifndef CB2_ROWCONV_NUM_ACC
+#define CB2_ROWCONV_NUM_ACC 2
+#endif
+
 template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN> struct RowConvCfg {
   static constexpr int ES = KIND == 0 ? 2 : 1;            // operand element bytes
   static constexpr int OES = KIND == 0 ? 2 : 1;           // output element bytes
@@ -67,17 +83,17 @@ template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN> struct RowConvCfg {
   static constexpr int B_SLOT_BYTES = BLOCK_N * 128 * NATOM_K;
   static constexpr int OUT_ROW_BYTES = BLOCK_N * OES;
   static constexpr int STAGING_BYTES = TILE_M * OUT_ROW_BYTES;
-  static constexpr int NUM_ACC = 2;
+  static constexpr int NUM_ACC = CB2_ROWCONV_NUM_ACC;
   static constexpr int TMEM_COLS = NUM_ACC * BLOCK_N;     // 128 or 256: power of two >= 32
   static constexpr int EPI_THREADS = 256;                 // two threads per tile row: each takes half the columns
   static constexpr int EPI_HALVES = EPI_THREADS / 128;
-  static constexpr int GROUP_THREADS = 128;
+  static constexpr int GROUP_THREADS = CB2_ROWCONV_GROUP_THREADS;
   static constexpr int MMA_WARP = EPI_THREADS / 32;
   static constexpr int TMA_WARP = MMA_WARP + 1;
   static constexpr int FIRST_GATHER_WARP = TMA_WARP + 1;
   static constexpr int SCHED_WARP = FIRST_GATHER_WARP + SA * GROUP_THREADS / 32;  // the last warp hands out tiles
   static constexpr int THREADS = (SCHED_WARP + 1) * 32;   // 544
-  static constexpr int RING = 6;                          // tile ring slots
+  static constexpr int RING = CB2_ROWCONV_RING;                       // tile ring slots
   static constexpr int RING_SLOT_INTS = 264;              // tile, mask, pad; 128 gather rows; 128 output rows
   static constexpr int RING_CONSUMER_WARPS = SCHED_WARP;   // every warp but the scheduler
   // shared memory map (offsets from a 1024-byte aligned base)
@@ -88,8 +104,8 @@ template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN> struct RowConvCfg {
   static constexpr int OFF_OUTROW = OFF_ROWIDX + SA * 2 * 128 * 4;   // 128 ints
   static constexpr int OFF_SCALE = OFF_OUTROW + 128 * 4;             // 2 * BLOCK_N floats
   static constexpr int OFF_RING = OFF_SCALE + 2 * BLOCK_N * 4;       // RING slots
-  static constexpr int OFF_BARS = OFF_RING + RING * RING_SLOT_INTS * 4;  // 16 + 2 * RING mbarriers
-  static constexpr int OFF_MISC = OFF_BARS + (16 + 2 * RING) * 8;                 // tmem ptr, abort, flags
+  static constexpr int OFF_BARS = OFF_RING + RING * RING_SLOT_INTS * 4;  // 20 + 2 * RING mbarriers
+  static constexpr int OFF_MISC = OFF_BARS + (20 + 2 * RING) * 8;                 // tmem ptr, abort, flags
   static constexpr int SMEM_BYTES = OFF_MISC + 64 + 1024;            // + alignment slack
 };
 
@@ -179,8 +195,8 @@ __device__ __forceinline__ void cp_async_4(uint32_t dst, const void *src) {
 }
 
 __device__ __forceinline__ void scheduler_run(const RowConvParams &p, const RingView &rv, int ntiles, int kpasses) {
-  constexpr int DEPTH = 2;       // tiles whose words are in flight besides the one being published
-  constexpr int STEP_BUDGET = 6; // steps a CTA may hold (drawn, not finished) before it stops drawing tiles
+  constexpr int DEPTH = CB2_ROWCONV_DEPTH;     // tiles whose words are in flight besides the one being published
+  constexpr int STEP_BUDGET = CB2_ROWCONV_STEP_BUDGET; // steps a CTA may hold (drawn, not finished) before it stops drawing tiles
   const int lane = (int)lane_id();
   const bool dynamic = p.tickets != nullptr && gridDim.y == 1;
   const bool conv = p.mode == kModeMaskConv;
@@ -265,7 +281,11 @@ __device__ __forceinline__ void scheduler_run(const RowConvParams &p, const Ring
     }
     while (published < issued && (end || issued - published > DEPTH)) {
       const int pending = issued - published - 1;  // younger groups that may stay in flight
-      if (pending >= 2)
+      if (pending >= 4)
+        cp_async_wait<4>();
+      else if (pending == 3)
+        cp_async_wait<3>();
+      else if (pending == 2)
         cp_async_wait<2>();
       else if (pending == 1)
         cp_async_wait<1>();
@@ -337,12 +357,12 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
   auto full_b = [&](int s) { return bars + 8u * (6 + s); };
   auto empty_b = [&](int s) { return bars + 8u * (8 + s); };
   auto acc_full = [&](int s) { return bars + 8u * (10 + s); };
-  auto acc_empty = [&](int s) { return bars + 8u * (12 + s); };
-  const uint32_t final_bar = bars + 8u * 14;
+  auto acc_empty = [&](int s) { return bars + 8u * (14 + s); };
+  const uint32_t final_bar = bars + 8u * 18;
   RingView rv;
   rv.slots = reinterpret_cast<int *>(smem + Cfg::OFF_RING);
-  rv.full0 = bars + 8u * 16;
-  rv.empty0 = bars + 8u * (16 + Cfg::RING);
+  rv.full0 = bars + 8u * 20;
+  rv.empty0 = bars + 8u * (20 + Cfg::RING);
   rv.ring = Cfg::RING;
   rv.slot_ints = Cfg::RING_SLOT_INTS;
   rv.abort_flag = abort_flag;
@@ -729,7 +749,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
   } else {
     // ======================= operand-row gather: group g owns stage g
     constexpr int GT = Cfg::GROUP_THREADS;
-    constexpr int RPT = 128 / GT;                     // tile rows whose index each thread fetches
+    constexpr int RPT = (128 + GT - 1) / GT;                  // tile rows whose index each thread fetches
     const int g = (warp - Cfg::FIRST_GATHER_WARP) / (GT / 32);  // 0..2
     const int gt = threadIdx.x - (Cfg::FIRST_GATHER_WARP * 32 + g * GT);
     constexpr int CPR = NATOM_K * 8;                  // 16-byte chunks per operand row
@@ -750,7 +770,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
           // the rows this thread's gathers start from (sort index, or the row itself)
 #pragma unroll
           for (int r = 0; r < RPT; ++r)
-            o[r] = sl[8 + gt + r * GT];
+            o[r] = (gt + r * GT < 128) ? sl[8 + gt + r * GT] : -1;
           return true;
         },
         [&](int tile, int f, int kp, bool, bool) -> bool {
@@ -789,7 +809,8 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
           int *my_rowidx = group_rowidx + (use & 1) * 128;
 #pragma unroll
           for (int r = 0; r < RPT; ++r)
-            my_rowidx[gt + r * GT] = idx[r];
+            if (gt + r * GT < 128)
+              my_rowidx[gt + r * GT] = idx[r];
           named_bar_sync(2 + g, Cfg::GROUP_THREADS);
           if (*my_flag == 0)
             return false;
@@ -798,8 +819,10 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
           const bool col_ok = byte_off < p.red * Cfg::ES;
           const uint32_t dst_c = a_stage + (c >> 3) * (Cfg::TILE_M * 128);
 #pragma unroll
-          for (int i = 0; i < 128 / RSTEP; ++i) {
+          for (int i = 0; i < (128 + RSTEP - 1) / RSTEP; ++i) {
             const int row = row0 + i * RSTEP;
+            if ((128 % RSTEP) != 0 && row >= 128)
+              break;
             const int ridx = my_rowidx[row];
             const uint32_t dst = dst_c + (row >> 3) * 1024 + (row & 7) * 128 + (((c & 7) ^ (row & 7)) << 4);
             const bool valid = col_ok && ridx >= 0;
