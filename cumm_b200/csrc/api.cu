@@ -146,11 +146,11 @@ int gather_mode() {
   return mode;
 }
 
-template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN>
-int launch_rowconv_inst(const CUtensorMap &map, const RowConvParams &p, int grid_x, int grid_y,
-                        cudaStream_t stream) {
-  using Cfg = RowConvCfg<KIND, NATOM_K, BLOCK_N, B_MN>;
-  auto kern = rowconv_kernel<KIND, NATOM_K, BLOCK_N, B_MN>;
+template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN, bool TMA_GATHER>
+int launch_rowconv_inst(const CUtensorMap &map, const CUtensorMap &map_a, const RowConvParams &p, int grid_x,
+                        int grid_y, cudaStream_t stream) {
+  using Cfg = RowConvCfg<KIND, NATOM_K, BLOCK_N, B_MN, TMA_GATHER>;
+  auto kern = rowconv_kernel<KIND, NATOM_K, BLOCK_N, B_MN, TMA_GATHER>;
   static std::atomic<uint64_t> configured{0};  // bit per device
   int dev = 0;
   CB2_CUDA(cudaGetDevice(&dev));
@@ -158,7 +158,7 @@ int launch_rowconv_inst(const CUtensorMap &map, const RowConvParams &p, int grid
     CB2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     configured.fetch_or(1ull << dev);
   }
-  kern<<<dim3(grid_x, grid_y), Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(map, p);
+  kern<<<dim3(grid_x, grid_y), Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(map, map_a, p);
   CB2_CUDA(cudaGetLastError());
   g_launches.fetch_add(1);
   return CB2_OK;
@@ -183,11 +183,12 @@ int plan_rowconv(int kind, int red, int nn, bool b_mn, RowConvPlan *plan) {
   return CB2_OK;
 }
 
-int launch_rowconv(const RowConvPlan &pl, const CUtensorMap &map, const RowConvParams &p, int gx, int gy,
-                   cudaStream_t s) {
+int launch_rowconv(const RowConvPlan &pl, const CUtensorMap &map, const CUtensorMap &map_a, bool tma_gather,
+                   const RowConvParams &p, int gx, int gy, cudaStream_t s) {
 #define CB2_INST(K, A, N, M)                                                                      \
   if (pl.kind == K && pl.natom_k == A && pl.block_n == N && pl.b_mn == M)                          \
-    return launch_rowconv_inst<K, A, N, M>(map, p, gx, gy, s);
+    return tma_gather ? launch_rowconv_inst<K, A, N, M, true>(map, map_a, p, gx, gy, s)            \
+                      : launch_rowconv_inst<K, A, N, M, false>(map, map_a, p, gx, gy, s);
   CB2_INST(0, 1, 64, false)
   CB2_INST(0, 1, 128, false)
   CB2_INST(0, 2, 64, false)
@@ -228,6 +229,15 @@ int run_rowconv(DeviceState *dev, RowConvParams &p, int kind, bool b_mn, const v
                        b_mn ? kred : pl.block_n);
   if (rc)
     return rc;
+  // operand rows through the copy engine unless the 16-byte cp.async path is asked for
+  const bool tma_gather = gather_mode() != 0;
+  CUtensorMap map_a;
+  memset(&map_a, 0, sizeof(map_a));
+  if (tma_gather) {
+    rc = make_rows_map(&map_a, p.a, es, p.red, p.a_rows, p.lda);
+    if (rc)
+      return rc;
+  }
   p.b_lbo = static_cast<uint32_t>(kred * 128);
   p.b_sbo = 1024;
   if (const char *v = getenv("CUMM_B200_DEBUG_SWAP_BDESC")) {
@@ -251,7 +261,7 @@ int run_rowconv(DeviceState *dev, RowConvParams &p, int kind, bool b_mn, const v
     gx = 1;
   if (gx > ntiles)
     gx = ntiles;
-  return launch_rowconv(pl, map, p, gx, gy, stream);
+  return launch_rowconv(pl, map, map_a, tma_gather, p, gx, gy, stream);
 }
 
 // ---------------------------------------------------------------- weight gradient

@@ -22,11 +22,17 @@ struct TraceBuf {
   unsigned long long ev[8][512][2];  // [role][event][time, (code << 32) | step]
   int count[8];
   unsigned long long cta[256][3];    // per CTA: start time, end time, steps
+  long long prof[256][12];           // per CTA: clock cycles the MMA warp spent per phase
 };
 __device__ TraceBuf g_trace;
-__device__ int g_trace_cta = 0;  // the CTA whose events are recorded
+// 1 in the CTA whose events are recorded (a shared-memory flag: testing it must cost next to
+// nothing in the CTAs that are not recorded)
+__device__ __forceinline__ volatile int &trace_on() {
+  __shared__ int v;
+  return v;
+}
 __device__ __forceinline__ void trace_event(int role, int code, int step) {
-  if ((int)blockIdx.x != *(volatile int *)&g_trace_cta || blockIdx.y != 0)
+  if (!trace_on() || blockIdx.y != 0)
     return;
   int n = g_trace.count[role];
   if (n >= 512)
@@ -45,11 +51,23 @@ __device__ __forceinline__ void trace_cta(int which, unsigned long long value) {
   }
   g_trace.cta[blockIdx.x][which] = value;
 }
-#define CB2_TRACE_EVENT(role, code, step) ::cb2::trace_event(role, code, step)
-#define CB2_TRACE_CTA(which, value) ::cb2::trace_cta(which, value)
+#ifdef CB2_PROF_ONLY
+#define CB2_TRACE_EVENT(role, code, step) ((void)0)
 #else
+#define CB2_TRACE_EVENT(role, code, step) ::cb2::trace_event(role, code, step)
+#endif
+#define CB2_TRACE_CTA(which, value) ::cb2::trace_cta(which, value)
+#define CB2_TRACE_SELECT(on) (::cb2::trace_on() = (on))
+#define CB2_PROF_BEGIN() long long prof_c[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; long long prof_prev = clock64()
+#define CB2_PROF_MARK(i) do { long long prof_t = clock64(); prof_c[i] += prof_t - prof_prev; prof_prev = prof_t; } while (0)
+#define CB2_PROF_END() do { for (int i = 0; i < 12; ++i) ::cb2::g_trace.prof[blockIdx.x & 255][i] = prof_c[i]; } while (0)
+#else
+#define CB2_PROF_BEGIN() ((void)0)
+#define CB2_PROF_MARK(i) ((void)0)
+#define CB2_PROF_END() ((void)0)
 #define CB2_TRACE_EVENT(role, code, step) ((void)0)
 #define CB2_TRACE_CTA(which, value) ((void)0)
+#define CB2_TRACE_SELECT(on) ((void)0)
 #endif
 
 // ---------------------------------------------------------------- mbarrier

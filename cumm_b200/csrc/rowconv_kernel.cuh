@@ -66,11 +66,17 @@ struct RowConvParams {
 #ifndef CB2_ROWCONV_DEPTH
 #define CB2_ROWCONV_DEPTH 2
 #endif
+#ifndef CB2_ROWCONV_TICKET_BATCH
+#define CB2_ROWCONV_TICKET_BATCH 4
+#endif
 #ifndef CB2_ROWCONV_NUM_ACC
 #define CB2_ROWCONV_NUM_ACC 2
 #endif
 
-template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN> struct RowConvCfg {
+// TMA_GATHER: operand rows are fetched by the TMA unit (tile::gather4, four rows per request,
+// one warp per group) instead of 16-byte cp.async issued by 128 threads per group.  The copy
+// engine path keeps the load/store queues of the SM free for the other roles.
+template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN, bool TMA_GATHER> struct RowConvCfg {
   static constexpr int ES = KIND == 0 ? 2 : 1;            // operand element bytes
   static constexpr int OES = KIND == 0 ? 2 : 1;           // output element bytes
   static constexpr int ATOM_ELEMS = 128 / ES;             // elements per 128-byte swizzle row
@@ -87,7 +93,8 @@ template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN> struct RowConvCfg {
   static constexpr int TMEM_COLS = NUM_ACC * BLOCK_N;     // 128 or 256: power of two >= 32
   static constexpr int EPI_THREADS = 256;                 // two threads per tile row: each takes half the columns
   static constexpr int EPI_HALVES = EPI_THREADS / 128;
-  static constexpr int GROUP_THREADS = CB2_ROWCONV_GROUP_THREADS;
+  static constexpr int GROUP_THREADS = TMA_GATHER ? 32 : CB2_ROWCONV_GROUP_THREADS;
+  static constexpr int FULL_A_COUNT = TMA_GATHER ? 1 : GROUP_THREADS;
   static constexpr int MMA_WARP = EPI_THREADS / 32;
   static constexpr int TMA_WARP = MMA_WARP + 1;
   static constexpr int FIRST_GATHER_WARP = TMA_WARP + 1;
@@ -148,11 +155,26 @@ struct RingView {
 // the identical walk, so their step counters agree.  All 32 lanes take part.
 template <class TileFn, class StepFn>
 __device__ __forceinline__ bool walk_steps(const RowConvParams &p, const RingView &rv, int kpasses, TileFn on_tile,
-                                           StepFn on_step) {
+                                           StepFn on_step, long long *prof_c = nullptr,
+                                           long long *prof_prev_p = nullptr) {
+#ifdef CB2_TRACE
+#define CB2_WALK_MARK(i)                                                                                  \
+  do {                                                                                                    \
+    if (prof_c && lane_id() == 0) {                                                                       \
+      long long t = clock64();                                                                            \
+      prof_c[i] += t - *prof_prev_p;                                                                      \
+      *prof_prev_p = t;                                                                                   \
+    }                                                                                                     \
+  } while (0)
+#else
+#define CB2_WALK_MARK(i) ((void)0)
+#endif
   for (int seq = 0;; ++seq) {
     const int si = seq % rv.ring;
+    CB2_WALK_MARK(8);  // previous slot released
     if (!mbar_wait_warp(rv.full0 + 8u * si, (seq / rv.ring) & 1, rv.abort_flag))
       return false;
+    CB2_WALK_MARK(9);  // slot published
     const int *sl = rv.slot(si);
     const int tile = sl[0];
     uint32_t kmask = static_cast<uint32_t>(sl[1]);
@@ -174,6 +196,7 @@ __device__ __forceinline__ bool walk_steps(const RowConvParams &p, const RingVie
         }
       }
     }
+    CB2_WALK_MARK(10);  // steps done
     __syncwarp();
     if (lane_id() == 0)
       mbar_arrive(rv.empty0 + 8u * si);
@@ -201,13 +224,32 @@ __device__ __forceinline__ void scheduler_run(const RowConvParams &p, const Ring
   const bool dynamic = p.tickets != nullptr && gridDim.y == 1;
   const bool conv = p.mode == kModeMaskConv;
   int drawn = 0;
+  // Tickets come in batches and the next batch is requested before the current one is used up:
+  // the counter's round trip through L2 (a microsecond and more while the gathers saturate the
+  // memory system) would otherwise be paid per tile, and the whole CTA waits on this warp.
+  // Batches shrink to one ticket as the counter nears the end so the tail stays balanced.
+  constexpr int MAX_BATCH = CB2_ROWCONV_TICKET_BATCH;
+  int cur_base = 0, cur_left = 0, next_base = 0, next_cnt = 0;
+  auto request = [&](int seen) {
+    int b = (ntiles - seen) / ((int)gridDim.x * 4);
+    next_cnt = b < 1 ? 1 : (b > MAX_BATCH ? MAX_BATCH : b);
+    if (lane == 0)
+      next_base = atomicAdd(p.tickets, next_cnt);
+  };
+  if (dynamic)
+    request(0);
   auto draw = [&]() -> int {
     int t;
     if (dynamic) {
-      t = 0;
-      if (lane == 0)
-        t = atomicAdd(p.tickets, 1);
-      t = __shfl_sync(0xffffffffu, t, 0);
+      if (cur_left == 0) {
+        cur_base = __shfl_sync(0xffffffffu, next_base, 0);
+        cur_left = next_cnt;
+        next_cnt = 0;
+        if (cur_base < ntiles)
+          request(cur_base);
+      }
+      t = cur_base++;
+      --cur_left;
     } else {
       t = blockIdx.x + drawn * gridDim.x;
     }
@@ -243,10 +285,8 @@ __device__ __forceinline__ void scheduler_run(const RowConvParams &p, const Ring
         return;
       account_released();  // before the slot's step count is overwritten
       const int ticket = draw();
-#ifdef CB2_TRACE
       if (ticket == 0 && lane == 0)
-        g_trace_cta = blockIdx.x;  // follow the CTA that got the heaviest tile
-#endif
+        CB2_TRACE_SELECT(1);  // follow the CTA that got the heaviest tile
       held_steps += 1;
       int tile = -1;
       if (ticket < ntiles)
@@ -276,6 +316,8 @@ __device__ __forceinline__ void scheduler_run(const RowConvParams &p, const Ring
         }
       }
       cp_async_commit();
+      if (lane == 0)
+        CB2_TRACE_EVENT(6, 16, tile);  // tile drawn, fetch issued
       ++issued;
       end = tile < 0;
     }
@@ -308,6 +350,7 @@ __device__ __forceinline__ void scheduler_run(const RowConvParams &p, const Ring
       if (lane == 0) {
         sl[1] = static_cast<int>(kmask);
         sl[2] = nsteps;
+        CB2_TRACE_EVENT(6, 14, sl[0]);  // tile published
       }
       __syncwarp();
       if (lane == 0)
@@ -319,6 +362,9 @@ __device__ __forceinline__ void scheduler_run(const RowConvParams &p, const Ring
   }
   // the last CTA to run out of tiles puts the two counters back to zero for the next launch
   if (dynamic && lane == 0) {
+    if (next_cnt != 0)  // an outstanding request must have been served before the counters may be reset
+      asm volatile("" ::"r"(next_base) : "memory");
+    __threadfence();
     const int done = atomicAdd(p.tickets + 1, 1);
     if (done == (int)(gridDim.x * gridDim.y) - 1) {
       p.tickets[0] = 0;
@@ -328,15 +374,14 @@ __device__ __forceinline__ void scheduler_run(const RowConvParams &p, const Ring
   }
 }
 
-template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN>
-__global__ void __launch_bounds__(RowConvCfg<KIND, NATOM_K, BLOCK_N, B_MN>::THREADS, 1)
-rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p) {
-  using Cfg = RowConvCfg<KIND, NATOM_K, BLOCK_N, B_MN>;
+template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN, bool TMA_GATHER>
+__global__ void __launch_bounds__(RowConvCfg<KIND, NATOM_K, BLOCK_N, B_MN, TMA_GATHER>::THREADS, 1)
+rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_a,
+               const RowConvParams p) {
+  using Cfg = RowConvCfg<KIND, NATOM_K, BLOCK_N, B_MN, TMA_GATHER>;
   extern __shared__ uint8_t smem_raw[];
-  if (threadIdx.x == 0) {
-    CB2_TRACE_EVENT(5, 10, 0);  // kernel entered
+  if (threadIdx.x == 0)
     CB2_TRACE_CTA(0, 0);
-  }
   // 1024-byte alignment: required by the 128-byte swizzle atoms of TMA and tcgen05.
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -375,7 +420,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::SA; ++s) {
-      mbar_init(full_a(s), Cfg::GROUP_THREADS);
+      mbar_init(full_a(s), Cfg::FULL_A_COUNT);
       mbar_init(empty_a(s), 1);
     }
     for (int s = 0; s < Cfg::SB; ++s) {
@@ -394,6 +439,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
     mbar_init_fence();
     misc[1] = 0;
     misc[2] = misc[3] = misc[4] = misc[5] = 1;
+    CB2_TRACE_SELECT(0);
   }
   if (KIND == 1) {
     for (int i = threadIdx.x; i < BLOCK_N; i += blockDim.x) {
@@ -623,14 +669,22 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
     const uint64_t adesc_base = make_smem_desc(sbase + Cfg::OFF_A, 16, 1024);
     const uint64_t bdesc_base = B_MN ? make_smem_desc(sbase + Cfg::OFF_B, p.b_lbo, p.b_sbo)
                                      : make_smem_desc(sbase + Cfg::OFF_B, 16, 1024);
+    CB2_PROF_BEGIN();
     walk_steps(
-        p, rv, kpasses, [&](int, const int *, uint32_t, bool) -> bool { return true; },
+        p, rv, kpasses,
+        [&](int, const int *, uint32_t, bool) -> bool {
+          if (lane == 0)
+            CB2_PROF_MARK(7);  // previous slot released, this tile's slot read
+          return true;
+        },
         [&](int tile, int f, int kp, bool first, bool last) -> bool {
           const int buf = acc_use % Cfg::NUM_ACC;
           int ok = 1;
           if (lane == 0) {
+            CB2_PROF_MARK(0);  // the walk between steps
             if (first)
               ok = mbar_wait(acc_empty(buf), ((acc_use / Cfg::NUM_ACC) & 1) ^ 1, abort_flag);
+            CB2_PROF_MARK(1);  // accumulator free
             const int key = f * kpasses + kp;
             if (ok && key != last_key) {
               if (bcount > 0)
@@ -641,13 +695,17 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
               last_key = key;
             }
             const int stage = step % Cfg::SA;
+            CB2_PROF_MARK(2);  // weight tile present
             CB2_TRACE_EVENT(3, 4, step);  // waiting for rows
             if (ok)
               ok = mbar_wait(full_a(stage), (step / Cfg::SA) & 1, abort_flag);
             CB2_TRACE_EVENT(3, 5, step);  // rows landed
+            CB2_PROF_MARK(3);  // rows present
             if (ok) {
-              fence_proxy_async_smem();  // gathered rows were written through the generic proxy
+              if constexpr (!TMA_GATHER)
+                fence_proxy_async_smem();  // gathered rows were written through the generic proxy
               tc_fence_after();
+              CB2_PROF_MARK(4);  // fences
               // Descriptors differ from the stage's / slot's base descriptor only in the start
               // address field (bits 0-13, units of 16 bytes), so each one is an add.  This loop is
               // issued by a single thread: every instruction saved here shortens each step.
@@ -673,10 +731,12 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
                 for (int ks = 0; ks < ksteps_total; ++ks)
                   issue(ks, (first && ks == 0) ? 0u : 1u);
               }
+              CB2_PROF_MARK(5);  // MMAs issued
               tc_commit(empty_a(stage));
               CB2_TRACE_EVENT(3, 6, step);  // MMAs issued
               if (last)
                 tc_commit(acc_full(buf));
+              CB2_PROF_MARK(6);  // commits
             }
           }
           ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -690,9 +750,15 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
             return false;
           }
           return true;
-        });
-    if (lane == 0)
+        }
+#ifdef CB2_TRACE
+        , prof_c, &prof_prev
+#endif
+        );
+    if (lane == 0) {
       CB2_TRACE_CTA(2, (unsigned long long)step);
+      CB2_PROF_END();
+    }
     // make sure every MMA has retired before TMEM is released
     if (lane == 0 && ok_all) {
       tc_commit(final_bar);
@@ -748,96 +814,157 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowConvParams p
     scheduler_run(p, rv, ntiles, kpasses);
   } else {
     // ======================= operand-row gather: group g owns stage g
-    constexpr int GT = Cfg::GROUP_THREADS;
-    constexpr int RPT = (128 + GT - 1) / GT;                  // tile rows whose index each thread fetches
-    const int g = (warp - Cfg::FIRST_GATHER_WARP) / (GT / 32);  // 0..2
-    const int gt = threadIdx.x - (Cfg::FIRST_GATHER_WARP * 32 + g * GT);
-    constexpr int CPR = NATOM_K * 8;                  // 16-byte chunks per operand row
-    constexpr int RSTEP = GT / CPR;
-    const int c = gt % CPR;
-    const int row0 = gt / CPR;
-    int *group_rowidx = rowidx + g * 256;  // two buffers, alternating per use of the stage
-    volatile int *my_flag = misc + 3 + g;
-    int step = 0;
-    int o[RPT];
-#pragma unroll
-    for (int r = 0; r < RPT; ++r)
-      o[r] = -1;
-    const uint8_t *a_bytes = reinterpret_cast<const uint8_t *>(p.a);
-    walk_steps(
-        p, rv, kpasses,
-        [&](int tile, const int *sl, uint32_t, bool) -> bool {
-          // the rows this thread's gathers start from (sort index, or the row itself)
-#pragma unroll
-          for (int r = 0; r < RPT; ++r)
-            o[r] = (gt + r * GT < 128) ? sl[8 + gt + r * GT] : -1;
-          return true;
-        },
-        [&](int tile, int f, int kp, bool, bool) -> bool {
-          const bool mine = (step % Cfg::SA) == g;
-          const int use = step / Cfg::SA;
-          ++step;
-          if (!mine)
+    if constexpr (TMA_GATHER) {
+      // one warp per group; lane L fetches tile rows 4L .. 4L+3 with one request per 128-byte
+      // column block; a row index of -1 lies outside the tensor and reads as zeros
+      const int g = warp - Cfg::FIRST_GATHER_WARP;
+      if (lane == 0)
+        tma_prefetch_desc(&tmap_a);
+      int step = 0;
+      int o[4] = {-1, -1, -1, -1};
+      walk_steps(
+          p, rv, kpasses,
+          [&](int tile, const int *sl, uint32_t, bool) -> bool {
+            const int4 v = *reinterpret_cast<const int4 *>(sl + 8 + lane * 4);
+            o[0] = v.x, o[1] = v.y, o[2] = v.z, o[3] = v.w;
             return true;
-          int idx[RPT];
+          },
+          [&](int tile, int f, int kp, bool, bool) -> bool {
+            const bool mine = (step % Cfg::SA) == g;
+            const int use = step / Cfg::SA;
+            ++step;
+            if (!mine)
+              return true;
+            int idx[4];
 #pragma unroll
-          for (int r = 0; r < RPT; ++r) {
-            idx[r] = -1;
-            if (o[r] >= 0) {
-              if (p.mode == kModeMaskConv)
-                idx[r] = __ldg(p.indices + (long long)f * p.n_rows + o[r]);
-              else
-                idx[r] = p.a_inds ? __ldg(p.a_inds + o[r]) : o[r];
-            }
-          }
-#pragma unroll
-          for (int r = 0; r < RPT; ++r)
-            if (idx[r] >= p.a_rows) {  // never dereference a row the caller did not provide
-              fail(kStatusBadIndex);
+            for (int r = 0; r < 4; ++r) {
               idx[r] = -1;
+              if (o[r] >= 0) {
+                if (p.mode == kModeMaskConv)
+                  idx[r] = __ldg(p.indices + (long long)f * p.n_rows + o[r]);
+                else
+                  idx[r] = p.a_inds ? __ldg(p.a_inds + o[r]) : o[r];
+              }
             }
-          if (gt == 0) {
-            CB2_TRACE_EVENT(g, 1, step - 1 + (idx[0] == 0x7fffffff));  // index loaded
-            bool ok = mbar_wait(empty_a(g), (use & 1) ^ 1, abort_flag);
-            CB2_TRACE_EVENT(g, 2, step - 1);  // stage free
-            *my_flag = ok ? 1 : 0;
-            if (!ok)
-              fail(kStatusWaitTimeout);
-          }
-          // Double-buffered: a thread that runs ahead writes the other buffer than the one
-          // slower threads of the group may still be reading for the previous use.
-          int *my_rowidx = group_rowidx + (use & 1) * 128;
 #pragma unroll
-          for (int r = 0; r < RPT; ++r)
-            if (gt + r * GT < 128)
-              my_rowidx[gt + r * GT] = idx[r];
-          named_bar_sync(2 + g, Cfg::GROUP_THREADS);
-          if (*my_flag == 0)
-            return false;
-          const uint32_t a_stage = sbase + Cfg::OFF_A + g * Cfg::A_STAGE_BYTES;
-          const int byte_off = kp * Cfg::KRED * Cfg::ES + c * 16;
-          const bool col_ok = byte_off < p.red * Cfg::ES;
-          const uint32_t dst_c = a_stage + (c >> 3) * (Cfg::TILE_M * 128);
+            for (int r = 0; r < 4; ++r)
+              if (idx[r] >= p.a_rows) {  // reported; the copy engine would read such a row as zeros
+                fail(kStatusBadIndex);
+                idx[r] = -1;
+              }
+            if (lane == 0)
+              CB2_TRACE_EVENT(g, 1, step - 1 + (idx[0] == 0x7fffffff));  // index loaded
+            if (!mbar_wait_warp(empty_a(g), (use & 1) ^ 1, abort_flag)) {
+              if (lane == 0)
+                fail(kStatusWaitTimeout);
+              return false;
+            }
+            if (lane == 0) {
+              CB2_TRACE_EVENT(g, 2, step - 1);  // stage free
+              mbar_arrive_expect_tx(full_a(g), Cfg::A_STAGE_BYTES);
+            }
+            __syncwarp();
+            const uint32_t dst = sbase + Cfg::OFF_A + g * Cfg::A_STAGE_BYTES + lane * (4 * 128);
 #pragma unroll
-          for (int i = 0; i < (128 + RSTEP - 1) / RSTEP; ++i) {
-            const int row = row0 + i * RSTEP;
-            if ((128 % RSTEP) != 0 && row >= 128)
-              break;
-            const int ridx = my_rowidx[row];
-            const uint32_t dst = dst_c + (row >> 3) * 1024 + (row & 7) * 128 + (((c & 7) ^ (row & 7)) << 4);
-            const bool valid = col_ok && ridx >= 0;
-            const uint8_t *srcp = valid ? a_bytes + ((long long)ridx * p.lda) * Cfg::ES + byte_off : a_bytes;
-            cp_async_16(dst, srcp, valid ? 16u : 0u);
-          }
-          // The barrier is signalled by the copy engine when this thread's copies have landed;
-          // the thread itself runs on to its next step.  The consumer makes the data visible
-          // to the tensor core with a proxy fence after its wait.
-          cp_async_mbar_arrive_noinc(full_a(g));
-          if (gt == 0)
-            CB2_TRACE_EVENT(g, 3, step - 1);  // copies issued
-          return true;
-        });
-    cp_async_wait_all();
+            for (int ka = 0; ka < NATOM_K; ++ka)
+              tma_gather4(dst + ka * (Cfg::TILE_M * 128), &tmap_a, full_a(g), kp * Cfg::KRED + ka * Cfg::ATOM_ELEMS,
+                          idx[0], idx[1], idx[2], idx[3]);
+            if (lane == 0)
+              CB2_TRACE_EVENT(g, 3, step - 1);  // copies issued
+            return true;
+          });
+    } else {
+      constexpr int GT = Cfg::GROUP_THREADS;
+      constexpr int RPT = (128 + GT - 1) / GT;                  // tile rows whose index each thread fetches
+      const int g = (warp - Cfg::FIRST_GATHER_WARP) / (GT / 32);  // 0..2
+      const int gt = threadIdx.x - (Cfg::FIRST_GATHER_WARP * 32 + g * GT);
+      constexpr int CPR = NATOM_K * 8;                  // 16-byte chunks per operand row
+      constexpr int RSTEP = GT / CPR;
+      const int c = gt % CPR;
+      const int row0 = gt / CPR;
+      int *group_rowidx = rowidx + g * 256;  // two buffers, alternating per use of the stage
+      volatile int *my_flag = misc + 3 + g;
+      int step = 0;
+      int o[RPT];
+#pragma unroll
+      for (int r = 0; r < RPT; ++r)
+        o[r] = -1;
+      const uint8_t *a_bytes = reinterpret_cast<const uint8_t *>(p.a);
+      walk_steps(
+          p, rv, kpasses,
+          [&](int tile, const int *sl, uint32_t, bool) -> bool {
+            // the rows this thread's gathers start from (sort index, or the row itself)
+#pragma unroll
+            for (int r = 0; r < RPT; ++r)
+              o[r] = (gt + r * GT < 128) ? sl[8 + gt + r * GT] : -1;
+            return true;
+          },
+          [&](int tile, int f, int kp, bool, bool) -> bool {
+            const bool mine = (step % Cfg::SA) == g;
+            const int use = step / Cfg::SA;
+            ++step;
+            if (!mine)
+              return true;
+            int idx[RPT];
+#pragma unroll
+            for (int r = 0; r < RPT; ++r) {
+              idx[r] = -1;
+              if (o[r] >= 0) {
+                if (p.mode == kModeMaskConv)
+                  idx[r] = __ldg(p.indices + (long long)f * p.n_rows + o[r]);
+                else
+                  idx[r] = p.a_inds ? __ldg(p.a_inds + o[r]) : o[r];
+              }
+            }
+#pragma unroll
+            for (int r = 0; r < RPT; ++r)
+              if (idx[r] >= p.a_rows) {  // never dereference a row the caller did not provide
+                fail(kStatusBadIndex);
+                idx[r] = -1;
+              }
+            if (gt == 0) {
+              CB2_TRACE_EVENT(g, 1, step - 1 + (idx[0] == 0x7fffffff));  // index loaded
+              bool ok = mbar_wait(empty_a(g), (use & 1) ^ 1, abort_flag);
+              CB2_TRACE_EVENT(g, 2, step - 1);  // stage free
+              *my_flag = ok ? 1 : 0;
+              if (!ok)
+                fail(kStatusWaitTimeout);
+            }
+            // Double-buffered: a thread that runs ahead writes the other buffer than the one
+            // slower threads of the group may still be reading for the previous use.
+            int *my_rowidx = group_rowidx + (use & 1) * 128;
+#pragma unroll
+            for (int r = 0; r < RPT; ++r)
+              if (gt + r * GT < 128)
+                my_rowidx[gt + r * GT] = idx[r];
+            named_bar_sync(2 + g, Cfg::GROUP_THREADS);
+            if (*my_flag == 0)
+              return false;
+            const uint32_t a_stage = sbase + Cfg::OFF_A + g * Cfg::A_STAGE_BYTES;
+            const int byte_off = kp * Cfg::KRED * Cfg::ES + c * 16;
+            const bool col_ok = byte_off < p.red * Cfg::ES;
+            const uint32_t dst_c = a_stage + (c >> 3) * (Cfg::TILE_M * 128);
+#pragma unroll
+            for (int i = 0; i < (128 + RSTEP - 1) / RSTEP; ++i) {
+              const int row = row0 + i * RSTEP;
+              if ((128 % RSTEP) != 0 && row >= 128)
+                break;
+              const int ridx = my_rowidx[row];
+              const uint32_t dst = dst_c + (row >> 3) * 1024 + (row & 7) * 128 + (((c & 7) ^ (row & 7)) << 4);
+              const bool valid = col_ok && ridx >= 0;
+              const uint8_t *srcp = valid ? a_bytes + ((long long)ridx * p.lda) * Cfg::ES + byte_off : a_bytes;
+              cp_async_16(dst, srcp, valid ? 16u : 0u);
+            }
+            // The barrier is signalled by the copy engine when this thread's copies have landed;
+            // the thread itself runs on to its next step.  The consumer makes the data visible
+            // to the tensor core with a proxy fence after its wait.
+            cp_async_mbar_arrive_noinc(full_a(g));
+            if (gt == 0)
+              CB2_TRACE_EVENT(g, 3, step - 1);  // copies issued
+            return true;
+          });
+      cp_async_wait_all();
+    }
   }
 
   // ---------------------------------------------------------------- teardown

@@ -318,6 +318,7 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
     mbar_init_fence();
     misc[1] = 0;
     misc[2] = misc[3] = misc[4] = misc[5] = 1;
+    CB2_TRACE_SELECT(blockIdx.x == 0);
   }
   if (warp == 4) {
     tmem_alloc(sbase + Cfg::OFF_MISC, Cfg::TMEM_COLS);
