@@ -229,8 +229,11 @@ int run_rowconv(DeviceState *dev, RowConvParams &p, int kind, bool b_mn, const v
                        b_mn ? kred : pl.block_n);
   if (rc)
     return rc;
-  // operand rows through the copy engine unless the 16-byte cp.async path is asked for
-  const bool tma_gather = gather_mode() != 0;
+  // Operand rows of up to 128 bytes go through the copy engine (one tile::gather4 request per
+  // four rows); wider rows need a request per 128-byte column block, at which point the copy
+  // engine's request rate, not memory, bounds a step, and 16-byte cp.async is faster.
+  // CUMM_B200_GATHER forces one path for every width.
+  const bool tma_gather = getenv("CUMM_B200_GATHER") ? gather_mode() != 0 : pl.natom_k == 1;
   CUtensorMap map_a;
   memset(&map_a, 0, sizeof(map_a));
   if (tma_gather) {

@@ -63,9 +63,6 @@ struct RowConvParams {
 #ifndef CB2_ROWCONV_STEP_BUDGET
 #define CB2_ROWCONV_STEP_BUDGET 12
 #endif
-#ifndef CB2_ROWCONV_DEPTH
-#define CB2_ROWCONV_DEPTH 2
-#endif
 #ifndef CB2_ROWCONV_TICKET_BATCH
 #define CB2_ROWCONV_TICKET_BATCH 4
 #endif
@@ -111,8 +108,8 @@ template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN, bool TMA_GATHER> struct
   static constexpr int OFF_OUTROW = OFF_ROWIDX + SA * 2 * 128 * 4;   // 128 ints
   static constexpr int OFF_SCALE = OFF_OUTROW + 128 * 4;             // 2 * BLOCK_N floats
   static constexpr int OFF_RING = OFF_SCALE + 2 * BLOCK_N * 4;       // RING slots
-  static constexpr int OFF_BARS = OFF_RING + RING * RING_SLOT_INTS * 4;  // 20 + 2 * RING mbarriers
-  static constexpr int OFF_MISC = OFF_BARS + (20 + 2 * RING) * 8;                 // tmem ptr, abort, flags
+  static constexpr int OFF_BARS = OFF_RING + RING * RING_SLOT_INTS * 4;  // 20 + 3 * RING mbarriers
+  static constexpr int OFF_MISC = OFF_BARS + (20 + 3 * RING) * 8;                 // tmem ptr, abort, flags
   static constexpr int SMEM_BYTES = OFF_MISC + 64 + 1024;            // + alignment slack
 };
 
@@ -143,11 +140,26 @@ __device__ __forceinline__ uint32_t cvt_sat_s8(float t) {
 // the sorted order first because those carry the most offsets.
 struct RingView {
   int *slots;
-  uint32_t full0, empty0;  // addresses of the first "filled" / "released" barrier
+  uint32_t full0, empty0;  // addresses of the first "published" / "released" barrier
+  uint32_t landed0;        // first "copies landed" barrier (scheduler only)
   int ring, slot_ints;
   volatile int *abort_flag;
   __device__ __forceinline__ int *slot(int i) const { return slots + i * slot_ints; }
 };
+
+// OR of the neighbour masks of a tile's rows, from the raw mask words of its ring slot
+// (warp-collective).
+__device__ __forceinline__ uint32_t ring_tile_mask(const RowConvParams &p, const int *sl, int tile) {
+  if (tile < 0 || p.mode != kModeMaskConv)
+    return 1u;
+  const int lane = (int)lane_id();
+  const uint32_t m = static_cast<uint32_t>(sl[136 + lane]) | static_cast<uint32_t>(sl[136 + 32 + lane]) |
+                     static_cast<uint32_t>(sl[136 + 64 + lane]) | static_cast<uint32_t>(sl[136 + 96 + lane]);
+  uint32_t kmask = __reduce_or_sync(0xffffffffu, m) & p.mask_filter;
+  if (p.kv < 32)
+    kmask &= (1u << p.kv) - 1u;
+  return kmask;
+}
 
 // Walks the tiles the scheduler publishes and, inside each, the (filter offset, reduction
 // pass) steps.  on_tile(tile, slot, kmask_for_store, has_work) -> bool; on_step(tile, f, kp,
@@ -207,27 +219,26 @@ __device__ __forceinline__ bool walk_steps(const RowConvParams &p, const RingVie
   }
 }
 
-// The scheduler warp: draws tiles, fetches their mask words and row numbers straight into
-// the ring slot with 4-byte cp.async (no registers involved, so several tiles can be in
-// flight and a slot is published when ITS copies have landed), then publishes the slot.
-// Slot layout (ints): [0] tile (-1 = no more tiles), [1] OR-ed mask, [8,136) rows the gather
-// starts from, [136,264) destination rows in gather-GEMM mode / raw mask words in conv mode
-// (in conv mode the destination rows are the gather rows).
+// The scheduler warp: draws tiles and fetches their mask words and row numbers straight into
+// a ring slot with 4-byte cp.async.  The slot's "landed" barrier is completed by the copies
+// themselves (one asynchronous arrival per lane), so any number of tiles can be in flight and
+// each is published -- its OR-ed mask computed once, here -- as soon as ITS words are there.
+// Slot layout (ints): [0] tile (-1 = no more tiles), [1] OR-ed mask, [2] steps charged for the
+// tile (scheduler only), [8,136) rows the gather starts from, [136,264) destination rows in gather-GEMM mode /
+// raw mask words in conv mode (in conv mode the destination rows are the gather rows).
 __device__ __forceinline__ void cp_async_4(uint32_t dst, const void *src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
 
 __device__ __forceinline__ void scheduler_run(const RowConvParams &p, const RingView &rv, int ntiles, int kpasses) {
-  constexpr int DEPTH = CB2_ROWCONV_DEPTH;     // tiles whose words are in flight besides the one being published
-  constexpr int STEP_BUDGET = CB2_ROWCONV_STEP_BUDGET; // steps a CTA may hold (drawn, not finished) before it stops drawing tiles
+  constexpr int STEP_BUDGET = CB2_ROWCONV_STEP_BUDGET;  // steps a CTA may hold (drawn, not finished)
   const int lane = (int)lane_id();
   const bool dynamic = p.tickets != nullptr && gridDim.y == 1;
   const bool conv = p.mode == kModeMaskConv;
   int drawn = 0;
   // Tickets come in batches and the next batch is requested before the current one is used up:
-  // the counter's round trip through L2 (a microsecond and more while the gathers saturate the
-  // memory system) would otherwise be paid per tile, and the whole CTA waits on this warp.
-  // Batches shrink to one ticket as the counter nears the end so the tail stays balanced.
+  // the counter's round trip through L2 would otherwise be paid per tile.  Batches shrink to
+  // one ticket as the counter nears the end so the tail stays balanced.
   constexpr int MAX_BATCH = CB2_ROWCONV_TICKET_BATCH;
   int cur_base = 0, cur_left = 0, next_base = 0, next_cnt = 0;
   auto request = [&](int seen) {
@@ -257,108 +268,97 @@ __device__ __forceinline__ void scheduler_run(const RowConvParams &p, const Ring
     return t;
   };
   const uint32_t slots_addr = smem_u32(rv.slots);
-  int issued = 0, published = 0, released = 0, held_steps = 0;
-  bool end = false;
-  for (;;) {
-    if (!end) {
-      // Tiles a CTA has drawn but not finished cannot be taken over by an idle CTA, so the
-      // look-ahead is bounded by WORK, not by tiles: a CTA keeps drawing while the steps it
-      // holds (one per offset in a tile's mask; 1 assumed until the mask has arrived) are within
-      // STEP_BUDGET.  Light tiles keep the pipeline deep; after a tile with many offsets the CTA
-      // draws nothing until that tile is finished.
-      auto account_released = [&]() {
-        while (released < published &&
-               mbar_test_warp(rv.empty0 + 8u * (released % rv.ring), (released / rv.ring) & 1)) {
-          held_steps -= rv.slot(released % rv.ring)[2];
-          ++released;
-        }
-      };
-      for (;;) {
-        account_released();
-        if (held_steps <= STEP_BUDGET || released == published)
-          break;
-        if (!mbar_wait_warp(rv.empty0 + 8u * (released % rv.ring), (released / rv.ring) & 1, rv.abort_flag))
-          return;
-      }
-      const int si = issued % rv.ring;
-      if (!mbar_wait_warp(rv.empty0 + 8u * si, ((issued / rv.ring) & 1) ^ 1, rv.abort_flag))
-        return;
-      account_released();  // before the slot's step count is overwritten
-      const int ticket = draw();
-      if (ticket == 0 && lane == 0)
-        CB2_TRACE_SELECT(1);  // follow the CTA that got the heaviest tile
-      held_steps += 1;
-      int tile = -1;
-      if (ticket < ntiles)
-        tile = conv ? (ntiles - 1 - ticket) : ticket;  // the last tiles of the sorted order carry the most offsets
-      int *sl = rv.slot(si);
-      const uint32_t sa = slots_addr + static_cast<uint32_t>(si * rv.slot_ints) * 4u;
-      if (lane == 0)
-        sl[0] = tile;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int j = i * 32 + lane;
-        const int r = tile * 128 + j;
-        if (tile >= 0 && r < p.n_rows) {
-          if (conv) {
-            cp_async_4(sa + (8 + j) * 4, p.argsort + r);
-            cp_async_4(sa + (136 + j) * 4, p.mask + r);
-          } else {
-            sl[8 + j] = r;
-            if (p.c_inds)
-              cp_async_4(sa + (136 + j) * 4, p.c_inds + r);
-            else
-              sl[136 + j] = r;
-          }
-        } else {
-          sl[8 + j] = -1;
-          sl[136 + j] = conv ? 0 : -1;
-        }
-      }
-      cp_async_commit();
-      if (lane == 0)
-        CB2_TRACE_EVENT(6, 16, tile);  // tile drawn, fetch issued
-      ++issued;
-      end = tile < 0;
-    }
-    while (published < issued && (end || issued - published > DEPTH)) {
-      const int pending = issued - published - 1;  // younger groups that may stay in flight
-      if (pending >= 4)
-        cp_async_wait<4>();
-      else if (pending == 3)
-        cp_async_wait<3>();
-      else if (pending == 2)
-        cp_async_wait<2>();
-      else if (pending == 1)
-        cp_async_wait<1>();
-      else
-        cp_async_wait<0>();
-      __syncwarp();
-      const int si = published % rv.ring;
-      int *sl = rv.slot(si);
-      uint32_t kmask = 1u;
-      if (conv) {
-        const uint32_t m = static_cast<uint32_t>(sl[136 + lane]) | static_cast<uint32_t>(sl[136 + 32 + lane]) |
-                           static_cast<uint32_t>(sl[136 + 64 + lane]) | static_cast<uint32_t>(sl[136 + 96 + lane]);
-        kmask = __reduce_or_sync(0xffffffffu, m) & p.mask_filter;
-        if (p.kv < 32)
-          kmask &= (1u << p.kv) - 1u;
-      }
+  // Tiles a CTA has drawn but not finished cannot be taken over by an idle CTA, so the
+  // look-ahead is bounded by WORK, not by tiles: a CTA draws while the steps it holds (one per
+  // offset in a tile's mask) are within STEP_BUDGET.  Until a tile's mask has landed it is
+  // charged what the previous tile cost -- tiles arrive heaviest first, so that is an upper
+  // estimate -- and the very first one is charged the whole budget: a CTA learns what its
+  // first tile weighs before it takes a second.
+  int issued = 0, accounted = 0, released = 0, held_steps = 0;
+  int guess = (conv && dynamic) ? STEP_BUDGET + 1 : 1;
+  auto account = [&]() {
+    while (accounted < issued &&
+           mbar_test_warp(rv.landed0 + 8u * (accounted % rv.ring), (accounted / rv.ring) & 1)) {
+      int *sl = rv.slot(accounted % rv.ring);
+      const uint32_t kmask = ring_tile_mask(p, sl, sl[0]);
       const int nsteps = (sl[0] >= 0) ? max(1, __popc(kmask) * kpasses) : 1;
-      held_steps += nsteps - 1;  // the tile was counted as one step when it was drawn
+      held_steps += nsteps - sl[2];
       __syncwarp();
       if (lane == 0) {
         sl[1] = static_cast<int>(kmask);
         sl[2] = nsteps;
         CB2_TRACE_EVENT(6, 14, sl[0]);  // tile published
+        mbar_arrive(rv.full0 + 8u * (accounted % rv.ring));
       }
       __syncwarp();
-      if (lane == 0)
-        mbar_arrive(rv.full0 + 8u * si);
-      ++published;
+      guess = nsteps;
+      ++accounted;
     }
-    if (end && published == issued)
+    while (released < accounted &&
+           mbar_test_warp(rv.empty0 + 8u * (released % rv.ring), (released / rv.ring) & 1)) {
+      held_steps -= rv.slot(released % rv.ring)[2];
+      ++released;
+    }
+  };
+  for (;;) {
+    account();
+    const bool may_draw = (held_steps <= STEP_BUDGET || released == issued) && (issued - released < rv.ring);
+    if (!may_draw) {
+      // first learn what the tiles in flight weigh, then wait for the oldest one to be finished
+      const bool ok = accounted < issued
+                          ? mbar_wait_warp(rv.landed0 + 8u * (accounted % rv.ring), (accounted / rv.ring) & 1, rv.abort_flag)
+                          : mbar_wait_warp(rv.empty0 + 8u * (released % rv.ring), (released / rv.ring) & 1, rv.abort_flag);
+      if (!ok)
+        return;
+      continue;
+    }
+    const int si = issued % rv.ring;
+    const int ticket = draw();
+    if (ticket == 0 && lane == 0)
+      CB2_TRACE_SELECT(1);  // follow the CTA that got the heaviest tile
+    int tile = -1;
+    if (ticket < ntiles)
+      tile = conv ? (ntiles - 1 - ticket) : ticket;  // the last tiles of the sorted order carry the most offsets
+    int *sl = rv.slot(si);
+    const uint32_t sa = slots_addr + static_cast<uint32_t>(si * rv.slot_ints) * 4u;
+    if (lane == 0) {
+      sl[0] = tile;
+      sl[2] = guess;
+    }
+    held_steps += guess;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int j = i * 32 + lane;
+      const int r = tile * 128 + j;
+      if (tile >= 0 && r < p.n_rows) {
+        if (conv) {
+          cp_async_4(sa + (8 + j) * 4, p.argsort + r);
+          cp_async_4(sa + (136 + j) * 4, p.mask + r);
+        } else {
+          sl[8 + j] = r;
+          if (p.c_inds)
+            cp_async_4(sa + (136 + j) * 4, p.c_inds + r);
+          else
+            sl[136 + j] = r;
+        }
+      } else {
+        sl[8 + j] = -1;
+        sl[136 + j] = conv ? 0 : -1;
+      }
+    }
+    cp_async_mbar_arrive_noinc(rv.landed0 + 8u * si);  // arrives when this lane's copies have landed
+    __syncwarp();  // the plain stores above are read by other lanes when the slot is published
+    if (lane == 0)
+      CB2_TRACE_EVENT(6, 16, tile);  // tile drawn, fetch issued
+    ++issued;
+    if (tile < 0)
       break;
+  }
+  // publish what is still in flight (the end marker at the latest)
+  while (accounted < issued) {
+    if (!mbar_wait_warp(rv.landed0 + 8u * (accounted % rv.ring), (accounted / rv.ring) & 1, rv.abort_flag))
+      return;
+    account();
   }
   // the last CTA to run out of tiles puts the two counters back to zero for the next launch
   if (dynamic && lane == 0) {
@@ -372,6 +372,7 @@ __device__ __forceinline__ void scheduler_run(const RowConvParams &p, const Ring
       __threadfence();
     }
   }
+  cp_async_wait_all();
 }
 
 template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN, bool TMA_GATHER>
@@ -408,6 +409,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
   rv.slots = reinterpret_cast<int *>(smem + Cfg::OFF_RING);
   rv.full0 = bars + 8u * 20;
   rv.empty0 = bars + 8u * (20 + Cfg::RING);
+  rv.landed0 = bars + 8u * (20 + 2 * Cfg::RING);
   rv.ring = Cfg::RING;
   rv.slot_ints = Cfg::RING_SLOT_INTS;
   rv.abort_flag = abort_flag;
@@ -434,6 +436,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
     mbar_init(final_bar, 1);
     for (int s = 0; s < Cfg::RING; ++s) {
       mbar_init(rv.full0 + 8u * s, 1);
+      mbar_init(rv.landed0 + 8u * s, 32);  // one copy-completion arrival per scheduler lane
       mbar_init(rv.empty0 + 8u * s, Cfg::RING_CONSUMER_WARPS);
     }
     mbar_init_fence();
