@@ -23,6 +23,7 @@ struct TraceBuf {
   int count[8];
   unsigned long long cta[256][3];    // per CTA: start time, end time, steps
   long long prof[256][12];           // per CTA: clock cycles the MMA warp spent per phase
+  long long prof2[256][12];          // per CTA: the same for thread 0 of the epilogue
 };
 __device__ TraceBuf g_trace;
 // 1 in the CTA whose events are recorded (a shared-memory flag: testing it must cost next to
@@ -61,10 +62,12 @@ __device__ __forceinline__ void trace_cta(int which, unsigned long long value) {
 #define CB2_PROF_BEGIN() long long prof_c[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; long long prof_prev = clock64()
 #define CB2_PROF_MARK(i) do { long long prof_t = clock64(); prof_c[i] += prof_t - prof_prev; prof_prev = prof_t; } while (0)
 #define CB2_PROF_END() do { for (int i = 0; i < 12; ++i) ::cb2::g_trace.prof[blockIdx.x & 255][i] = prof_c[i]; } while (0)
+#define CB2_PROF_END2() do { for (int i = 0; i < 12; ++i) ::cb2::g_trace.prof2[blockIdx.x & 255][i] = prof_c[i]; } while (0)
 #else
 #define CB2_PROF_BEGIN() ((void)0)
 #define CB2_PROF_MARK(i) ((void)0)
 #define CB2_PROF_END() ((void)0)
+#define CB2_PROF_END2() ((void)0)
 #define CB2_TRACE_EVENT(role, code, step) ((void)0)
 #define CB2_TRACE_CTA(which, value) ((void)0)
 #define CB2_TRACE_SELECT(on) ((void)0)
@@ -154,6 +157,10 @@ __device__ __forceinline__ bool mbar_test_warp(uint32_t bar, uint32_t parity) {
   if (lane_id() == 0)
     ok = mbar_test(bar, parity) ? 1 : 0;
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
+__device__ __forceinline__ void st_shared_zero16(uint32_t addr) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0) : "memory");
 }
 
 // ---------------------------------------------------------------- named barriers

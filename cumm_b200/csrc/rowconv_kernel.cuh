@@ -81,11 +81,18 @@ template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN, bool TMA_GATHER> struct
   static constexpr int KRED = NATOM_K * ATOM_ELEMS;       // reduction elements per stage
   static constexpr int TILE_M = 128;
   static constexpr int SA = 3;                            // A stages == producer groups
-  static constexpr int SB = 2;                            // weight slots
   static constexpr int A_STAGE_BYTES = TILE_M * 128 * NATOM_K;
   static constexpr int B_SLOT_BYTES = BLOCK_N * 128 * NATOM_K;
   static constexpr int OUT_ROW_BYTES = BLOCK_N * OES;
   static constexpr int STAGING_BYTES = TILE_M * OUT_ROW_BYTES;
+  static constexpr int RING = CB2_ROWCONV_RING;           // tile ring slots
+  static constexpr int RING_SLOT_INTS = 264;              // tile, mask, pad; 128 gather rows; 128 output rows
+  // Weight slots: as many as fit (2 to 6).  A tile whose mask carries many offsets needs a new
+  // weight tile every step, and with two slots the L2 latency of that load bounds the step.
+  static constexpr int FIXED_BYTES = SA * A_STAGE_BYTES + STAGING_BYTES + SA * 2 * 128 * 4 + 128 * 4 +
+                                     2 * BLOCK_N * 4 + RING * RING_SLOT_INTS * 4 + (32 + 3 * RING) * 8 + 64 + 1024;
+  static constexpr int SB_FIT = (232448 - FIXED_BYTES) / B_SLOT_BYTES;
+  static constexpr int SB = SB_FIT < 2 ? 2 : (SB_FIT > 6 ? 6 : SB_FIT);
   static constexpr int NUM_ACC = CB2_ROWCONV_NUM_ACC;
   static constexpr int TMEM_COLS = NUM_ACC * BLOCK_N;     // 128 or 256: power of two >= 32
   static constexpr int EPI_THREADS = 256;                 // two threads per tile row: each takes half the columns
@@ -97,8 +104,6 @@ template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN, bool TMA_GATHER> struct
   static constexpr int FIRST_GATHER_WARP = TMA_WARP + 1;
   static constexpr int SCHED_WARP = FIRST_GATHER_WARP + SA * GROUP_THREADS / 32;  // the last warp hands out tiles
   static constexpr int THREADS = (SCHED_WARP + 1) * 32;   // 544
-  static constexpr int RING = CB2_ROWCONV_RING;                       // tile ring slots
-  static constexpr int RING_SLOT_INTS = 264;              // tile, mask, pad; 128 gather rows; 128 output rows
   static constexpr int RING_CONSUMER_WARPS = SCHED_WARP;   // every warp but the scheduler
   // shared memory map (offsets from a 1024-byte aligned base)
   static constexpr int OFF_A = 0;
@@ -108,9 +113,11 @@ template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN, bool TMA_GATHER> struct
   static constexpr int OFF_OUTROW = OFF_ROWIDX + SA * 2 * 128 * 4;   // 128 ints
   static constexpr int OFF_SCALE = OFF_OUTROW + 128 * 4;             // 2 * BLOCK_N floats
   static constexpr int OFF_RING = OFF_SCALE + 2 * BLOCK_N * 4;       // RING slots
-  static constexpr int OFF_BARS = OFF_RING + RING * RING_SLOT_INTS * 4;  // 20 + 3 * RING mbarriers
-  static constexpr int OFF_MISC = OFF_BARS + (20 + 3 * RING) * 8;                 // tmem ptr, abort, flags
+  static constexpr int OFF_BARS = OFF_RING + RING * RING_SLOT_INTS * 4;  // 32 + 3 * RING mbarriers
+  static constexpr int OFF_MISC = OFF_BARS + (32 + 3 * RING) * 8;                 // tmem ptr, abort, flags
   static constexpr int SMEM_BYTES = OFF_MISC + 64 + 1024;            // + alignment slack
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget of one CTA exceeded");
+  static_assert(SB <= 8, "barrier table holds eight weight slots");
 };
 
 __device__ __forceinline__ float apply_act(float x, int act_type, float act_alpha) {
@@ -165,14 +172,17 @@ __device__ __forceinline__ uint32_t ring_tile_mask(const RowConvParams &p, const
 // pass) steps.  on_tile(tile, slot, kmask_for_store, has_work) -> bool; on_step(tile, f, kp,
 // first, last) -> bool; a false return aborts the walk.  Every consumer warp of the CTA runs
 // the identical walk, so their step counters agree.  All 32 lanes take part.
-template <class TileFn, class StepFn>
-__device__ __forceinline__ bool walk_steps(const RowConvParams &p, const RingView &rv, int kpasses, TileFn on_tile,
-                                           StepFn on_step, long long *prof_c = nullptr,
-                                           long long *prof_prev_p = nullptr) {
+// SINGLE: the walk is run by one thread on its own (no warp-collective operation inside), which
+// is what the roles that issue from a single thread anyway use: their time per step is pure
+// instruction latency, and the collectives would only add to it.
+template <bool SINGLE, class TileFn, class StepFn>
+__device__ __forceinline__ bool walk_steps_impl(const RowConvParams &p, const RingView &rv, int kpasses,
+                                                TileFn on_tile, StepFn on_step, long long *prof_c = nullptr,
+                                                long long *prof_prev_p = nullptr) {
 #ifdef CB2_TRACE
 #define CB2_WALK_MARK(i)                                                                                  \
   do {                                                                                                    \
-    if (prof_c && lane_id() == 0) {                                                                       \
+    if (prof_c && (SINGLE || lane_id() == 0)) {                                                           \
       long long t = clock64();                                                                            \
       prof_c[i] += t - *prof_prev_p;                                                                      \
       *prof_prev_p = t;                                                                                   \
@@ -184,7 +194,8 @@ __device__ __forceinline__ bool walk_steps(const RowConvParams &p, const RingVie
   for (int seq = 0;; ++seq) {
     const int si = seq % rv.ring;
     CB2_WALK_MARK(8);  // previous slot released
-    if (!mbar_wait_warp(rv.full0 + 8u * si, (seq / rv.ring) & 1, rv.abort_flag))
+    if (!(SINGLE ? mbar_wait(rv.full0 + 8u * si, (seq / rv.ring) & 1, rv.abort_flag)
+                 : mbar_wait_warp(rv.full0 + 8u * si, (seq / rv.ring) & 1, rv.abort_flag)))
       return false;
     CB2_WALK_MARK(9);  // slot published
     const int *sl = rv.slot(si);
@@ -209,14 +220,27 @@ __device__ __forceinline__ bool walk_steps(const RowConvParams &p, const RingVie
       }
     }
     CB2_WALK_MARK(10);  // steps done
-    __syncwarp();
-    if (lane_id() == 0)
+    if (!SINGLE)
+      __syncwarp();
+    if (SINGLE || lane_id() == 0)
       mbar_arrive(rv.empty0 + 8u * si);
     if (!cont)
       return false;
     if (tile < 0)
       return true;  // end marker
   }
+}
+
+template <class TileFn, class StepFn>
+__device__ __forceinline__ bool walk_steps(const RowConvParams &p, const RingView &rv, int kpasses, TileFn on_tile,
+                                           StepFn on_step) {
+  return walk_steps_impl<false>(p, rv, kpasses, on_tile, on_step);
+}
+template <class TileFn, class StepFn>
+__device__ __forceinline__ bool walk_steps_single(const RowConvParams &p, const RingView &rv, int kpasses,
+                                                  TileFn on_tile, StepFn on_step, long long *prof_c = nullptr,
+                                                  long long *prof_prev_p = nullptr) {
+  return walk_steps_impl<true>(p, rv, kpasses, on_tile, on_step, prof_c, prof_prev_p);
 }
 
 // The scheduler warp: draws tiles and fetches their mask words and row numbers straight into
@@ -400,16 +424,16 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
   const uint32_t bars = sbase + Cfg::OFF_BARS;
   auto full_a = [&](int s) { return bars + 8u * s; };
   auto empty_a = [&](int s) { return bars + 8u * (3 + s); };
-  auto full_b = [&](int s) { return bars + 8u * (6 + s); };
-  auto empty_b = [&](int s) { return bars + 8u * (8 + s); };
-  auto acc_full = [&](int s) { return bars + 8u * (10 + s); };
-  auto acc_empty = [&](int s) { return bars + 8u * (14 + s); };
-  const uint32_t final_bar = bars + 8u * 18;
+  auto acc_full = [&](int s) { return bars + 8u * (6 + s); };
+  auto acc_empty = [&](int s) { return bars + 8u * (10 + s); };
+  const uint32_t final_bar = bars + 8u * 14;
+  auto full_b = [&](int s) { return bars + 8u * (16 + s); };
+  auto empty_b = [&](int s) { return bars + 8u * (24 + s); };
   RingView rv;
   rv.slots = reinterpret_cast<int *>(smem + Cfg::OFF_RING);
-  rv.full0 = bars + 8u * 20;
-  rv.empty0 = bars + 8u * (20 + Cfg::RING);
-  rv.landed0 = bars + 8u * (20 + 2 * Cfg::RING);
+  rv.full0 = bars + 8u * 32;
+  rv.empty0 = bars + 8u * (32 + Cfg::RING);
+  rv.landed0 = bars + 8u * (32 + 2 * Cfg::RING);
   rv.ring = Cfg::RING;
   rv.slot_ints = Cfg::RING_SLOT_INTS;
   rv.abort_flag = abort_flag;
@@ -479,9 +503,12 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
     constexpr int SWZ = (CPR >= 8 ? 8 : CPR) - 1;
     constexpr int CH_PER_ROUND = 32 * Cfg::OES / 16;   // chunks produced per 32 columns
     int acc_use = 0;
+    CB2_PROF_BEGIN();
     walk_steps(
         p, rv, kpasses,
         [&](int tile, const int *sl, uint32_t kmask_store, bool has_work) -> bool {
+          if (et == 0)
+            CB2_PROF_MARK(0);  // walk
           const int o = (p.mode == kModeMaskConv) ? sl[8 + erow] : sl[136 + erow];  // destination row of this thread's tile row
           if (et == 0 && p.mask_out && blockIdx.y == 0)
             p.mask_out[tile] = kmask_store;
@@ -494,9 +521,12 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
               misc[2] = ok ? 1 : 0;
               if (!ok)
                 fail(kStatusWaitTimeout);
+              CB2_PROF_MARK(1);  // accumulator complete
             }
           }
           named_bar_sync(1, Cfg::EPI_THREADS);  // wait result visible; staging free again
+          if (et == 0)
+            CB2_PROF_MARK(2);  // barrier
           if (has_work && misc[2] == 0)
             return false;
           if (half == 0)
@@ -635,9 +665,13 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
             mbar_arrive(acc_empty(buf));
             ++acc_use;
           }
-          if (et == 0)
+          if (et == 0) {
             CB2_TRACE_EVENT(4, 12, tile);  // staged
+            CB2_PROF_MARK(3);  // TMEM -> staging
+          }
           named_bar_sync(1, Cfg::EPI_THREADS);  // staging complete
+          if (et == 0)
+            CB2_PROF_MARK(4);  // barrier
           // phase 2: CPR threads per row write whole rows
           {
             const int c = et % CPR;
@@ -659,13 +693,17 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
               }
             }
           }
-          if (et == 0)
+          if (et == 0) {
             CB2_TRACE_EVENT(4, 9, tile);  // rows stored
+            CB2_PROF_MARK(5);  // staging -> global
+          }
           return true;
         },
         [&](int, int, int, bool, bool) -> bool { return true; });
+    if (et == 0)
+      CB2_PROF_END2();
   } else if (warp == Cfg::MMA_WARP) {
-    // ======================= MMA issuer (lane 0 issues; the warp walks together)
+    // ======================= MMA issuer (one thread walks and issues)
     constexpr uint32_t idesc = make_idesc(KIND, false, B_MN, 128, BLOCK_N);
     int step = 0, acc_use = 0, bcount = 0, last_key = -1, cur_slot = 0;
     bool ok_all = true;
@@ -673,17 +711,17 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
     const uint64_t bdesc_base = B_MN ? make_smem_desc(sbase + Cfg::OFF_B, p.b_lbo, p.b_sbo)
                                      : make_smem_desc(sbase + Cfg::OFF_B, 16, 1024);
     CB2_PROF_BEGIN();
-    walk_steps(
+    if (lane == 0) {
+    walk_steps_single(
         p, rv, kpasses,
         [&](int, const int *, uint32_t, bool) -> bool {
-          if (lane == 0)
-            CB2_PROF_MARK(7);  // previous slot released, this tile's slot read
+          CB2_PROF_MARK(7);  // previous slot released, this tile's slot read
           return true;
         },
         [&](int tile, int f, int kp, bool first, bool last) -> bool {
           const int buf = acc_use % Cfg::NUM_ACC;
           int ok = 1;
-          if (lane == 0) {
+          {
             CB2_PROF_MARK(0);  // the walk between steps
             if (first)
               ok = mbar_wait(acc_empty(buf), ((acc_use / Cfg::NUM_ACC) & 1) ^ 1, abort_flag);
@@ -742,13 +780,11 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
               CB2_PROF_MARK(6);  // commits
             }
           }
-          ok = __shfl_sync(0xffffffffu, ok, 0);
           ++step;
           if (last)
             ++acc_use;
           if (!ok) {
-            if (lane == 0)
-              fail(kStatusWaitTimeout);
+            fail(kStatusWaitTimeout);
             ok_all = false;
             return false;
           }
@@ -758,29 +794,28 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
         , prof_c, &prof_prev
 #endif
         );
-    if (lane == 0) {
       CB2_TRACE_CTA(2, (unsigned long long)step);
       CB2_PROF_END();
-    }
-    // make sure every MMA has retired before TMEM is released
-    if (lane == 0 && ok_all) {
-      tc_commit(final_bar);
-      if (!mbar_wait(final_bar, 0, abort_flag))
-        fail(kStatusWaitTimeout);
+      // make sure every MMA has retired before TMEM is released
+      if (ok_all) {
+        tc_commit(final_bar);
+        if (!mbar_wait(final_bar, 0, abort_flag))
+          fail(kStatusWaitTimeout);
+      }
     }
     __syncwarp();
   } else if (warp == Cfg::TMA_WARP) {
     // ======================= weight tiles by TMA (lane 0 issues)
-    if (lane == 0)
-      tma_prefetch_desc(&tmap_b);
     int bcount = 0, last_key = -1;
-    walk_steps(
+    if (lane == 0) {
+    tma_prefetch_desc(&tmap_b);
+    walk_steps_single(
         p, rv, kpasses, [&](int, const int *, uint32_t, bool) -> bool { return true; },
         [&](int tile, int f, int kp, bool, bool) -> bool {
           int ok = 1;
           const int key = f * kpasses + kp;
           if (key != last_key) {
-            if (lane == 0) {
+            {
               const int slot = bcount % Cfg::SB;
               ok = mbar_wait(empty_b(slot), ((bcount / Cfg::SB) & 1) ^ 1, abort_flag);
               if (ok) {
@@ -801,28 +836,44 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
                 }
               }
             }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
             ++bcount;
             last_key = key;
           }
           if (!ok) {
-            if (lane == 0)
-              fail(kStatusWaitTimeout);
+            fail(kStatusWaitTimeout);
             return false;
           }
           return true;
         });
+    }
+    __syncwarp();
   } else if (warp == Cfg::SCHED_WARP) {
     // ======================= scheduler: draws tiles, publishes their masks and row numbers
     scheduler_run(p, rv, ntiles, kpasses);
   } else {
     // ======================= operand-row gather: group g owns stage g
     if constexpr (TMA_GATHER) {
-      // one warp per group; lane L fetches tile rows 4L .. 4L+3 with one request per 128-byte
-      // column block; a row index of -1 lies outside the tensor and reads as zeros
+      // One warp per group; lane L fetches tile rows 4L .. 4L+3 ("its quad") with one request
+      // per 128-byte column block.  A quad none of whose rows has a neighbour at this offset is
+      // not requested at all -- for the offsets away from the centre that is most quads, and the
+      // copy engine's request rate is what bounds such steps.  The stage therefore keeps the
+      // invariant "a quad that was not requested holds zeros": it is cleared once here, and a
+      // quad that was filled in the previous use and is not refilled now is cleared again.
       const int g = warp - Cfg::FIRST_GATHER_WARP;
       if (lane == 0)
         tma_prefetch_desc(&tmap_a);
+      const uint32_t my_quad = sbase + Cfg::OFF_A + g * Cfg::A_STAGE_BYTES + lane * (4 * 128);
+      auto clear_quad = [&]() {
+#pragma unroll
+        for (int ka = 0; ka < NATOM_K; ++ka)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            st_shared_zero16(my_quad + ka * (Cfg::TILE_M * 128) + i * 16);
+      };
+      clear_quad();
+      fence_proxy_async_smem();
+      __syncwarp();
+      uint32_t dirty = 0;  // quads of this stage that hold gathered rows
       int step = 0;
       int o[4] = {-1, -1, -1, -1};
       walk_steps(
@@ -862,16 +913,25 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
                 fail(kStatusWaitTimeout);
               return false;
             }
-            if (lane == 0) {
-              CB2_TRACE_EVENT(g, 2, step - 1);  // stage free
-              mbar_arrive_expect_tx(full_a(g), Cfg::A_STAGE_BYTES);
+            const bool wanted = (idx[0] & idx[1] & idx[2] & idx[3]) >= 0;  // some row index is not -1
+            const uint32_t need = __ballot_sync(0xffffffffu, wanted);
+            if (((dirty >> lane) & 1u) && !wanted) {
+              clear_quad();
+              fence_proxy_async_smem();  // generic-proxy stores, read by the tensor core
             }
             __syncwarp();
-            const uint32_t dst = sbase + Cfg::OFF_A + g * Cfg::A_STAGE_BYTES + lane * (4 * 128);
+            if (lane == 0) {
+              CB2_TRACE_EVENT(g, 2, step - 1);  // stage free
+              mbar_arrive_expect_tx(full_a(g), static_cast<uint32_t>(__popc(need)) * (NATOM_K * 512));
+            }
+            __syncwarp();
+            if (wanted) {
 #pragma unroll
-            for (int ka = 0; ka < NATOM_K; ++ka)
-              tma_gather4(dst + ka * (Cfg::TILE_M * 128), &tmap_a, full_a(g), kp * Cfg::KRED + ka * Cfg::ATOM_ELEMS,
-                          idx[0], idx[1], idx[2], idx[3]);
+              for (int ka = 0; ka < NATOM_K; ++ka)
+                tma_gather4(my_quad + ka * (Cfg::TILE_M * 128), &tmap_a, full_a(g),
+                            kp * Cfg::KRED + ka * Cfg::ATOM_ELEMS, idx[0], idx[1], idx[2], idx[3]);
+            }
+            dirty = need;
             if (lane == 0)
               CB2_TRACE_EVENT(g, 3, step - 1);  // copies issued
             return true;
