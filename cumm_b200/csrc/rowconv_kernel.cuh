@@ -66,6 +66,12 @@ struct RowConvParams {
 #ifndef CB2_ROWCONV_TICKET_BATCH
 #define CB2_ROWCONV_TICKET_BATCH 4
 #endif
+#ifndef CB2_ROWCONV_EPI_PARTS
+#define CB2_ROWCONV_EPI_PARTS 4
+#endif
+#ifndef CB2_ROWCONV_EPI_PIPE
+#define CB2_ROWCONV_EPI_PIPE 0
+#endif
 #ifndef CB2_ROWCONV_NUM_ACC
 #define CB2_ROWCONV_NUM_ACC 2
 #endif
@@ -95,8 +101,11 @@ template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN, bool TMA_GATHER> struct
   static constexpr int SB = SB_FIT < 2 ? 2 : (SB_FIT > 6 ? 6 : SB_FIT);
   static constexpr int NUM_ACC = CB2_ROWCONV_NUM_ACC;
   static constexpr int TMEM_COLS = NUM_ACC * BLOCK_N;     // 128 or 256: power of two >= 32
-  static constexpr int EPI_THREADS = 256;                 // two threads per tile row: each takes half the columns
-  static constexpr int EPI_HALVES = EPI_THREADS / 128;
+  // Epilogue: several threads per tile row, each converting its share of the columns.  The
+  // conversion is a chain of dependent fixed-latency instructions, so its rate is set by how
+  // many warps each SM sub-partition can switch between, not by arithmetic throughput.
+  static constexpr int EPI_HALVES = (KIND == 1 && BLOCK_N >= 128) ? CB2_ROWCONV_EPI_PARTS : 2;
+  static constexpr int EPI_THREADS = 128 * EPI_HALVES;
   static constexpr int GROUP_THREADS = TMA_GATHER ? 32 : CB2_ROWCONV_GROUP_THREADS;
   static constexpr int FULL_A_COUNT = TMA_GATHER ? 1 : GROUP_THREADS;
   static constexpr int MMA_WARP = EPI_THREADS / 32;
@@ -133,10 +142,23 @@ __device__ __forceinline__ float apply_act(float x, int act_type, float act_alph
   }
 }
 
+// float -> int8, round-to-nearest-even, saturating, NaN -> 0 (what cvt.rni.sat.s8.f32 returns),
+// with the int8 value in the low byte of the result.  Conversion instructions issue at a
+// quarter of the rate of plain arithmetic and the requant epilogue already spends one per
+// element on int32 -> float, so this direction is done in the arithmetic pipes: clamp to
+// [-128, 127] with the NaN-propagating min/max, then add 1.5 * 2^23, which leaves the rounded
+// integer in the low mantissa bits (a NaN stays a NaN, whose low byte is 0).
 __device__ __forceinline__ uint32_t cvt_sat_s8(float t) {
-  int r;
-  asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(t));
-  return static_cast<uint32_t>(r) & 0xffu;
+  float c;
+  asm("max.NaN.f32 %0, %1, 0fC3000000;\n\t"
+      "min.NaN.f32 %0, %0, 0f42FE0000;"
+      : "=f"(c)
+      : "f"(t));
+  return __float_as_uint(__fadd_rn(c, 12582912.0f));
+}
+// low bytes of a, b, c, d -> one word (three byte-permutes instead of masks, shifts and ors)
+__device__ __forceinline__ uint32_t pack_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
 }
 
 // Tiles are handed out by one scheduler warp per CTA through a small shared-memory ring.
@@ -537,13 +559,26 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
           const bool use_src = (p.src_mode != kSrcNone) && (p.beta != 0.f);
           // fast path: out = cvt(acc); everything else goes through the general epilogue
           const bool plain = !use_src && p.act_type == 0 && p.alpha == 1.f;
-#pragma unroll 1
-          for (int round = 0; round < COLS_PER_HALF / 32; ++round) {
-            uint32_t v[32];
+          // With registers to spare (the variants with few threads) the next 32 columns are
+          // already on their way from TMEM while the current ones are converted.
+          constexpr int ROUNDS = COLS_PER_HALF / 32;
+          constexpr bool PIPE = CB2_ROWCONV_EPI_PIPE && Cfg::THREADS <= 512 && ROUNDS > 1;
+          uint32_t vbuf[PIPE ? 2 : 1][32];
+          if (PIPE && has_work)
+            tmem_ld32(trow + half * COLS_PER_HALF, vbuf[0]);
+#pragma unroll PIPE ? ROUNDS : 1
+          for (int round = 0; round < ROUNDS; ++round) {
+            uint32_t(&v)[32] = vbuf[PIPE ? (round & 1) : 0];
             const int col0 = half * COLS_PER_HALF + round * 32;
             if (has_work) {
-              tmem_ld32(trow + col0, v);
-              tmem_ld_wait();
+              if constexpr (PIPE) {
+                tmem_ld_wait_regs(v);
+                if (round + 1 < ROUNDS)
+                  tmem_ld32(trow + col0 + 32, vbuf[(round + 1) & 1]);
+              } else {
+                tmem_ld32(trow + col0, v);
+                tmem_ld_wait();
+              }
             } else {
 #pragma unroll
               for (int i = 0; i < 32; ++i)
@@ -618,10 +653,20 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
             } else {
               uint32_t packed[8];
               float t[32];
+              {
 #pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                const int col = col0 + i;
-                t[i] = __fmaf_rn(s_scale[col], __int2float_rn(static_cast<int>(v[i])), s_bias[col]);
+                for (int i = 0; i < 32; ++i)
+                  t[i] = __int2float_rn(static_cast<int>(v[i]));
+                const float4 *sc4 = reinterpret_cast<const float4 *>(s_scale + col0);
+                const float4 *bi4 = reinterpret_cast<const float4 *>(s_bias + col0);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  const float4 sc = sc4[q], bi = bi4[q];
+                  t[4 * q + 0] = __fmaf_rn(sc.x, t[4 * q + 0], bi.x);
+                  t[4 * q + 1] = __fmaf_rn(sc.y, t[4 * q + 1], bi.y);
+                  t[4 * q + 2] = __fmaf_rn(sc.z, t[4 * q + 2], bi.z);
+                  t[4 * q + 3] = __fmaf_rn(sc.w, t[4 * q + 3], bi.w);
+                }
               }
               if (use_src) {
                 uint4 srcv[2];
@@ -649,8 +694,8 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
               }
 #pragma unroll
               for (int i = 0; i < 32; i += 4)
-                packed[i / 4] = cvt_sat_s8(t[i]) | (cvt_sat_s8(t[i + 1]) << 8) | (cvt_sat_s8(t[i + 2]) << 16) |
-                                (cvt_sat_s8(t[i + 3]) << 24);
+                packed[i / 4] = pack_low_bytes(cvt_sat_s8(t[i]), cvt_sat_s8(t[i + 1]), cvt_sat_s8(t[i + 2]),
+                                               cvt_sat_s8(t[i + 3]));
 #pragma unroll
               for (int q = 0; q < 2; ++q) {
                 const int c = (col0 / 32) * CH_PER_ROUND + q;

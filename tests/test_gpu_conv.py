@@ -224,6 +224,25 @@ def test_int8_inference_bit_exact(torch, oracle, n, C, K):
     assert (got == want).all(), f"{int((got != want).sum())} of {got.size} int8 outputs differ"
 
 
+def test_int8_large_accumulators_bit_exact(torch, oracle):
+    """Extreme int8 inputs on a dense block: |accumulator| reaches 127 * 127 * 128 * 27 > 2^24, far
+    outside the range in which int32 -> float is a mantissa add, and part of the outputs saturate."""
+    coords = W.dense_block_coords(10)
+    tb = W.build_tables(coords)
+    C = K = 128
+    rng = np.random.default_rng(77)
+    x = np.where(rng.random((tb.n_in, C)) < 0.9, 127, -127).astype(np.int8)
+    w = np.where(rng.random((K, 27, C)) < 0.9, 127, -127).astype(np.int8)
+    scale = (rng.uniform(1.5e-6, 4.5e-6, K)).astype(np.float32)
+    bias = rng.standard_normal(K).astype(np.float32)
+    got = H.run_conv_s8(torch, x, w, scale, bias, tb)
+    H.check_status()
+    want = oracle.mask_igemm_s8(x, w, np.zeros((tb.n_out, K), np.int8), scale, bias, tb.indices, tb.mask,
+                                tb.mask_argsort)
+    assert (np.abs(want.astype(int)) < 127).mean() > 0.2 and (want == 127).any(), "degenerate test data"
+    assert (got == want).all(), f"{int((got != want).sum())} of {got.size} int8 outputs differ"
+
+
 def test_int8_output_add_and_relu(torch, oracle):
     tb, _, _, _ = make(2000, 451, 16, 16)
     rng = np.random.default_rng(8)
