@@ -269,11 +269,14 @@ int run_rowconv(DeviceState *dev, RowConvParams &p, int kind, bool b_mn, const v
 
 // ---------------------------------------------------------------- weight gradient
 struct WgradLayout {
-  int block_n, gy, G, slots;
-  size_t off_flags, off_partials, total;
+  int block_n, gy, G, slots, list_stride;
+  size_t off_flags, off_partials, off_lists, total;
 };
 
-void wgrad_layout(int num_sms, int m_total, int n_total, WgradLayout *L) {
+// Workspace of the weight gradient: 512-byte header (tile counts per offset), unit flags,
+// fp32 partials (one per unit: at most G + kv - 1 <= G + 32), and per offset the list of the
+// row tiles that carry it.
+void wgrad_layout(int num_sms, int m_total, int n_total, long long n_rows, int kv, WgradLayout *L) {
   L->block_n = n_total <= 64 ? 64 : 128;
   const int mt = (m_total + 127) / 128, nt = (n_total + L->block_n - 1) / L->block_n;
   L->gy = mt * nt;
@@ -284,7 +287,33 @@ void wgrad_layout(int num_sms, int m_total, int n_total, WgradLayout *L) {
   L->off_flags = 512;
   size_t flags_bytes = ((size_t)L->slots * L->gy * 4 + 255) / 256 * 256;
   L->off_partials = L->off_flags + flags_bytes;
-  L->total = L->off_partials + (size_t)L->slots * L->gy * 128 * L->block_n * 4;
+  L->off_lists = L->off_partials + (size_t)L->slots * L->gy * 128 * L->block_n * 4;
+  const long long ntiles = (n_rows + 127) / 128;
+  L->list_stride = (int)((ntiles + 63) / 64 * 64);
+  L->total = L->off_lists + (size_t)(kv > 0 ? kv : 1) * L->list_stride * 4;
+}
+
+// Launch with programmatic stream serialisation: the kernel may be scheduled while its
+// predecessor on the stream is still running and synchronises with it through
+// griddepcontrol.wait in its own code.  CUMM_B200_PDL=0 launches the ordinary way.
+template <class Kern, class... Args>
+cudaError_t launch_after(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  static const bool pdl = [] {
+    const char *v = getenv("CUMM_B200_PDL");
+    return !(v && v[0] == '0');
+  }();
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
 }
 
 template <int BLOCK_N, int GATHER>
@@ -299,8 +328,7 @@ int launch_wgrad_inst(const CUtensorMap &ma, const CUtensorMap &mb, const WgradP
     CB2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     configured.fetch_or(1ull << dev);
   }
-  kern<<<dim3(gx, gy), Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, p);
-  CB2_CUDA(cudaGetLastError());
+  CB2_CUDA(launch_after(kern, dim3(gx, gy), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, stream, ma, mb, p));
   g_launches.fetch_add(1);
   return CB2_OK;
 }
@@ -309,7 +337,7 @@ int run_wgrad(DeviceState *dev, WgradParams &p, void *workspace, size_t workspac
               const void *src, long long ldo, long long f_stride, float alpha, float beta, int out_f32,
               cudaStream_t stream) {
   WgradLayout L;
-  wgrad_layout(dev->num_sms, p.m_total, p.n_total, &L);
+  wgrad_layout(dev->num_sms, p.m_total, p.n_total, p.n_rows, p.kv, &L);
   CB2_CHECK_RT(workspace != nullptr && workspace_bytes >= L.total, "workspace at least %zu bytes.", L.total);
   CB2_CHECK_ARG(reinterpret_cast<uintptr_t>(workspace) % 256 == 0, "workspace must be 256-byte aligned");
   CB2_CHECK_ARG(p.m_total % 8 == 0 && p.n_total % 8 == 0, "channel counts must be multiples of 8");
@@ -317,12 +345,16 @@ int run_wgrad(DeviceState *dev, WgradParams &p, void *workspace, size_t workspac
   CB2_CHECK_ARG(aligned16(p.dout) && aligned16(p.x), "operand pointers must be 16-byte aligned");
   uint8_t *ws = reinterpret_cast<uint8_t *>(workspace);
   p.sched = reinterpret_cast<int *>(ws);
-  p.unit_flags = reinterpret_cast<int *>(ws + L.off_flags);
   p.partials = reinterpret_cast<float *>(ws + L.off_partials);
+  p.lists = reinterpret_cast<const int *>(ws + L.off_lists);
+  p.list_stride = L.list_stride;
   p.status = dev->status;
   const int ntiles = (p.n_rows + 127) / 128;
   int rc;
   if (ntiles > 0) {
+    wgrad_plan_kernel<<<p.kv, 1024, 0, stream>>>(p, reinterpret_cast<int *>(ws + L.off_lists), L.list_stride);
+    CB2_CUDA(cudaGetLastError());
+    g_launches.fetch_add(1);
     CUtensorMap ma, mb;
     rc = make_rows_map(&ma, p.dout, 2, p.m_total, p.a_rows, p.ld_dout);
     if (rc)
@@ -347,7 +379,6 @@ int run_wgrad(DeviceState *dev, WgradParams &p, void *workspace, size_t workspac
   WgradReduceParams r;
   r.partials = p.partials;
   r.sched = p.sched;
-  r.unit_flags = p.unit_flags;
   r.out = out;
   r.src = src ? src : out;
   r.ldo = ldo;
@@ -357,14 +388,14 @@ int run_wgrad(DeviceState *dev, WgradParams &p, void *workspace, size_t workspac
   r.kv = p.kv;
   r.block_n = L.block_n;
   r.gy = L.gy;
+  r.G = L.G;
   r.mask_filter = p.mode == kWgradMaskConv ? p.mask_filter : 1u;
   r.alpha = alpha;
   r.beta = beta;
   r.out_f32 = out_f32;
   const long long e4 = (long long)L.gy * (L.block_n / 4) * 128;
   const int bx = (int)((e4 + 31) / 32);
-  wgrad_reduce_kernel<<<dim3(bx, p.kv), 256, 0, stream>>>(r);
-  CB2_CUDA(cudaGetLastError());
+  CB2_CUDA(launch_after(wgrad_reduce_kernel, dim3(bx, p.kv), dim3(256), 0, stream, r));
   g_launches.fetch_add(1);
   return CB2_OK;
 }
@@ -472,7 +503,7 @@ size_t cb2_gemm_workspace_size(const cb2_gemm_args *a) {
   if (get_device(&dev))
     return 0;
   WgradLayout L;
-  wgrad_layout(dev->num_sms, a->m, a->n, &L);
+  wgrad_layout(dev->num_sms, a->m, a->n, a->k, 1, &L);
   return L.total;
 }
 
@@ -483,7 +514,7 @@ size_t cb2_conv_workspace_size(const cb2_conv_args *a) {
   if (get_device(&dev))
     return 0;
   WgradLayout L;
-  wgrad_layout(dev->num_sms, a->K, a->C, &L);
+  wgrad_layout(dev->num_sms, a->K, a->C, a->N, a->kernel_volume, &L);
   return L.total;
 }
 
@@ -509,11 +540,11 @@ int cb2_conv_backward_weight_static(const cb2_conv_args *a, void *stream_v) {
   const int need_words = (a->N + a->mask_width - 1) / a->mask_width;
   CB2_CHECK_RT(a->mask_words >= need_words, "reduced mask has %d words, %d needed", a->mask_words, need_words);
   WgradLayout L;
-  wgrad_layout(st->dev.num_sms, a->K, a->C, &L);
+  wgrad_layout(st->dev.num_sms, a->K, a->C, a->N, a->kernel_volume, &L);
   CB2_CHECK_RT(L.total <= kStaticScratchBytes,
-               "this problem (K=%d, C=%d) needs %zu bytes of scratch; the static scratch holds %zu. Use cb2_conv_run "
-               "with a caller-provided workspace instead.",
-               a->K, a->C, L.total, kStaticScratchBytes);
+               "this problem (K=%d, C=%d, N=%d) needs %zu bytes of scratch; the static scratch holds %zu. Use "
+               "cb2_conv_run with a caller-provided workspace instead.",
+               a->K, a->C, a->N, L.total, kStaticScratchBytes);
   WgradParams p;
   memset(&p, 0, sizeof(p));
   p.dout = a->ptr_A;

@@ -36,8 +36,10 @@ struct WgradParams {
   const int32_t *a_inds;   // pair-list mode
   const int32_t *b_inds;   //   "
   float *partials;         // workspace: [unit][m_tile][n_tile][128][BLOCK_N] fp32
-  int *sched;              // workspace header: [0,32) units per f, [32,64) first unit of f, [64] total units
-  int *unit_flags;         // workspace: [unit] 1 when the unit produced a partial
+  int *sched;              // workspace header: [0,32) number of row tiles carrying offset f; [32,64) units of
+                           // offset f and [64,96) the first of them (written by the first stage for the second)
+  const int *lists;        // workspace: per offset, the ordered list of those tiles
+  int list_stride;         // ints between two offsets' lists
   int *status;
   long long ld_dout, ld_x;
   int n_rows;
@@ -60,11 +62,10 @@ template <int BLOCK_N, int GATHER> struct WgradCfg {
   static constexpr int FULL_COUNT = GATHER == kGatherCpAsync ? 128 : 1;
   static constexpr int OFF_STAGES = 0;
   static constexpr int OFF_ROWIDX = SA * STAGE_BYTES;       // SA x 2 buffers x 2 operands x 128 ints
-  static constexpr int OFF_SCHED = OFF_ROWIDX + SA * 2 * 2 * 128 * 4;  // 96 ints + unit table
-  static constexpr int MAX_UNITS = 4;                        // units of one CTA with a bitmap
-  static constexpr int BITMAP_WORDS = 2048;                  // 32 tiles per word
-  static constexpr int OFF_BITMAP = OFF_SCHED + 128 * 4;
-  static constexpr int OFF_BARS = OFF_BITMAP + BITMAP_WORDS * 4;
+  static constexpr int OFF_SCHED = OFF_ROWIDX + SA * 2 * 2 * 128 * 4;  // this CTA's units
+  static constexpr int TILE_CAP = 2048;                      // tiles of one CTA staged in shared memory
+  static constexpr int OFF_TILES = OFF_SCHED + 256 * 4;
+  static constexpr int OFF_BARS = OFF_TILES + TILE_CAP * 4;
   static constexpr int OFF_MISC = OFF_BARS + 16 * 8;
   static constexpr int SMEM_BYTES = OFF_MISC + 64 + 1024;
 };
@@ -73,6 +74,8 @@ template <int BLOCK_N, int GATHER> struct WgradCfg {
 __device__ __forceinline__ uint32_t wgrad_tile_mask(const WgradParams &p, int tile) {
   if (p.mode != kWgradMaskConv)
     return 1u;
+  if (p.mask_width == 128)  // the usual case: one word per tile
+    return tile < p.rmask_words ? (__ldg(p.rmask + tile) & p.mask_filter) : 0u;
   const int r0 = tile * 128;
   int r1 = r0 + 127;
   if (r1 >= p.n_rows)
@@ -85,193 +88,181 @@ __device__ __forceinline__ uint32_t wgrad_tile_mask(const WgradParams &p, int ti
   return v & p.mask_filter;
 }
 
-// Unit schedule, identical in every CTA: S_f units for offset f, proportional to the
-// number of row tiles that carry f; unit (f, s) covers tiles [T*s/S_f, T*(s+1)/S_f).
-// s_sched: [0,32) S_f, [32,64) first unit of f, [64] total units,
-//          [96 + 4k .. 96 + 4k + 3] for this CTA's k-th unit: f, first bitmap word index
-//          (absolute tile / 32), offset of its words in the bitmap, number of words (0 = the
-//          unit has no bitmap and is scanned from global memory).
-// bitmap: for each of the CTA's first MAX_UNITS units, one bit per tile of its range that
-// carries f, so that every role can enumerate the unit's tiles without touching memory.
-template <int MAX_UNITS, int BITMAP_WORDS>
-__device__ __forceinline__ void wgrad_build_schedule(const WgradParams &p, int ntiles, int *s_sched,
-                                                     uint32_t *bitmap) {
-  constexpr int MAXK = 16;  // tile masks kept in registers per thread
-  for (int i = threadIdx.x; i < 128; i += blockDim.x)
-    s_sched[i] = 0;
-  __syncthreads();
-  uint32_t mk[MAXK];
+// ---------------------------------------------------------------- schedule
+// The work is the sequence of all (filter offset f, row tile carrying f) pairs, offsets in
+// ascending order, tiles in ascending order inside an offset: T steps in all.  CTA c of G takes
+// the steps [c*T/G, (c+1)*T/G) -- every CTA the same number, whatever the offsets' shares --
+// and each maximal run of one offset inside a CTA's range is a UNIT: it accumulates in TMEM
+// and leaves one fp32 partial.  The units of an offset are consecutive in this numbering, and
+// there are at most G + kv - 1 of them.
+//
+// A first small kernel (one block per offset) writes, per offset, the count and the ordered
+// list of its tiles; both later kernels derive everything else from the kv counts.
+//   sched[f]                      tiles carrying offset f
+//   lists[f * list_stride + k]    the k-th of them
+
+// For lane f of one warp, given cnt_f: P = steps before offset f, T = all steps, c_first =
+// CTA holding step P, S = units of f, U = units before f.
+__device__ __forceinline__ void wgrad_plan_warp(int cnt, int G, int &P, int &T, int &c_first, int &S, int &U) {
+  const int lane = (int)lane_id();
+  int incl = cnt;
 #pragma unroll
-  for (int k = 0; k < MAXK; ++k) {
-    const int t = k * blockDim.x + threadIdx.x;
-    mk[k] = (t < ntiles) ? wgrad_tile_mask(p, t) : 0u;
+  for (int d = 1; d < 32; d <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= d)
+      incl += v;
   }
-  // per-offset tile counts: one ballot per (offset, 32 tiles), one shared-memory add per warp
-  {
-    const int ln = threadIdx.x & 31;
-    int mine = 0;  // lane f accumulates the count of offset f
+  T = __shfl_sync(0xffffffffu, incl, 31);
+  P = incl - cnt;
+  // the CTA holding step x is the largest c with c*T/G <= x, i.e. ceil((x+1)*G/T) - 1
+  auto chunk_of = [&](int x) -> int {
+    const int c = (int)((((long long)x + 1) * G + T - 1) / T) - 1;
+    return c < G - 1 ? c : G - 1;
+  };
+  c_first = 0;
+  S = 0;
+  if (cnt > 0) {
+    c_first = chunk_of(P);
+    S = chunk_of(P + cnt - 1) - c_first + 1;
+  }
+  int incl_s = S;
 #pragma unroll
-    for (int k = 0; k < MAXK; ++k) {
-      if (k * (int)blockDim.x < ntiles) {  // uniform
-        const uint32_t any = __reduce_or_sync(0xffffffffu, mk[k]);
-        for (uint32_t rest = any; rest;) {
-          const int f = __ffs(rest) - 1;
-          rest &= rest - 1;
-          const int c = __popc(__ballot_sync(0xffffffffu, (mk[k] >> f) & 1u));
-          if (ln == f)
-            mine += c;
-        }
-      }
-    }
-    for (int t0 = MAXK * blockDim.x; t0 < ntiles; t0 += blockDim.x) {  // uniform trip count
-      const int t = t0 + threadIdx.x;
-      const uint32_t m = (t < ntiles) ? wgrad_tile_mask(p, t) : 0u;
-      const uint32_t any = __reduce_or_sync(0xffffffffu, m);
-      for (uint32_t rest = any; rest;) {
-        const int f = __ffs(rest) - 1;
-        rest &= rest - 1;
-        const int c = __popc(__ballot_sync(0xffffffffu, (m >> f) & 1u));
-        if (ln == f)
-          mine += c;
-      }
-    }
-    if (mine)
-      atomicAdd(&s_sched[ln], mine);
+  for (int d = 1; d < 32; d <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, incl_s, d);
+    if (lane >= d)
+      incl_s += v;
   }
-  __syncthreads();
+  U = incl_s - S;
+}
+
+// One block per filter offset: count and list the tiles that carry it.  Warp w owns a
+// contiguous span of tiles, so the list comes out in ascending order with one block-wide
+// synchronisation per batch of 1024 * K tiles.
+__global__ void __launch_bounds__(1024) wgrad_plan_kernel(const WgradParams p, int *lists, int list_stride) {
+  constexpr int K = 4;
+  __shared__ int s_w[32];
+  const int f = blockIdx.x;
+  const int ntiles = (p.n_rows + 127) / 128;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  grid_dep_launch();  // the first stage may set itself up meanwhile; it waits before reading the lists
+  int *list = lists + (long long)f * list_stride;
+  int running = 0;
+  for (int base = 0; base < ntiles; base += 1024 * K) {
+    bool on[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int t = base + (wid * K + k) * 32 + lane;
+      on[k] = t < ntiles && ((wgrad_tile_mask(p, t) >> f) & 1u);
+    }
+    int mine = 0;
+#pragma unroll
+    for (int k = 0; k < K; ++k)
+      mine += __popc(__ballot_sync(0xffffffffu, on[k]));
+    __syncthreads();  // s_w of the previous batch has been read
+    if (lane == 0)
+      s_w[wid] = mine;
+    __syncthreads();
+    int before = 0, all = 0;
+    for (int w = 0; w < 32; ++w) {
+      const int v = s_w[w];
+      all += v;
+      if (w < wid)
+        before += v;
+    }
+    int pos = running + before;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const uint32_t bal = __ballot_sync(0xffffffffu, on[k]);
+      if (on[k])
+        list[pos + __popc(bal & ((1u << lane) - 1u))] = base + (wid * K + k) * 32 + lane;
+      pos += __popc(bal);
+    }
+    running += all;
+  }
+  if (threadIdx.x == 0)
+    p.sched[f] = running;
+}
+
+// Per CTA, in shared memory: s_plan[0] = number of units of this CTA, then five ints per unit
+// {f, first list index, one past the last, unit number, offset of its tiles in s_tiles};
+// s_tiles = the CTA's tiles in step order (when they fit; otherwise the walk reads the lists).
+constexpr int kWgradPlanInts = 8 + 5 * 32;
+template <int TILE_CAP>
+__device__ __forceinline__ void wgrad_load_plan(const WgradParams &p, const int *lists, int list_stride, int *s_plan,
+                                                int *s_tiles) {
+  const int G = gridDim.x, c = blockIdx.x;
   if (threadIdx.x < 32) {
     const int f = threadIdx.x;
-    const int cnt = (f < p.kv) ? s_sched[f] : 0;
-    int total = cnt, nf = cnt > 0 ? 1 : 0;
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) {
-      total += __shfl_xor_sync(0xffffffffu, total, d);
-      nf += __shfl_xor_sync(0xffffffffu, nf, d);
+    const int cnt = (f < p.kv) ? __ldg(p.sched + f) : 0;
+    int P, T, c_first, S, U;
+    wgrad_plan_warp(cnt, G, P, T, c_first, S, U);
+    if (c == 0 && blockIdx.y == 0) {
+      p.sched[32 + f] = S;
+      p.sched[64 + f] = U;
     }
-    // S_f ~ cnt_f / total of the CTAs left after every present offset got one; the sum stays
-    // within the grid so that no CTA gets a second unit (unless there are more offsets than CTAs)
-    const int G = gridDim.x;
-    const int spare = max(G - nf, 0);
-    int S = 0;
-    if (cnt > 0) {
-      S = 1 + (int)(((float)cnt * (float)spare) / (float)total);
-      S = max(1, min(S, min(cnt, G)));
+    const int b0 = (int)(((long long)c * T) / G), b1 = (int)(((long long)(c + 1) * T) / G);
+    const bool has = cnt > 0 && c >= c_first && c < c_first + S;
+    int k0 = 0, k1 = 0;
+    if (has) {
+      k0 = max(b0, P) - P;
+      k1 = min(b1, P + cnt) - P;
+      if (k1 < k0)
+        k1 = k0;
     }
-    int incl = S;
+    const uint32_t bal = __ballot_sync(0xffffffffu, has);
+    int len_incl = k1 - k0;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
-      const int v = __shfl_up_sync(0xffffffffu, incl, d);
+      const int v = __shfl_up_sync(0xffffffffu, len_incl, d);
       if (f >= d)
-        incl += v;
+        len_incl += v;
     }
-    __syncwarp();
-    s_sched[f] = S;
-    s_sched[32 + f] = incl - S;
-    if (f == 31)
-      s_sched[64] = incl;
+    const int total_len = __shfl_sync(0xffffffffu, len_incl, 31);
+    if (has) {
+      int *e = s_plan + 8 + 5 * __popc(bal & ((1u << f) - 1u));
+      e[0] = f;
+      e[1] = k0;
+      e[2] = k1;
+      e[3] = U + (c - c_first);
+      e[4] = len_incl - (k1 - k0);
+    }
+    if (f == 0) {
+      s_plan[0] = __popc(bal);
+      s_plan[1] = total_len <= TILE_CAP ? 1 : 0;  // tiles are staged in shared memory
+    }
   }
   __syncthreads();
-  // unit table and bitmaps of this CTA's first MAX_UNITS units
-  const int total_units = s_sched[64];
-  int word_off = 0;
-  for (int k = 0; k < MAX_UNITS; ++k) {
-    const int u = blockIdx.x + k * gridDim.x;
-    if (u >= total_units)
-      break;
-    int f = 0;
-    while (f < 31 && !(u >= s_sched[32 + f] && u < s_sched[32 + f] + s_sched[f]))
-      ++f;
-    const int S = s_sched[f], si = u - s_sched[32 + f];
-    const int t0 = (int)(((long long)ntiles * si) / S);
-    const int t1 = (int)(((long long)ntiles * (si + 1)) / S);
-    const int w0 = t0 >> 5, w1 = (t1 + 31) >> 5;
-    const int nwords = (t1 > t0 && word_off + (w1 - w0) <= BITMAP_WORDS) ? (w1 - w0) : 0;
-    if (threadIdx.x == 0) {
-      s_sched[96 + 4 * k] = f;
-      s_sched[96 + 4 * k + 1] = w0;
-      s_sched[96 + 4 * k + 2] = word_off;
-      s_sched[96 + 4 * k + 3] = nwords;
-    }
-    if (nwords > 0) {
-      // warp-per-word: lane l tests tile 32*w + l
-      const int nwarps = blockDim.x >> 5, wid = threadIdx.x >> 5, ln = threadIdx.x & 31;
-#pragma unroll
-      for (int kk = 0; kk < MAXK; ++kk) {
-        const int w = kk * nwarps + wid;  // word that mk[kk] belongs to (tile = kk*blockDim + tid)
-        const int t = w * 32 + ln;
-        const bool on = t >= t0 && t < t1 && ((mk[kk] >> f) & 1u);
-        const uint32_t bal = __ballot_sync(0xffffffffu, on);
-        if (ln == 0 && w >= w0 && w < w1)
-          bitmap[word_off + w - w0] = bal;
-      }
-      for (int w = MAXK * nwarps + wid; w < w1; w += nwarps) {
-        const int t = w * 32 + ln;
-        const uint32_t m = (t < ntiles) ? wgrad_tile_mask(p, t) : 0u;
-        const bool on = t >= t0 && t < t1 && ((m >> f) & 1u);
-        const uint32_t bal = __ballot_sync(0xffffffffu, on);
-        if (ln == 0 && w >= w0)
-          bitmap[word_off + w - w0] = bal;
-      }
-      word_off += nwords;
+  if (s_plan[1]) {
+    const int n = s_plan[0];
+    for (int j = 0; j < n; ++j) {
+      const int *e = s_plan + 8 + 5 * j;
+      const int *src = lists + (long long)e[0] * list_stride + e[1];
+      for (int i = threadIdx.x; i < e[2] - e[1]; i += blockDim.x)
+        s_tiles[e[4] + i] = __ldg(src + i);
     }
   }
   __syncthreads();
 }
 
-// Walk the active tiles of this CTA's units.  on_unit(u, f) at unit start, on_tile(tile, f,
-// first_of_unit) for each tile carrying f, on_unit_end(u, f, n_active).
-template <int MAX_UNITS, class UnitFn, class TileFn, class EndFn>
-__device__ __forceinline__ void wgrad_walk(const WgradParams &p, int ntiles, const int *s_sched,
-                                           const uint32_t *bitmap, UnitFn on_unit, TileFn on_tile,
-                                           EndFn on_unit_end) {
-  const int total = s_sched[64];
-  int k = 0;
-  for (int u = blockIdx.x; u < total; u += gridDim.x, ++k) {
-    int f, w0 = 0, woff = 0, nwords = 0;
-    if (k < MAX_UNITS) {
-      f = s_sched[96 + 4 * k];
-      w0 = s_sched[96 + 4 * k + 1];
-      woff = s_sched[96 + 4 * k + 2];
-      nwords = s_sched[96 + 4 * k + 3];
-    } else {
-      f = 0;
-      while (f < 31 && !(u >= s_sched[32 + f] && u < s_sched[32 + f] + s_sched[f]))
-        ++f;
-    }
+// Walk this CTA's units.  on_unit(u, f) at unit start, on_tile(tile, f, first_of_unit) for each
+// of its tiles, on_unit_end(u, f, n_tiles).  Every role runs the identical walk.
+template <class UnitFn, class TileFn, class EndFn>
+__device__ __forceinline__ void wgrad_walk(const int *lists, int list_stride, const int *s_plan, const int *s_tiles,
+                                           UnitFn on_unit, TileFn on_tile, EndFn on_unit_end) {
+  const int n = s_plan[0];
+  const bool staged = s_plan[1] != 0;
+  for (int j = 0; j < n; ++j) {
+    const int *e = s_plan + 8 + 5 * j;
+    const int f = e[0], k0 = e[1], k1 = e[2], u = e[3], toff = e[4];
     if (!on_unit(u, f))
       return;
-    int active = 0;
-    if (nwords > 0) {
-      for (int w = 0; w < nwords; ++w) {
-        uint32_t bits = bitmap[woff + w];
-        while (bits) {
-          const int j = __ffs(bits) - 1;
-          bits &= bits - 1;
-          if (!on_tile((w0 + w) * 32 + j, f, active == 0))
-            return;
-          ++active;
-        }
-      }
-    } else {
-      // no bitmap (more units or tiles than the bitmap holds): scan the masks in global memory
-      const int S = s_sched[f];
-      const int si = u - s_sched[32 + f];
-      const int t0 = (int)(((long long)ntiles * si) / S);
-      const int t1 = (int)(((long long)ntiles * (si + 1)) / S);
-      for (int tb = t0; tb < t1; tb += 32) {
-        const int t = tb + (int)lane_id();
-        uint32_t m = (t < t1) ? wgrad_tile_mask(p, t) : 0u;
-        uint32_t ball = __ballot_sync(0xffffffffu, (m >> f) & 1u);
-        while (ball) {
-          const int j = __ffs(ball) - 1;
-          ball &= ball - 1;
-          if (!on_tile(tb + j, f, active == 0))
-            return;
-          ++active;
-        }
-      }
+    const int *src = lists + (long long)f * list_stride + k0;
+    for (int i = 0; i < k1 - k0; ++i) {
+      const int tile = staged ? s_tiles[toff + i] : __ldg(src + i);
+      if (!on_tile(tile, f, i == 0))
+        return;
     }
-    if (!on_unit_end(u, f, active))
+    if (!on_unit_end(u, f, k1 - k0))
       return;
   }
 }
@@ -282,13 +273,15 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
              const WgradParams p) {
   using Cfg = WgradCfg<BLOCK_N, GATHER>;
   extern __shared__ uint8_t smem_raw[];
+  if (threadIdx.x == 0)
+    CB2_TRACE_CTA(0, 0);
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
   uint8_t *smem = smem_raw + pad;
   const uint32_t sbase = raw_addr + pad;
   int *rowidx = reinterpret_cast<int *>(smem + Cfg::OFF_ROWIDX);
-  int *s_sched = reinterpret_cast<int *>(smem + Cfg::OFF_SCHED);
-  uint32_t *bitmap = reinterpret_cast<uint32_t *>(smem + Cfg::OFF_BITMAP);
+  int *s_plan = reinterpret_cast<int *>(smem + Cfg::OFF_SCHED);
+  int *s_tiles = reinterpret_cast<int *>(smem + Cfg::OFF_TILES);
   volatile int *misc = reinterpret_cast<volatile int *>(smem + Cfg::OFF_MISC);
   volatile int *abort_flag = misc + 1;
   const uint32_t bars = sbase + Cfg::OFF_BARS;
@@ -300,7 +293,6 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int ntiles = (p.n_rows + 127) / 128;
   const int n_tiles_n = (p.n_total + BLOCK_N - 1) / BLOCK_N;
   const int mt = blockIdx.y / n_tiles_n, nt = blockIdx.y % n_tiles_n;
   const int m0 = mt * 128, n0 = nt * BLOCK_N;
@@ -326,15 +318,15 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
   }
   if (threadIdx.x == 0)
     CB2_TRACE_EVENT(5, 10, 0);
-  wgrad_build_schedule<Cfg::MAX_UNITS, Cfg::BITMAP_WORDS>(p, ntiles, s_sched, bitmap);  // contains __syncthreads
+  grid_dep_launch();  // lets the second stage be scheduled as soon as SMs free up
+  grid_dep_wait();    // counts and lists come from the planning kernel
+  wgrad_load_plan<Cfg::TILE_CAP>(p, p.lists, p.list_stride, s_plan, s_tiles);  // contains __syncthreads
   if (threadIdx.x == 0)
     CB2_TRACE_EVENT(5, 11, 0);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = static_cast<uint32_t>(misc[0]);
-  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x < 96)
-    p.sched[threadIdx.x] = s_sched[threadIdx.x];
 
   auto fail = [&](int code) {
     *abort_flag = 1;
@@ -347,14 +339,17 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
     // ======================= epilogue: one fp32 partial per unit
     const int et = threadIdx.x;
     int acc_use = 0;
-    wgrad_walk<Cfg::MAX_UNITS>(
-        p, ntiles, s_sched, bitmap, [&](int, int) -> bool { return true; },
+    wgrad_walk(
+        p.lists, p.list_stride, s_plan, s_tiles, [&](int, int) -> bool { return true; },
         [&](int, int, bool) -> bool { return true; },
         [&](int u, int f, int active) -> bool {
-          if (et == 0)
-            p.unit_flags[(long long)u * gy + blockIdx.y] = active > 0 ? 1 : 0;
-          if (active == 0)
+          if (active == 0) {
+            // a unit without tiles (fewer steps than CTAs) still owns a partial: all zeros
+            uint4 *dst = reinterpret_cast<uint4 *>(p.partials + ((long long)u * gy + blockIdx.y) * 128 * BLOCK_N) + et;
+            for (int q = 0; q < BLOCK_N / 4; ++q)
+              dst[q * 128] = make_uint4(0u, 0u, 0u, 0u);
             return true;
+          }
           const int buf = acc_use & 1;
           if (et == 0) {
             CB2_TRACE_EVENT(4, 7, u);
@@ -394,8 +389,8 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
     constexpr uint32_t idesc = make_idesc(0, true, true, 128, BLOCK_N);
     int step = 0, acc_use = 0;
     bool ok_all = true;
-    wgrad_walk<Cfg::MAX_UNITS>(
-        p, ntiles, s_sched, bitmap, [&](int, int) -> bool { return true; },
+    wgrad_walk(
+        p.lists, p.list_stride, s_plan, s_tiles, [&](int, int) -> bool { return true; },
         [&](int tile, int f, bool first) -> bool {
           const int buf = acc_use & 1;
           int ok = 1;
@@ -446,6 +441,8 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
           }
           return true;
         });
+    if (lane == 0)
+      CB2_TRACE_CTA(2, (unsigned long long)step);
     if (lane == 0 && ok_all) {
       tc_commit(final_bar);
       if (!mbar_wait(final_bar, 0, abort_flag))
@@ -464,8 +461,8 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
     const uint8_t *a_bytes = reinterpret_cast<const uint8_t *>(p.dout);
     const uint8_t *b_bytes = reinterpret_cast<const uint8_t *>(p.x);
     constexpr int CPR_B = BLOCK_N / 8;  // 16-byte chunks per B row (fp16)
-    wgrad_walk<Cfg::MAX_UNITS>(
-        p, ntiles, s_sched, bitmap, [&](int, int) -> bool { return true; },
+    wgrad_walk(
+        p.lists, p.list_stride, s_plan, s_tiles, [&](int, int) -> bool { return true; },
         [&](int tile, int f, bool) -> bool {
           const bool mine = (step % Cfg::SA) == g;
           const int use = step / Cfg::SA;
@@ -587,6 +584,8 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
 
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0)
+    CB2_TRACE_CTA(1, 0);
   if (warp == 4) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
@@ -598,7 +597,6 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
 struct WgradReduceParams {
   const float *partials;
   const int *sched;
-  const int *unit_flags;
   void *out;
   const void *src;
   long long ldo;       // elements between consecutive m rows of out
@@ -606,6 +604,7 @@ struct WgradReduceParams {
   int m_total, n_total, kv;
   int block_n;
   int gy;              // m_tiles * n_tiles of the first stage
+  int G;               // CTAs per (m, n) tile of the first stage: fixes the unit numbering
   uint32_t mask_filter;
   float alpha, beta;
   int out_f32;
@@ -618,13 +617,13 @@ struct WgradReduceParams {
 // for 32 float4, and the 8 sums are combined in a fixed order.  No atomics: deterministic.
 __global__ void __launch_bounds__(256) wgrad_reduce_kernel(const WgradReduceParams p) {
   __shared__ float4 s_part[8][32];
-  __shared__ int s_flags[512];
   // blocks are dispatched in blockIdx order: start with the centre offset, which carries by
   // far the most units in a submanifold convolution, so its blocks are not left for the tail
   const int f = (blockIdx.y + p.kv / 2) % p.kv;
   if (!((p.mask_filter >> f) & 1u))
     return;
-  const int S = p.sched[f], base = p.sched[32 + f];
+  grid_dep_wait();  // partials and unit ranges come from the first stage
+  const int S = p.sched[32 + f], base = p.sched[64 + f];
   const int bn4 = p.block_n >> 2;
   const long long E4 = (long long)p.gy * bn4 * 128;
   const bool split = S > 8;
@@ -640,27 +639,17 @@ __global__ void __launch_bounds__(256) wgrad_reduce_kernel(const WgradReducePara
   const bool in_range = e4 < E4;
   const int by = in_range ? (int)(e4 / (bn4 * 128)) : 0;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int s0 = 0; s0 < S; s0 += 512) {
-    const int cnt = min(512, S - s0);
-    __syncthreads();
-    // a block's elements share one (m-tile, n-tile) pair `by`: 32 or 256 consecutive e4 never
-    // straddle a multiple of block_n/4 * 128 >= 2048
-    for (int i = threadIdx.x; i < cnt; i += blockDim.x)
-      s_flags[i] = p.unit_flags[(long long)(base + s0 + i) * p.gy + by];
-    __syncthreads();
-    if (in_range) {
-      const float4 *src = reinterpret_cast<const float4 *>(p.partials) + (long long)(base + s0) * E4 + e4;
-      const int first = split ? wid : 0, stride = split ? 8 : 1;
+  if (in_range) {
+    // every unit owns a partial (all zeros if it had no tiles), so the sum is a plain strided read
+    const float4 *src = reinterpret_cast<const float4 *>(p.partials) + (long long)base * E4 + e4;
+    const int first = split ? wid : 0, stride = split ? 8 : 1;
 #pragma unroll 8
-      for (int s = first; s < cnt; s += stride) {
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (s_flags[s])
-          v = __ldg(src + (long long)s * E4);
-        acc.x += v.x;
-        acc.y += v.y;
-        acc.z += v.z;
-        acc.w += v.w;
-      }
+    for (int s = first; s < S; s += stride) {
+      const float4 v = __ldg(src + (long long)s * E4);
+      acc.x += v.x;
+      acc.y += v.y;
+      acc.z += v.z;
+      acc.w += v.w;
     }
   }
   float r[4] = {acc.x, acc.y, acc.z, acc.w};
