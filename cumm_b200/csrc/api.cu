@@ -146,6 +146,34 @@ int gather_mode() {
   return mode;
 }
 
+// Launch with programmatic stream serialisation: the kernel may be scheduled while its
+// predecessor on the stream is still running and synchronises with it through
+// griddepcontrol.wait in its own code.  `level` 1: the chain of the three weight-gradient
+// kernels, where it measurably shortens the gaps; level 2: the row kernels, where it measured
+// neutral and is therefore off unless CUMM_B200_PDL=2.  CUMM_B200_PDL=0 launches everything the
+// ordinary way.
+template <class Kern, class... Args>
+cudaError_t launch_after(int level, Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                         Args... args) {
+  static const int enabled = [] {
+    const char *v = getenv("CUMM_B200_PDL");
+    return v ? atoi(v) : 1;
+  }();
+  const bool pdl = enabled >= level;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN, bool TMA_GATHER>
 int launch_rowconv_inst(const CUtensorMap &map, const CUtensorMap &map_a, const RowConvParams &p, int grid_x,
                         int grid_y, cudaStream_t stream) {
@@ -158,8 +186,7 @@ int launch_rowconv_inst(const CUtensorMap &map, const CUtensorMap &map_a, const 
     CB2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     configured.fetch_or(1ull << dev);
   }
-  kern<<<dim3(grid_x, grid_y), Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(map, map_a, p);
-  CB2_CUDA(cudaGetLastError());
+  CB2_CUDA(launch_after(2, kern, dim3(grid_x, grid_y), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, stream, map, map_a, p));
   g_launches.fetch_add(1);
   return CB2_OK;
 }
@@ -293,29 +320,6 @@ void wgrad_layout(int num_sms, int m_total, int n_total, long long n_rows, int k
   L->total = L->off_lists + (size_t)(kv > 0 ? kv : 1) * L->list_stride * 4;
 }
 
-// Launch with programmatic stream serialisation: the kernel may be scheduled while its
-// predecessor on the stream is still running and synchronises with it through
-// griddepcontrol.wait in its own code.  CUMM_B200_PDL=0 launches the ordinary way.
-template <class Kern, class... Args>
-cudaError_t launch_after(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
-  static const bool pdl = [] {
-    const char *v = getenv("CUMM_B200_PDL");
-    return !(v && v[0] == '0');
-  }();
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = grid;
-  cfg.blockDim = block;
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, kern, args...);
-}
-
 template <int BLOCK_N, int GATHER>
 int launch_wgrad_inst(const CUtensorMap &ma, const CUtensorMap &mb, const WgradParams &p, int gx, int gy,
                       cudaStream_t stream) {
@@ -328,7 +332,7 @@ int launch_wgrad_inst(const CUtensorMap &ma, const CUtensorMap &mb, const WgradP
     CB2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     configured.fetch_or(1ull << dev);
   }
-  CB2_CUDA(launch_after(kern, dim3(gx, gy), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, stream, ma, mb, p));
+  CB2_CUDA(launch_after(1, kern, dim3(gx, gy), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, stream, ma, mb, p));
   g_launches.fetch_add(1);
   return CB2_OK;
 }
@@ -395,7 +399,7 @@ int run_wgrad(DeviceState *dev, WgradParams &p, void *workspace, size_t workspac
   r.out_f32 = out_f32;
   const long long e4 = (long long)L.gy * (L.block_n / 4) * 128;
   const int bx = (int)((e4 + 31) / 32);
-  CB2_CUDA(launch_after(wgrad_reduce_kernel, dim3(bx, p.kv), dim3(256), 0, stream, r));
+  CB2_CUDA(launch_after(1, wgrad_reduce_kernel, dim3(bx, p.kv), dim3(256), 0, stream, r));
   g_launches.fetch_add(1);
   return CB2_OK;
 }

@@ -429,6 +429,12 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   if (threadIdx.x == 0)
     CB2_TRACE_CTA(0, 0);
+  // Programmatic dependent launch: the next kernel on the stream may be scheduled onto SMs as
+  // they free up, and this one may itself have started before its predecessor finished.  What
+  // runs ahead is the set-up, the scheduler's tickets and mask words and the first row-index
+  // loads -- tables no kernel of this library writes.  Every role calls grid_dep_wait() before
+  // it first touches operand rows, weights or the output.
+  grid_dep_launch();
   // 1024-byte alignment: required by the 128-byte swizzle atoms of TMA and tcgen05.
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -525,12 +531,17 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
     constexpr int SWZ = (CPR >= 8 ? 8 : CPR) - 1;
     constexpr int CH_PER_ROUND = 32 * Cfg::OES / 16;   // chunks produced per 32 columns
     int acc_use = 0;
+    bool dep_waited = false;
     CB2_PROF_BEGIN();
     walk_steps(
         p, rv, kpasses,
         [&](int tile, const int *sl, uint32_t kmask_store, bool has_work) -> bool {
           if (et == 0)
             CB2_PROF_MARK(0);  // walk
+          if (!dep_waited) {
+            grid_dep_wait();
+            dep_waited = true;
+          }
           const int o = (p.mode == kModeMaskConv) ? sl[8 + erow] : sl[136 + erow];  // destination row of this thread's tile row
           if (et == 0 && p.mask_out && blockIdx.y == 0)
             p.mask_out[tile] = kmask_store;
@@ -854,6 +865,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
     int bcount = 0, last_key = -1;
     if (lane == 0) {
     tma_prefetch_desc(&tmap_b);
+    grid_dep_wait();
     walk_steps_single(
         p, rv, kpasses, [&](int, const int *, uint32_t, bool) -> bool { return true; },
         [&](int tile, int f, int kp, bool, bool) -> bool {
@@ -919,6 +931,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
       fence_proxy_async_smem();
       __syncwarp();
       uint32_t dirty = 0;  // quads of this stage that hold gathered rows
+      bool dep_waited = false;
       int step = 0;
       int o[4] = {-1, -1, -1, -1};
       walk_steps(
@@ -958,6 +971,10 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
                 fail(kStatusWaitTimeout);
               return false;
             }
+            if (!dep_waited) {
+              grid_dep_wait();
+              dep_waited = true;
+            }
             const bool wanted = (idx[0] & idx[1] & idx[2] & idx[3]) >= 0;  // some row index is not -1
             const uint32_t need = __ballot_sync(0xffffffffu, wanted);
             if (((dirty >> lane) & 1u) && !wanted) {
@@ -992,6 +1009,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
       const int row0 = gt / CPR;
       int *group_rowidx = rowidx + g * 256;  // two buffers, alternating per use of the stage
       volatile int *my_flag = misc + 3 + g;
+      bool dep_waited = false;
       int step = 0;
       int o[RPT];
 #pragma unroll
@@ -1048,6 +1066,10 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
             named_bar_sync(2 + g, Cfg::GROUP_THREADS);
             if (*my_flag == 0)
               return false;
+            if (!dep_waited) {
+              grid_dep_wait();
+              dep_waited = true;
+            }
             const uint32_t a_stage = sbase + Cfg::OFF_A + g * Cfg::A_STAGE_BYTES;
             const int byte_off = kp * Cfg::KRED * Cfg::ES + c * 16;
             const bool col_ok = byte_off < p.red * Cfg::ES;
