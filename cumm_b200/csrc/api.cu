@@ -148,9 +148,9 @@ int gather_mode() {
 
 // Launch with programmatic stream serialisation: the kernel may be scheduled while its
 // predecessor on the stream is still running and synchronises with it through
-// griddepcontrol.wait in its own code.  `level` 1: the chain of the three weight-gradient
-// kernels, where it measurably shortens the gaps; level 2: the row kernels, where it measured
-// neutral and is therefore off unless CUMM_B200_PDL=2.  CUMM_B200_PDL=0 launches everything the
+// griddepcontrol.wait in its own code.  `level` 1 (on by default): the chain of the three
+// weight-gradient kernels and the gather-GEMM-scatter calls; level 2 (only with
+// CUMM_B200_PDL=2): the convolution row kernels.  CUMM_B200_PDL=0 launches everything the
 // ordinary way.
 template <class Kern, class... Args>
 cudaError_t launch_after(int level, Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
@@ -186,7 +186,11 @@ int launch_rowconv_inst(const CUtensorMap &map, const CUtensorMap &map_a, const 
     CB2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     configured.fetch_or(1ull << dev);
   }
-  CB2_CUDA(launch_after(2, kern, dim3(grid_x, grid_y), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, stream, map, map_a, p));
+  // A gather-GEMM-scatter call is one of a run of small kernels (one per filter offset), where
+  // overlapping each kernel's set-up with its predecessor's tail nearly halves the run; for the
+  // one-kernel convolutions it measured neutral to slightly worse.
+  CB2_CUDA(launch_after(p.mode == kModeMaskConv ? 2 : 1, kern, dim3(grid_x, grid_y), dim3(Cfg::THREADS),
+                        Cfg::SMEM_BYTES, stream, map, map_a, p));
   g_launches.fetch_add(1);
   return CB2_OK;
 }
