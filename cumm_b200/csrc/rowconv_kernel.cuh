@@ -69,6 +69,9 @@ struct RowConvParams {
 #ifndef CB2_ROWCONV_EPI_PARTS
 #define CB2_ROWCONV_EPI_PARTS 4
 #endif
+#ifndef CB2_ROWCONV_XU_SHARE
+#define CB2_ROWCONV_XU_SHARE 2
+#endif
 #ifndef CB2_ROWCONV_EPI_PIPE
 #define CB2_ROWCONV_EPI_PIPE 0
 #endif
@@ -155,6 +158,14 @@ __device__ __forceinline__ uint32_t cvt_sat_s8(float t) {
       : "=f"(c)
       : "f"(t));
   return __float_as_uint(__fadd_rn(c, 12582912.0f));
+}
+// The same conversion as one instruction of the conversion unit.  That unit is slow but idle
+// otherwise, so the epilogue sends part of the elements through it and the rest through the
+// arithmetic pipes, which then work side by side.
+__device__ __forceinline__ uint32_t cvt_sat_s8_xu(float t) {
+  int r;
+  asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(t));
+  return static_cast<uint32_t>(r);
 }
 // low bytes of a, b, c, d -> one word (three byte-permutes instead of masks, shifts and ors)
 __device__ __forceinline__ uint32_t pack_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
@@ -705,8 +716,16 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
               }
 #pragma unroll
               for (int i = 0; i < 32; i += 4)
+#if CB2_ROWCONV_XU_SHARE == 2
+                packed[i / 4] = pack_low_bytes(cvt_sat_s8(t[i]), cvt_sat_s8_xu(t[i + 1]), cvt_sat_s8(t[i + 2]),
+                                               cvt_sat_s8_xu(t[i + 3]));
+#elif CB2_ROWCONV_XU_SHARE == 1
+                packed[i / 4] = pack_low_bytes(cvt_sat_s8(t[i]), cvt_sat_s8(t[i + 1]), cvt_sat_s8(t[i + 2]),
+                                               cvt_sat_s8_xu(t[i + 3]));
+#else
                 packed[i / 4] = pack_low_bytes(cvt_sat_s8(t[i]), cvt_sat_s8(t[i + 1]), cvt_sat_s8(t[i + 2]),
                                                cvt_sat_s8(t[i + 3]));
+#endif
 #pragma unroll
               for (int q = 0; q < 2; ++q) {
                 const int c = (col0 / 32) * CH_PER_ROUND + q;

@@ -139,7 +139,7 @@ __device__ __forceinline__ void wgrad_plan_warp(int cnt, int G, int &P, int &T, 
 // contiguous span of tiles, so the list comes out in ascending order with one block-wide
 // synchronisation per batch of 1024 * K tiles.
 __global__ void __launch_bounds__(1024) wgrad_plan_kernel(const WgradParams p, int *lists, int list_stride) {
-  constexpr int K = 4;
+  constexpr int K = 4;  // 4096 tiles per batch
   __shared__ int s_w[32];
   const int f = blockIdx.x;
   const int ntiles = (p.n_rows + 127) / 128;
