@@ -556,9 +556,9 @@ def config1_gather_gemm(torch, dev, stream, coords, time_calls, hbm_peak, nsets)
     d.dtype_a = d.dtype_b = d.dtype_c = float16
     d.dacc = d.dcomp = float32
     d.trans_a, d.trans_b, d.trans_c = False, True, False
-    d.tile_shape = [128, 128, 64]
-    d.warp_tile_shape = [128, 128, 64]
-    d.tensorop = [128, 128, 16]
+    d.tile_shape = [128, 64, 64]  # C = K = 64: the narrowest tiles
+    d.warp_tile_shape = [128, 64, 64]
+    d.tensorop = [128, 64, 16]
     d.num_stage = 3
     d.algo = "Blackwell"
     d.shuffle_type = ShuffleStrideType.ShuffleAC

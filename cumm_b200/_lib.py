@@ -52,6 +52,7 @@ class GemmArgs(ctypes.Structure):
         ("shuffle_type", ctypes.c_int),
         ("d_is_vector", ctypes.c_int),
         ("rows_A", ctypes.c_int), ("rows_B", ctypes.c_int),
+        ("tile_n", ctypes.c_int), ("tile_k", ctypes.c_int),
     ]
 
 
@@ -85,6 +86,7 @@ class ConvArgs(ctypes.Structure):
         ("is_int8_inference", ctypes.c_int),
         ("rows_A", ctypes.c_int), ("rows_B", ctypes.c_int),
         ("mask_words", ctypes.c_int),
+        ("tile_n", ctypes.c_int), ("tile_k", ctypes.c_int),
     ]
 
 

@@ -202,12 +202,20 @@ struct RowConvPlan {
   bool b_mn;
 };
 
-int plan_rowconv(int kind, int red, int nn, bool b_mn, RowConvPlan *plan) {
+// tile_n / tile_k: GemmAlgoDesp::tile_shape[1] / [2] of the caller's descriptor (0 = choose from the
+// problem: the narrowest tile that covers the output width / the reduction width).
+int plan_rowconv(int kind, int red, int nn, bool b_mn, int tile_n, int tile_k, RowConvPlan *plan) {
   plan->kind = kind;
   plan->b_mn = b_mn;
   const int atom = kind == 0 ? 64 : 128;
-  plan->natom_k = (kind == 0 && red > atom) ? 2 : 1;
-  plan->block_n = nn <= 64 ? 64 : 128;
+  if (tile_n != 0 && tile_n != 64 && tile_n != 128)
+    return set_err(CB2_ERR_UNSUPPORTED, "can't find any suitable algo: tile_shape[1] = %d (kernels exist for 64 and 128)",
+                   tile_n);
+  if (tile_k != 0 && tile_k != atom && !(kind == 0 && tile_k == 2 * atom))
+    return set_err(CB2_ERR_UNSUPPORTED, "can't find any suitable algo: tile_shape[2] = %d (kernels exist for %d%s)",
+                   tile_k, atom, kind == 0 ? " and 128" : "");
+  plan->natom_k = tile_k ? tile_k / atom : ((kind == 0 && red > atom) ? 2 : 1);
+  plan->block_n = tile_n ? tile_n : (nn <= 64 ? 64 : 128);
   if (kind == 1 && b_mn)
     return set_err(CB2_ERR_UNSUPPORTED, "int8 is supported for forward only (the reference skips 1-byte "
                                         "dtypes for backward ops)");
@@ -236,11 +244,11 @@ int launch_rowconv(const RowConvPlan &pl, const CUtensorMap &map, const CUtensor
 }
 
 // Common tail of the row-gather launches (forward, backward input, ShuffleAC GEMM).
-int run_rowconv(DeviceState *dev, RowConvParams &p, int kind, bool b_mn, const void *w_ptr, uint64_t w_inner,
-                uint64_t w_mid, uint64_t w_outer, uint64_t w_mid_stride, uint64_t w_outer_stride,
-                cudaStream_t stream) {
+int run_rowconv(DeviceState *dev, RowConvParams &p, int kind, bool b_mn, int tile_n, int tile_k, const void *w_ptr,
+                uint64_t w_inner, uint64_t w_mid, uint64_t w_outer, uint64_t w_mid_stride,
+                uint64_t w_outer_stride, cudaStream_t stream) {
   RowConvPlan pl;
-  int rc = plan_rowconv(kind, p.red, p.nn, b_mn, &pl);
+  int rc = plan_rowconv(kind, p.red, p.nn, b_mn, tile_n, tile_k, &pl);
   if (rc)
     return rc;
   const int es = kind == 0 ? 2 : 1;
@@ -307,8 +315,8 @@ struct WgradLayout {
 // Workspace of the weight gradient: 512-byte header (tile counts per offset), unit flags,
 // fp32 partials (one per unit: at most G + kv - 1 <= G + 32), and per offset the list of the
 // row tiles that carry it.
-void wgrad_layout(int num_sms, int m_total, int n_total, long long n_rows, int kv, WgradLayout *L) {
-  L->block_n = n_total <= 64 ? 64 : 128;
+void wgrad_layout(int num_sms, int m_total, int n_total, long long n_rows, int kv, int tile_n, WgradLayout *L) {
+  L->block_n = (tile_n == 64 || tile_n == 128) ? tile_n : (n_total <= 64 ? 64 : 128);
   const int mt = (m_total + 127) / 128, nt = (n_total + L->block_n - 1) / L->block_n;
   L->gy = mt * nt;
   L->G = num_sms / L->gy;
@@ -341,11 +349,13 @@ int launch_wgrad_inst(const CUtensorMap &ma, const CUtensorMap &mb, const WgradP
   return CB2_OK;
 }
 
-int run_wgrad(DeviceState *dev, WgradParams &p, void *workspace, size_t workspace_bytes, void *out,
+int run_wgrad(DeviceState *dev, WgradParams &p, int tile_n, void *workspace, size_t workspace_bytes, void *out,
               const void *src, long long ldo, long long f_stride, float alpha, float beta, int out_f32,
               cudaStream_t stream) {
+  CB2_CHECK_RT(tile_n == 0 || tile_n == 64 || tile_n == 128,
+               "can't find any suitable algo: tile_shape[1] = %d (kernels exist for 64 and 128)", tile_n);
   WgradLayout L;
-  wgrad_layout(dev->num_sms, p.m_total, p.n_total, p.n_rows, p.kv, &L);
+  wgrad_layout(dev->num_sms, p.m_total, p.n_total, p.n_rows, p.kv, tile_n, &L);
   CB2_CHECK_RT(workspace != nullptr && workspace_bytes >= L.total, "workspace at least %zu bytes.", L.total);
   CB2_CHECK_ARG(reinterpret_cast<uintptr_t>(workspace) % 256 == 0, "workspace must be 256-byte aligned");
   CB2_CHECK_ARG(p.m_total % 8 == 0 && p.n_total % 8 == 0, "channel counts must be multiples of 8");
@@ -511,7 +521,7 @@ size_t cb2_gemm_workspace_size(const cb2_gemm_args *a) {
   if (get_device(&dev))
     return 0;
   WgradLayout L;
-  wgrad_layout(dev->num_sms, a->m, a->n, a->k, 1, &L);
+  wgrad_layout(dev->num_sms, a->m, a->n, a->k, 1, a->tile_n, &L);
   return L.total;
 }
 
@@ -522,7 +532,7 @@ size_t cb2_conv_workspace_size(const cb2_conv_args *a) {
   if (get_device(&dev))
     return 0;
   WgradLayout L;
-  wgrad_layout(dev->num_sms, a->K, a->C, a->N, a->kernel_volume, &L);
+  wgrad_layout(dev->num_sms, a->K, a->C, a->N, a->kernel_volume, a->tile_n, &L);
   return L.total;
 }
 
@@ -548,7 +558,7 @@ int cb2_conv_backward_weight_static(const cb2_conv_args *a, void *stream_v) {
   const int need_words = (a->N + a->mask_width - 1) / a->mask_width;
   CB2_CHECK_RT(a->mask_words >= need_words, "reduced mask has %d words, %d needed", a->mask_words, need_words);
   WgradLayout L;
-  wgrad_layout(st->dev.num_sms, a->K, a->C, a->N, a->kernel_volume, &L);
+  wgrad_layout(st->dev.num_sms, a->K, a->C, a->N, a->kernel_volume, a->tile_n, &L);
   CB2_CHECK_RT(L.total <= kStaticScratchBytes,
                "this problem (K=%d, C=%d, N=%d) needs %zu bytes of scratch; the static scratch holds %zu. Use "
                "cb2_conv_run with a caller-provided workspace instead.",
@@ -574,7 +584,7 @@ int cb2_conv_backward_weight_static(const cb2_conv_args *a, void *stream_v) {
   p.mode = kWgradMaskConv;
   // every unit flag and partial the second stage reads is rewritten by the first stage of
   // the same call, so nothing has to be cleared between calls
-  return run_wgrad(&st->dev, p, st->scratch, kStaticScratchBytes, a->ptr_C, a->ptr_D,
+  return run_wgrad(&st->dev, p, a->tile_n, st->scratch, kStaticScratchBytes, a->ptr_C, a->ptr_D,
                    (long long)a->kernel_volume * a->C, a->C, a->alpha, a->beta, a->dtype_c == CB2_DTYPE_F32 ? 1 : 0,
                    stream);
 }
@@ -629,7 +639,7 @@ int cb2_gemm_run(const cb2_gemm_args *a, void *stream_v) {
     p.mask_width = 128;
     p.mask_filter = 0xffffffffu;
     p.mode = kWgradPairList;
-    return run_wgrad(dev, p, a->workspace, a->workspace_bytes, a->ptr_C, a->ptr_D, a->stride_C, 0, a->alpha,
+    return run_wgrad(dev, p, a->tile_n, a->workspace, a->workspace_bytes, a->ptr_C, a->ptr_D, a->stride_C, 0, a->alpha,
                      a->beta, 0, stream);
   }
   CB2_CHECK_RT(a->shuffle_type == CB2_SHUFFLE_AC || a->shuffle_type == CB2_SHUFFLE_NONE, "unknown shuffle type %d",
@@ -668,7 +678,7 @@ int cb2_gemm_run(const cb2_gemm_args *a, void *stream_v) {
   const bool b_mn = !a->trans_b;
   const uint64_t inner = b_mn ? a->n : a->k;
   const uint64_t outer = b_mn ? a->k : a->n;
-  return run_rowconv(dev, p, 0, b_mn, a->ptr_B, inner, 1, outer, a->stride_B, a->stride_B, stream);
+  return run_rowconv(dev, p, 0, b_mn, a->tile_n, a->tile_k, a->ptr_B, inner, 1, outer, a->stride_B, a->stride_B, stream);
 }
 
 int cb2_conv_run(const cb2_conv_args *a, void *stream_v) {
@@ -722,7 +732,7 @@ int cb2_conv_run(const cb2_conv_args *a, void *stream_v) {
     p.rmask_words = a->mask_words;
     p.mask_filter = a->mask_filter;
     p.mode = kWgradMaskConv;
-    return run_wgrad(dev, p, a->workspace, a->workspace_bytes, a->ptr_C, a->ptr_D,
+    return run_wgrad(dev, p, a->tile_n, a->workspace, a->workspace_bytes, a->ptr_C, a->ptr_D,
                      (long long)a->kernel_volume * a->C, a->C, a->alpha, a->beta,
                      a->dtype_c == CB2_DTYPE_F32 ? 1 : 0, stream);
   }
@@ -765,7 +775,7 @@ int cb2_conv_run(const cb2_conv_args *a, void *stream_v) {
     p.lds = p.nn;
   }
   // weight [K, kv, C]: forward reduces over C (K-major B), backward input over K (MN-major B)
-  return run_rowconv(dev, p, kind, dgrad, a->ptr_B, a->C, a->kernel_volume, a->K, a->C,
+  return run_rowconv(dev, p, kind, dgrad, a->tile_n, a->tile_k, a->ptr_B, a->C, a->kernel_volume, a->K, a->C,
                      (uint64_t)a->kernel_volume * a->C, stream);
 }
 

@@ -16,7 +16,21 @@ from .tensorview.gemm import (ConvAlgoDesp, ConvOpType, ConvParams, PreparedCall
 from .workloads import ConvTables
 
 
-def make_desp(op, int8_inference: bool = False) -> ConvAlgoDesp:
+def default_tile(op, C: int, K: int, int8_inference: bool = False):
+    """The tile shape used when nothing has been tuned: the narrowest column tile that covers the
+    output width and the narrowest reduction tile that covers the reduction width."""
+    op = ConvOpType(int(op))
+    n_width = K if op == ConvOpType.Forward else C
+    red = C if op == ConvOpType.Forward else K
+    tile_n = 64 if n_width <= 64 else 128
+    if op == ConvOpType.BackwardWeight or int8_inference:
+        tile_k = 128
+    else:
+        tile_k = 64 if red <= 64 else 128
+    return [TILE_M, tile_n, tile_k]
+
+
+def make_desp(op, int8_inference: bool = False, C: int = 128, K: int = 128, tile=None) -> ConvAlgoDesp:
     d = ConvAlgoDesp(3, op)
     if int8_inference:
         d.dtype_a = d.dtype_b = d.dtype_c = int8
@@ -29,9 +43,9 @@ def make_desp(op, int8_inference: bool = False) -> ConvAlgoDesp:
     d.trans_a, d.trans_b, d.trans_c = {ConvOpType.Forward: (False, True, False),
                                        ConvOpType.BackwardInput: (False, False, False),
                                        ConvOpType.BackwardWeight: (True, False, False)}[ConvOpType(int(op))]
-    d.tile_shape = [TILE_M, 128, 128]
-    d.warp_tile_shape = [TILE_M, 128, 128]
-    d.tensorop = [128, 128, 32 if int8_inference else 16]
+    d.tile_shape = list(tile) if tile is not None else default_tile(op, C, K, int8_inference)
+    d.warp_tile_shape = list(d.tile_shape)
+    d.tensorop = [128, d.tile_shape[1], 32 if int8_inference else 16]
     d.num_stage = 3
     d.algo = "Blackwell"
     d.split_k_serial = int(op) == ConvOpType.BackwardWeight
@@ -74,14 +88,19 @@ class DeviceTables:
 class SparseConvLayer:
     """Prepared forward / backward-input / backward-weight calls over fixed buffers."""
 
-    def __init__(self, tables: DeviceTables, weight, x, out, dout=None, din=None, dw=None, stream: int = 0):
+    def __init__(self, tables: DeviceTables, weight, x, out, dout=None, din=None, dw=None, stream: int = 0,
+                 tiles=None):
+        """``tiles``: optional {ConvOpType: tile_shape} (e.g. from the tuner); ops without an entry
+        use :func:`default_tile`."""
         self.t = tables
+        tiles = dict(tiles or {})
+        K, C = int(weight.shape[0]), int(weight.shape[2])
         self.fwd: Optional[PreparedCall] = None
         self.dgrad: Optional[PreparedCall] = None
         self.wgrad: Optional[PreparedCall] = None
         int8_inf = str(x.dtype).endswith("int8")
         p = ConvParams(3, ConvOpType.Forward)
-        p.conv_algo_desp = make_desp(ConvOpType.Forward, int8_inf)
+        p.conv_algo_desp = make_desp(ConvOpType.Forward, int8_inf, C, K, tiles.get(ConvOpType.Forward))
         p.input, p.weight, p.output = x, weight, out
         p.indices, p.mask, p.mask_argsort = tables.indices, tables.mask, tables.mask_argsort
         p.mask_output = tables.mask_output
@@ -91,14 +110,14 @@ class SparseConvLayer:
             self.fwd = prepare_conv(p)
         if dout is not None and din is not None:
             q = ConvParams(3, ConvOpType.BackwardInput)
-            q.conv_algo_desp = make_desp(ConvOpType.BackwardInput)
+            q.conv_algo_desp = make_desp(ConvOpType.BackwardInput, False, C, K, tiles.get(ConvOpType.BackwardInput))
             q.input, q.weight, q.output = din, weight, dout
             q.indices, q.mask, q.mask_argsort = tables.indices_bwd, tables.mask_bwd, tables.mask_argsort_bwd
             q.stream = stream
             self.dgrad = prepare_conv(q)
         if dout is not None and dw is not None:
             r = ConvParams(3, ConvOpType.BackwardWeight)
-            r.conv_algo_desp = make_desp(ConvOpType.BackwardWeight)
+            r.conv_algo_desp = make_desp(ConvOpType.BackwardWeight, False, C, K, tiles.get(ConvOpType.BackwardWeight))
             r.input, r.weight, r.output = x, dw, dout
             r.indices, r.mask, r.mask_argsort = tables.indices, tables.mask_output, tables.mask_argsort
             r.mask_width = TILE_M

@@ -579,6 +579,12 @@ def _gemm_args(params: GemmParams) -> _lib.GemmArgs:
     args.shuffle_type = int(desp.shuffle_type)
     args.rows_A = a.dim(0)
     args.rows_B = b.dim(0)
+    # The descriptor selects the kernel: tile_shape = [rows, columns, reduction] of one CTA tile.
+    if desp.tile_shape[0] != 128:
+        raise RuntimeError(f"can't find any suitable algo: tile_shape[0] = {desp.tile_shape[0]} (the sm_100a "
+                           "kernels work on 128-row tiles)")
+    args.tile_n = int(desp.tile_shape[1])
+    args.tile_k = int(desp.tile_shape[2]) if desp.shuffle_type != ShuffleStrideType.ShuffleAB else 0
     args._device = c.device
     return args
 
@@ -697,6 +703,13 @@ def _conv_args(params: ConvParams) -> _lib.ConvArgs:
     if op == ConvOpType.Forward and mask_output is not None:
         if mask_output.size() < _div_up(N, 128):
             raise RuntimeError("mask_output is too small")
+    # The descriptor selects the kernel: tile_shape = [rows, columns, reduction] of one CTA tile
+    # (for backward weight the reduction runs over rows and is tied to mask_width).
+    if desp.tile_shape[0] != 128:
+        raise RuntimeError(f"can't find any suitable algo: tile_shape[0] = {desp.tile_shape[0]} (the sm_100a "
+                           "kernels work on 128-row tiles)")
+    args.tile_n = int(desp.tile_shape[1])
+    args.tile_k = int(desp.tile_shape[2]) if op != ConvOpType.BackwardWeight else 0
     args._device = c_t.device
     return args
 

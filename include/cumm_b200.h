@@ -83,6 +83,10 @@ typedef struct cb2_gemm_args {
   int d_is_vector;
   int rows_A; /* rows addressable in A (bounds for indiceA); rows_B likewise for ShuffleAB */
   int rows_B;
+  /* GemmAlgoDesp::tile_shape[1] and [2] (params.h:24-45): the output columns of one CTA's tile (64 or
+   * 128) and the reduction elements per pipeline stage (fp16: 64 or 128); 0 = chosen from the problem.
+   * This is what a tuner varies.  ShuffleAB uses tile_n only. */
+  int tile_n, tile_k;
 } cb2_gemm_args;
 
 /*
@@ -131,6 +135,9 @@ typedef struct cb2_conv_args {
   int rows_A; /* rows addressable in A; rows_B likewise for backward weight */
   int rows_B;
   int mask_words; /* backward weight: number of reduced-mask words available */
+  /* ConvAlgoDesp::tile_shape[1] and [2], as in cb2_gemm_args; backward weight uses tile_n only.  Int8
+   * kernels exist for tile_k = 128. */
+  int tile_n, tile_k;
 } cb2_conv_args;
 
 /* Launches.  `stream` is a cudaStream_t (the reference passes it as uintptr_t,

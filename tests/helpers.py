@@ -28,9 +28,10 @@ def conv_desp(op, C, K, int8_inference=False):
     ta, tb, tc = {ConvOpType.Forward: (False, True, False), ConvOpType.BackwardInput: (False, False, False),
                   ConvOpType.BackwardWeight: (True, False, False)}[ConvOpType(int(op))]
     d.trans_a, d.trans_b, d.trans_c = ta, tb, tc
-    d.tile_shape = [128, 128, 128]
-    d.warp_tile_shape = [128, 128, 128]
-    d.tensorop = [128, 128, 16]
+    from cumm_b200.layer import default_tile
+    d.tile_shape = default_tile(op, C, K, int8_inference)
+    d.warp_tile_shape = list(d.tile_shape)
+    d.tensorop = [128, d.tile_shape[1], 32 if int8_inference else 16]
     d.num_stage = 3
     d.algo = "Blackwell"
     d.split_k_serial = int(op) == ConvOpType.BackwardWeight
@@ -41,14 +42,15 @@ def conv_desp(op, C, K, int8_inference=False):
     return d
 
 
-def gemm_desp(shuffle, trans_a=False, trans_b=True):
+def gemm_desp(shuffle, trans_a=False, trans_b=True, n=128, k=128):
+    """n, k: output and reduction widths of the problem; the tile is the narrowest that covers them."""
     d = GemmAlgoDesp()
     d.dtype_a = d.dtype_b = d.dtype_c = float16
     d.dacc = d.dcomp = float32
     d.trans_a, d.trans_b, d.trans_c = trans_a, trans_b, False
-    d.tile_shape = [128, 128, 64]
-    d.warp_tile_shape = [128, 128, 64]
-    d.tensorop = [128, 128, 16]
+    d.tile_shape = [128, 64 if n <= 64 else 128, 64 if k <= 64 else 128]
+    d.warp_tile_shape = list(d.tile_shape)
+    d.tensorop = [128, d.tile_shape[1], 16]
     d.num_stage = 3
     d.algo = "Blackwell"
     d.shuffle_type = shuffle
@@ -72,10 +74,11 @@ def mask_to_torch(mask, torch):
 
 
 def run_conv_fwd(torch, x, w, tb, *, out_init=None, beta=0.0, alpha=1.0, bias=None, act=Activation.None_,
-                 act_alpha=0.0, mask_filter=0xFFFFFFFF, want_mask_out=True):
+                 act_alpha=0.0, mask_filter=0xFFFFFFFF, want_mask_out=True, tile=None):
     K, kv, C = w.shape
     p = ConvParams(3, ConvOpType.Forward)
     p.conv_algo_desp = conv_desp(ConvOpType.Forward, C, K)
+    _apply_tile(p, tile)
     p.input = dev(x, torch)
     p.weight = dev(w, torch)
     out = torch.zeros((tb.n_out, K), dtype=torch.float16, device="cuda") if out_init is None else dev(out_init, torch)
@@ -96,10 +99,12 @@ def run_conv_fwd(torch, x, w, tb, *, out_init=None, beta=0.0, alpha=1.0, bias=No
     return out.cpu().numpy(), mo.cpu().numpy().view(np.uint32)
 
 
-def run_conv_dgrad(torch, dout, w, tb, *, din_init=None, beta=0.0, use_reverse=False, mask_filter=0xFFFFFFFF):
+def run_conv_dgrad(torch, dout, w, tb, *, din_init=None, beta=0.0, use_reverse=False, mask_filter=0xFFFFFFFF,
+                   tile=None):
     K, kv, C = w.shape
     p = ConvParams(3, ConvOpType.BackwardInput)
     p.conv_algo_desp = conv_desp(ConvOpType.BackwardInput, C, K)
+    _apply_tile(p, tile)
     din = torch.zeros((tb.n_in, C), dtype=torch.float16, device="cuda") if din_init is None else dev(din_init, torch)
     p.input = din
     p.weight = dev(w, torch)
@@ -122,10 +127,11 @@ def run_conv_dgrad(torch, dout, w, tb, *, din_init=None, beta=0.0, use_reverse=F
 
 
 def run_conv_wgrad(torch, dout, x, tb, reduced_mask, *, kv=27, dw_init=None, beta=0.0, alpha=1.0,
-                   mask_filter=0xFFFFFFFF, mask_width=128, fp32_out=False):
+                   mask_filter=0xFFFFFFFF, mask_width=128, fp32_out=False, tile=None):
     K, C = dout.shape[1], x.shape[1]
     p = ConvParams(3, ConvOpType.BackwardWeight)
     p.conv_algo_desp = conv_desp(ConvOpType.BackwardWeight, C, K)
+    _apply_tile(p, tile)
     p.input = dev(x, torch)
     dt = torch.float32 if fp32_out else torch.float16
     dw = torch.zeros((K, kv, C), dtype=dt, device="cuda") if dw_init is None else dev(dw_init, torch)
@@ -145,10 +151,12 @@ def run_conv_wgrad(torch, dout, x, tb, reduced_mask, *, kv=27, dw_init=None, bet
     return dw.cpu().numpy()
 
 
-def run_conv_s8(torch, x, w, scale, bias, tb, *, output_add=None, beta=0.0, act=Activation.None_, act_alpha=0.0):
+def run_conv_s8(torch, x, w, scale, bias, tb, *, output_add=None, beta=0.0, act=Activation.None_, act_alpha=0.0,
+                tile=None):
     K, kv, C = w.shape
     p = ConvParams(3, ConvOpType.Forward)
     p.conv_algo_desp = conv_desp(ConvOpType.Forward, C, K, int8_inference=True)
+    _apply_tile(p, tile)
     p.input = dev(x, torch)
     p.weight = dev(w, torch)
     out = torch.zeros((tb.n_out, K), dtype=torch.int8, device="cuda")
@@ -165,6 +173,12 @@ def run_conv_s8(torch, x, w, scale, bias, tb, *, output_add=None, beta=0.0, act=
     ConvMainUnitTest.implicit_gemm2(p)
     torch.cuda.synchronize()
     return out.cpu().numpy()
+
+
+def _apply_tile(p, tile):
+    if tile is not None:
+        p.conv_algo_desp.tile_shape = list(tile)
+        p.conv_algo_desp.warp_tile_shape = list(tile)
 
 
 def check_status():

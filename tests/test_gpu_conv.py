@@ -280,3 +280,35 @@ def test_errors_surface_as_exceptions(torch):
     with pytest.raises(RuntimeError, match="CUDA device"):
         ConvMainUnitTest.implicit_gemm2(q)
     H.check_status()
+
+
+def _tiles_for(op, int8=False):
+    return [tuple(d.tile_shape) for d in ConvMainUnitTest.get_all_conv_algo_desp()
+            if d.op_type == op and bool(d.is_int8_inference) == int8]
+
+
+def test_every_listed_tile_shape_computes_the_same(torch, oracle):
+    """The descriptor's tile shape selects the kernel variant (what the tuner varies): every entry of
+    get_all_conv_algo_desp gives the oracle's result."""
+    tb, x, w, dout = make(2500, 611, 128, 128)
+    want_f = oracle.mask_igemm(x, w, np.zeros((tb.n_out, 128), np.float16), tb.indices, tb.mask, tb.mask_argsort)
+    want_d = oracle.mask_igemm(dout, w, np.zeros((tb.n_in, 128), np.float16), tb.indices_bwd, tb.mask_bwd,
+                               tb.mask_argsort_bwd, is_dgrad=True)
+    tiles_f, tiles_d, tiles_w = (_tiles_for(ConvOpType.Forward), _tiles_for(ConvOpType.BackwardInput),
+                                 _tiles_for(ConvOpType.BackwardWeight))
+    assert len(tiles_f) == 4 and len(tiles_d) == 4 and len(tiles_w) == 2
+    mo = None
+    for t in tiles_f:
+        got, mo = H.run_conv_fwd(torch, x, w, tb, tile=t)
+        H.check_status()
+        H.assert_close_f16(got, want_f, f"forward tile {t}")
+    for t in tiles_d:
+        got = H.run_conv_dgrad(torch, dout, w, tb, tile=t)
+        H.check_status()
+        H.assert_close_f16(got, want_d, f"dgrad tile {t}")
+    want_w = oracle.mask_igemm_wgrad(dout, x, np.zeros((128, 27, 128), np.float16), tb.indices, mo, tb.mask_argsort)
+    for t in tiles_w:
+        got = H.run_conv_wgrad(torch, dout, x, tb, mo, tile=t)
+        H.check_status()
+        s = max(1.0, float(np.sqrt(tb.n_out)))
+        H.assert_close_f16(got / s, want_w.astype(np.float32) / s, f"wgrad tile {t}")

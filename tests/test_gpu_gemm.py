@@ -24,7 +24,7 @@ def test_dense_gemm_simulator_sized(torch, oracle):
     a = rng.uniform(-1, 1, (128, 64)).astype(np.float32).astype(np.float16)
     b = rng.uniform(-1, 1, (64, 128)).astype(np.float32).astype(np.float16)
     p = GemmParams()
-    p.algo_desp = H.gemm_desp(ShuffleStrideType.NoShuffle, trans_b=False)
+    p.algo_desp = H.gemm_desp(ShuffleStrideType.NoShuffle, trans_b=False, n=128, k=64)
     p.a, p.b = H.dev(a, torch), H.dev(b, torch)
     c = torch.zeros((128, 128), dtype=torch.float16, device="cuda")
     p.c = c
@@ -46,7 +46,7 @@ def test_shuffle_ac(torch, oracle, m, k, n, trans_b):
     ci = rng.permutation(rows_c)[:m].astype(np.int32)
     c0 = rng.uniform(-1, 1, (rows_c, n)).astype(np.float16)
     p = GemmParams()
-    p.algo_desp = H.gemm_desp(ShuffleStrideType.ShuffleAC, trans_b=trans_b)
+    p.algo_desp = H.gemm_desp(ShuffleStrideType.ShuffleAC, trans_b=trans_b, n=n, k=k)
     p.a, p.b = H.dev(a, torch), H.dev(b, torch)
     c = H.dev(c0, torch)
     p.c = c
@@ -71,7 +71,7 @@ def test_shuffle_ac_beta_bias_act(torch, oracle):
     c0 = rng.uniform(-1, 1, (2200, n)).astype(np.float16)
     for d, beta, act in ((None, 1.0, Activation.None_), ("bias", 1.0, Activation.ReLU), ("rows", 0.5, Activation.LeakyReLU)):
         p = GemmParams()
-        p.algo_desp = H.gemm_desp(ShuffleStrideType.ShuffleAC)
+        p.algo_desp = H.gemm_desp(ShuffleStrideType.ShuffleAC, n=n, k=k)
         p.a, p.b = H.dev(a, torch), H.dev(b, torch)
         c = H.dev(c0, torch)
         p.c = c
@@ -111,7 +111,7 @@ def test_native_sparse_conv_as_27_gemm_calls(torch, oracle):
         oracle.gemm_shuffle_ac(x, np.ascontiguousarray(w[:, f, :]), want, i_idx.astype(np.int32),
                                o_idx.astype(np.int32), beta=1.0)
         p = GemmParams()
-        p.algo_desp = H.gemm_desp(ShuffleStrideType.ShuffleAC, trans_b=True)
+        p.algo_desp = H.gemm_desp(ShuffleStrideType.ShuffleAC, trans_b=True, n=K, k=C)
         p.a = xd
         p.b = wd[:, f, :]  # [K, C] view with row stride kv*C
         p.c = out
@@ -136,7 +136,7 @@ def test_shuffle_ab(torch, oracle, kk, m, n):
     ai = rng.permutation(rows)[:kk].astype(np.int32)
     bi = rng.permutation(rows)[:kk].astype(np.int32)
     p = GemmParams()
-    p.algo_desp = H.gemm_desp(ShuffleStrideType.ShuffleAB, trans_a=True, trans_b=False)
+    p.algo_desp = H.gemm_desp(ShuffleStrideType.ShuffleAB, trans_a=True, trans_b=False, n=n)
     p.a, p.b = H.dev(a, torch), H.dev(b, torch)
     c = torch.zeros((m, n), dtype=torch.float16, device="cuda")
     p.c = c
@@ -159,7 +159,7 @@ def test_out_of_range_row_index_sets_status_not_fault(torch):
     ai = np.arange(50, dtype=np.int32)
     ai[7] = 100000
     p = GemmParams()
-    p.algo_desp = H.gemm_desp(ShuffleStrideType.ShuffleAC)
+    p.algo_desp = H.gemm_desp(ShuffleStrideType.ShuffleAC, n=64, k=64)
     p.a, p.b = H.dev(a, torch), H.dev(b, torch)
     p.c = torch.zeros((50, 64), dtype=torch.float16, device="cuda")
     p.a_inds, p.c_inds = H.dev(ai, torch), H.dev(np.arange(50, dtype=np.int32), torch)
@@ -167,3 +167,40 @@ def test_out_of_range_row_index_sets_status_not_fault(torch):
     assert _lib.device_status() == 2
     assert _lib.device_status() == 0
     assert (p.c[7] == 0).all()
+
+
+@pytest.mark.parametrize("tile_n,tile_k", [(64, 64), (64, 128), (128, 64), (128, 128)])
+def test_shuffle_ac_every_tile_shape(torch, oracle, tile_n, tile_k):
+    """The descriptor's tile shape selects the kernel variant; all of them compute the same thing."""
+    rng = np.random.default_rng(5)
+    m, k, n = 3000, 128, 128
+    a = rng.uniform(-1, 1, (m + 100, k)).astype(np.float16)
+    b = rng.uniform(-1, 1, (n, k)).astype(np.float16)
+    ai = rng.permutation(m + 100)[:m].astype(np.int32)
+    ci = rng.permutation(m)[:m].astype(np.int32)
+    p = GemmParams()
+    p.algo_desp = H.gemm_desp(ShuffleStrideType.ShuffleAC)
+    p.algo_desp.tile_shape = [128, tile_n, tile_k]
+    p.algo_desp.warp_tile_shape = [128, tile_n, tile_k]
+    p.a, p.b = H.dev(a, torch), H.dev(b, torch)
+    c = torch.zeros((m, n), dtype=torch.float16, device="cuda")
+    p.c = c
+    p.a_inds, p.c_inds = H.dev(ai, torch), H.dev(ci, torch)
+    GemmMainUnitTest.matmul2(p)
+    torch.cuda.synchronize()
+    H.check_status()
+    want = oracle.gemm_shuffle_ac(a, b, np.zeros((m, n), np.float16), ai, ci)
+    H.assert_close_f16(c.cpu().numpy(), want, f"ShuffleAC tile {tile_n}x{tile_k}")
+
+
+def test_unknown_tile_shape_is_refused(torch):
+    p = GemmParams()
+    p.algo_desp = H.gemm_desp(ShuffleStrideType.ShuffleAC)
+    p.algo_desp.tile_shape = [128, 96, 64]
+    p.algo_desp.warp_tile_shape = [128, 96, 64]
+    p.a = torch.zeros((10, 64), dtype=torch.float16, device="cuda")
+    p.b = torch.zeros((64, 64), dtype=torch.float16, device="cuda")
+    p.c = torch.zeros((10, 64), dtype=torch.float16, device="cuda")
+    p.a_inds = p.c_inds = torch.arange(10, dtype=torch.int32, device="cuda")
+    with pytest.raises(RuntimeError, match="can't find any suitable algo"):
+        GemmMainUnitTest.matmul2(p)
