@@ -29,6 +29,9 @@ EXPORTED_SYMBOLS = (
     "cb2_conv_backward_weight_static",
     "cb2_static_scratch_bytes",
     "cb2_static_status",
+    "cb2_pairgen_workspace_size",
+    "cb2_pairgen_count_outputs",
+    "cb2_pairgen_run",
 )
 
 
@@ -90,6 +93,28 @@ class ConvArgs(ctypes.Structure):
     ]
 
 
+class PairgenArgs(ctypes.Structure):
+    """``cb2_pairgen_args``."""
+    _fields_ = [
+        ("in_coords", ctypes.c_void_p),
+        ("n_in", ctypes.c_int),
+        ("batch_size", ctypes.c_int),
+        ("grid", ctypes.c_int * 3),
+        ("ksize", ctypes.c_int * 3), ("stride", ctypes.c_int * 3), ("pad", ctypes.c_int * 3), ("dil", ctypes.c_int * 3),
+        ("subm", ctypes.c_int),
+        ("n_out", ctypes.c_int),
+        ("out_coords", ctypes.c_void_p),
+        ("indices", ctypes.c_void_p),
+        ("mask", ctypes.c_void_p),
+        ("mask_argsort", ctypes.c_void_p),
+        ("indices_bwd", ctypes.c_void_p),
+        ("mask_bwd", ctypes.c_void_p),
+        ("mask_argsort_bwd", ctypes.c_void_p),
+        ("workspace", ctypes.c_void_p),
+        ("workspace_bytes", ctypes.c_size_t),
+    ]
+
+
 _lib = None
 
 
@@ -121,6 +146,12 @@ def load() -> ctypes.CDLL:
     L.cb2_static_scratch_bytes.restype = ctypes.c_size_t
     L.cb2_static_status.restype = ctypes.c_int
     L.cb2_static_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
+    L.cb2_pairgen_workspace_size.restype = ctypes.c_size_t
+    L.cb2_pairgen_workspace_size.argtypes = [ctypes.POINTER(PairgenArgs)]
+    L.cb2_pairgen_count_outputs.restype = ctypes.c_int
+    L.cb2_pairgen_count_outputs.argtypes = [ctypes.POINTER(PairgenArgs), ctypes.POINTER(ctypes.c_int), ctypes.c_void_p]
+    L.cb2_pairgen_run.restype = ctypes.c_int
+    L.cb2_pairgen_run.argtypes = [ctypes.POINTER(PairgenArgs), ctypes.c_void_p]
     _lib = L
     return L
 

@@ -5,7 +5,9 @@
 #include "../../include/cumm_b200.h"
 #include "rowconv_kernel.cuh"
 #include "wgrad_kernel.cuh"
+#include "pairgen_kernels.cuh"
 
+#include <algorithm>
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
@@ -492,6 +494,234 @@ int cb2_debug_read_trace(void *host_dst, size_t bytes) {
   return CB2_OK;
 }
 #endif
+
+} // extern "C" (reopened below, after the helpers of the table builder)
+
+// ---------------------------------------------------------------- neighbour tables on the GPU
+namespace {
+
+struct PairgenLayout {
+  cb2pg::Geometry g;
+  uint32_t cap_in, cap_set;  // hash capacities (powers of two)
+  long long list_cap;        // active outputs a strided conv can have at most
+  long long nmax;            // rows the mask sorts may have to hold
+  int key_bits;
+  size_t off_in_keys, off_in_vals, off_set_keys, off_list_a, off_list_b, off_m, off_v, off_hist, off_counters, total;
+};
+
+size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+uint32_t pow2_at_least(unsigned long long v) {
+  uint32_t c = 64;
+  while (c < v && c < (1u << 31))
+    c <<= 1;
+  return c;
+}
+
+int pairgen_layout(const cb2_pairgen_args *a, PairgenLayout *L) {
+  CB2_CHECK_ARG(a != nullptr, "null arguments");
+  CB2_CHECK_ARG(a->n_in >= 0 && a->batch_size >= 1, "bad n_in / batch_size (%d, %d)", a->n_in, a->batch_size);
+  long long kv = 1, cells = a->batch_size;
+  for (int i = 0; i < 3; ++i) {
+    CB2_CHECK_ARG(a->grid[i] >= 1 && a->ksize[i] >= 1 && a->stride[i] >= 1 && a->dil[i] >= 1 && a->pad[i] >= 0,
+                  "bad geometry on axis %d", i);
+    L->g.grid[i] = a->grid[i];
+    L->g.ksize[i] = a->ksize[i];
+    L->g.stride[i] = a->stride[i];
+    L->g.pad[i] = a->pad[i];
+    L->g.dil[i] = a->dil[i];
+    const int span = a->grid[i] + 2 * a->pad[i] - a->dil[i] * (a->ksize[i] - 1) - 1;
+    L->g.ogrid[i] = a->subm ? a->grid[i] : (span >= 0 ? span / a->stride[i] + 1 : 0);
+    CB2_CHECK_ARG(L->g.ogrid[i] >= 1, "the kernel does not fit the grid on axis %d", i);
+    kv *= a->ksize[i];
+    cells *= L->g.ogrid[i];
+  }
+  CB2_CHECK_RT(kv <= 32, "kernel volume %lld is not supported (masks are 32 bits)", kv);
+  if (a->subm)
+    for (int i = 0; i < 3; ++i)
+      CB2_CHECK_ARG(a->stride[i] == 1, "a submanifold convolution has stride 1");
+  L->g.kv = static_cast<int>(kv);
+  L->g.batch_size = a->batch_size;
+  L->cap_in = pow2_at_least(2ull * static_cast<unsigned long long>(a->n_in));
+  L->list_cap = a->subm ? 0 : std::min<long long>(static_cast<long long>(a->n_in) * kv, cells);
+  CB2_CHECK_RT(L->list_cap < (1ll << 30), "too many candidate outputs (%lld)", L->list_cap);
+  L->cap_set = a->subm ? 0 : pow2_at_least(2ull * static_cast<unsigned long long>(L->list_cap));
+  L->nmax = std::max<long long>(a->subm ? a->n_in : L->list_cap, a->n_in);
+  L->key_bits = 1;
+  while (L->key_bits < 63 && (1ll << L->key_bits) < cells)
+    ++L->key_bits;
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    const size_t at = off;
+    off = align256(off + bytes);
+    return at;
+  };
+  L->off_counters = take(256);
+  L->off_in_keys = take(static_cast<size_t>(L->cap_in) * 8);
+  L->off_in_vals = take(static_cast<size_t>(L->cap_in) * 4);
+  L->off_set_keys = take(static_cast<size_t>(L->cap_set) * 8);
+  L->off_list_a = take(static_cast<size_t>(L->list_cap) * 8);
+  L->off_list_b = take(static_cast<size_t>(L->list_cap) * 8);
+  L->off_m = take(static_cast<size_t>(L->nmax) * 4);
+  L->off_v = take(static_cast<size_t>(L->nmax) * 4);
+  const long long sort_n = std::max<long long>(L->nmax, L->list_cap);
+  L->off_hist = take(static_cast<size_t>(256) * ((sort_n + cb2pg::kSortTile - 1) / cb2pg::kSortTile + 1) * 4);
+  L->total = off;
+  return CB2_OK;
+}
+
+// Stable ascending sort of n keys (and values) on `bits` low bits, 8 per pass, ping-ponging
+// between (k0, v0) and (k1, v1); the result is left in (k1, v1): an extra pass over zero
+// bits (the identity, since the sort is stable) makes the number of passes odd.
+template <typename K, bool HAS_VAL>
+int radix_sort_into_second(K *k0, int *v0, K *k1, int *v1, int n, int bits, int *hist, cudaStream_t s) {
+  if (n <= 0)
+    return CB2_OK;
+  int passes = (bits + 7) / 8;
+  if (passes < 1)
+    passes = 1;
+  if (passes % 2 == 0)
+    ++passes;
+  const int ntiles = (n + cb2pg::kSortTile - 1) / cb2pg::kSortTile;
+  K *ks = k0, *kd = k1;
+  int *vs = v0, *vd = v1;
+  for (int p = 0; p < passes; ++p) {
+    const int shift = 8 * p;
+    if (shift >= static_cast<int>(sizeof(K)) * 8) {
+      // nothing left to sort on: the identity permutation
+      CB2_CUDA(cudaMemcpyAsync(kd, ks, sizeof(K) * n, cudaMemcpyDeviceToDevice, s));
+      if (HAS_VAL)
+        CB2_CUDA(cudaMemcpyAsync(vd, vs, sizeof(int) * n, cudaMemcpyDeviceToDevice, s));
+    } else {
+      cb2pg::sort_hist_kernel<K><<<ntiles, cb2pg::kSortThreads, 0, s>>>(ks, n, shift, hist, ntiles);
+      cb2pg::sort_scan_kernel<<<1, 1024, 0, s>>>(hist, 256 * ntiles);
+      cb2pg::sort_scatter_kernel<K, HAS_VAL><<<ntiles, cb2pg::kSortThreads, 0, s>>>(ks, vs, kd, vd, n, shift, hist, ntiles);
+      CB2_CUDA(cudaGetLastError());
+      g_launches.fetch_add(3);
+    }
+    std::swap(ks, kd);
+    std::swap(vs, vd);
+  }
+  return CB2_OK;
+}
+
+int pairgen_common(const cb2_pairgen_args *a, PairgenLayout *L, DeviceState **dev) {
+  int rc = get_device(dev);
+  if (rc)
+    return rc;
+  rc = pairgen_layout(a, L);
+  if (rc)
+    return rc;
+  CB2_CHECK_RT(a->in_coords != nullptr || a->n_in == 0, "in_coords must not empty");
+  CB2_CHECK_ARG(aligned16(a->in_coords), "in_coords must be 16-byte aligned");
+  CB2_CHECK_RT(a->workspace != nullptr && a->workspace_bytes >= L->total, "workspace at least %zu bytes.", L->total);
+  CB2_CHECK_ARG(reinterpret_cast<uintptr_t>(a->workspace) % 256 == 0, "workspace must be 256-byte aligned");
+  return CB2_OK;
+}
+
+} // namespace
+
+extern "C" {
+
+size_t cb2_pairgen_workspace_size(const cb2_pairgen_args *a) {
+  PairgenLayout L;
+  if (pairgen_layout(a, &L))
+    return 0;
+  return L.total;
+}
+
+int cb2_pairgen_count_outputs(const cb2_pairgen_args *a, int *n_out, void *stream_v) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  PairgenLayout L;
+  DeviceState *dev;
+  int rc = pairgen_common(a, &L, &dev);
+  if (rc)
+    return rc;
+  CB2_CHECK_ARG(n_out != nullptr, "n_out must not be null");
+  if (a->subm || a->n_in == 0) {
+    *n_out = a->n_in;
+    return CB2_OK;
+  }
+  uint8_t *ws = reinterpret_cast<uint8_t *>(a->workspace);
+  int *counter = reinterpret_cast<int *>(ws + L.off_counters);
+  unsigned long long *set_keys = reinterpret_cast<unsigned long long *>(ws + L.off_set_keys);
+  unsigned long long *list_a = reinterpret_cast<unsigned long long *>(ws + L.off_list_a);
+  unsigned long long *list_b = reinterpret_cast<unsigned long long *>(ws + L.off_list_b);
+  CB2_CUDA(cudaMemsetAsync(counter, 0, 256, stream));
+  CB2_CUDA(cudaMemsetAsync(set_keys, 0xFF, static_cast<size_t>(L.cap_set) * 8, stream));
+  const long long threads = static_cast<long long>(a->n_in) * L.g.kv;
+  cb2pg::out_candidates_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(
+      a->in_coords, a->n_in, L.g, set_keys, L.cap_set - 1, list_b, static_cast<int>(L.list_cap), counter, dev->status);
+  CB2_CUDA(cudaGetLastError());
+  g_launches.fetch_add(1);
+  int count = 0;
+  CB2_CUDA(cudaMemcpyAsync(&count, counter, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  CB2_CUDA(cudaStreamSynchronize(stream));
+  CB2_CHECK_RT(count >= 0 && count <= L.list_cap, "active-output count %d out of range", count);
+  rc = radix_sort_into_second<unsigned long long, false>(list_b, nullptr, list_a, nullptr, count, L.key_bits,
+                                                         reinterpret_cast<int *>(ws + L.off_hist), stream);
+  if (rc)
+    return rc;
+  *n_out = count;
+  return CB2_OK;
+}
+
+int cb2_pairgen_run(const cb2_pairgen_args *a, void *stream_v) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  PairgenLayout L;
+  DeviceState *dev;
+  int rc = pairgen_common(a, &L, &dev);
+  if (rc)
+    return rc;
+  const int n_in = a->n_in;
+  const int n_out = a->subm ? n_in : a->n_out;
+  CB2_CHECK_ARG(n_out >= 0 && n_out <= L.nmax, "n_out %d out of range", n_out);
+  if (n_out == 0)
+    return CB2_OK;
+  CB2_CHECK_RT(a->indices && a->mask && a->mask_argsort, "error: indices, mask or mask_argsort empty");
+  CB2_CHECK_RT(a->subm || a->out_coords, "out_coords must not empty");
+  CB2_CHECK_ARG(a->subm || aligned16(a->out_coords), "out_coords must be 16-byte aligned");
+  const bool bwd = a->indices_bwd != nullptr;
+  CB2_CHECK_RT(!bwd || (a->mask_bwd && a->mask_argsort_bwd), "error: backward mask or mask_argsort empty");
+  uint8_t *ws = reinterpret_cast<uint8_t *>(a->workspace);
+  unsigned long long *in_keys = reinterpret_cast<unsigned long long *>(ws + L.off_in_keys);
+  int *in_vals = reinterpret_cast<int *>(ws + L.off_in_vals);
+  uint32_t *m_tmp = reinterpret_cast<uint32_t *>(ws + L.off_m);
+  int *v_tmp = reinterpret_cast<int *>(ws + L.off_v);
+  int *hist = reinterpret_cast<int *>(ws + L.off_hist);
+  CB2_CUDA(cudaMemsetAsync(in_keys, 0xFF, static_cast<size_t>(L.cap_in) * 8, stream));
+  CB2_CUDA(cudaMemsetAsync(in_vals, 0x7F, static_cast<size_t>(L.cap_in) * 4, stream));
+  cb2pg::hash_insert_kernel<<<(n_in + 255) / 256, 256, 0, stream>>>(a->in_coords, n_in, L.g, in_keys, in_vals,
+                                                                     L.cap_in - 1, dev->status);
+  const int32_t *out_coords = a->in_coords;
+  if (!a->subm) {
+    cb2pg::decode_out_coords_kernel<<<(n_out + 255) / 256, 256, 0, stream>>>(
+        reinterpret_cast<const unsigned long long *>(ws + L.off_list_a), n_out, L.g, a->out_coords);
+    out_coords = a->out_coords;
+    g_launches.fetch_add(1);
+  }
+  cb2pg::probe_kernel<<<(n_out + 255) / 256, 256, 0, stream>>>(out_coords, n_out, L.g, in_keys, in_vals, L.cap_in - 1,
+                                                                a->indices, m_tmp, v_tmp);
+  CB2_CUDA(cudaGetLastError());
+  g_launches.fetch_add(2);
+  rc = radix_sort_into_second<uint32_t, true>(m_tmp, v_tmp, a->mask, a->mask_argsort, n_out, L.g.kv, hist, stream);
+  if (rc)
+    return rc;
+  if (bwd) {
+    CB2_CUDA(cudaMemsetAsync(a->indices_bwd, 0xFF, static_cast<size_t>(L.g.kv) * n_in * 4, stream));
+    const long long threads = static_cast<long long>(n_out) * L.g.kv;
+    cb2pg::invert_table_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(
+        a->indices, n_out, L.g.kv, n_in, a->indices_bwd);
+    cb2pg::mask_from_table_kernel<<<(n_in + 255) / 256, 256, 0, stream>>>(a->indices_bwd, n_in, L.g.kv, m_tmp, v_tmp);
+    CB2_CUDA(cudaGetLastError());
+    g_launches.fetch_add(2);
+    rc = radix_sort_into_second<uint32_t, true>(m_tmp, v_tmp, a->mask_bwd, a->mask_argsort_bwd, n_in, L.g.kv, hist,
+                                                stream);
+    if (rc)
+      return rc;
+  }
+  return CB2_OK;
+}
 
 const char *cb2_last_error(void) { return g_err.c_str(); }
 

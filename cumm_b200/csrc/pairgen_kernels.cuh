@@ -1,0 +1,290 @@
+// Neighbour tables of a sparse convolution, built on the GPU: input-voxel hash table, active
+// output voxels of a strided convolution, indices[f, o], neighbour masks, the stable sort of the
+// outputs by mask, and the same for the backward direction.
+//
+// This is the step BEFORE the convolution kernels.  It is not part of cumm itself (its callers
+// build these tables with cumm's hash headers, include/tensorview/hash/hash.cu.h:43-263 and
+// include/tensorview/hash/ops.h:24-150); the table convention is the one the convolution kernels
+// read (include/tensorview/gemm/core/nvrtc_params.h:38-65): indices [kv, N_out] in original row
+// order with -1 for a missing neighbour, filter offsets in (z, y, x) row-major order, bit f of a
+// row's mask set iff it has a neighbour at offset f, rows sorted by mask value with a STABLE
+// sort, active outputs of a strided convolution ordered by their linearised (batch, z, y, x).
+// Everything is integer work on HBM-resident arrays: coalesced passes, no tensor cores.
+// All loops are bounded: a probe sequence visits at most `capacity` slots and reports a full
+// table through the status word instead of spinning.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace cb2pg {
+
+constexpr unsigned long long kEmptyKey = ~0ULL;
+enum : int { kStatusTableFull = 3, kStatusBadCoord = 4 };
+
+struct Geometry {
+  int grid[3];    // input grid (z, y, x)
+  int ogrid[3];   // output grid
+  int ksize[3], stride[3], pad[3], dil[3];
+  int kv;
+  int batch_size;
+};
+
+__device__ __forceinline__ uint32_t mix64(unsigned long long k) {
+  k ^= k >> 33;
+  k *= 0xff51afd7ed558ccdULL;
+  k ^= k >> 33;
+  k *= 0xc4ceb9fe1a85ec53ULL;
+  k ^= k >> 33;
+  return static_cast<uint32_t>(k);
+}
+
+__device__ __forceinline__ unsigned long long linear_key(int b, int z, int y, int x, const int (&g)[3]) {
+  return ((static_cast<unsigned long long>(b) * g[0] + z) * g[1] + y) * g[2] + x;
+}
+
+// ---------------------------------------------------------------- hash table: key -> smallest row
+__global__ void __launch_bounds__(256) hash_insert_kernel(const int32_t *__restrict__ coords, int n, Geometry g,
+                                                          unsigned long long *keys, int *vals, uint32_t cap_mask,
+                                                          int *status) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n)
+    return;
+  const int4 c = reinterpret_cast<const int4 *>(coords)[i];
+  if (c.x < 0 || c.x >= g.batch_size || c.y < 0 || c.y >= g.grid[0] || c.z < 0 || c.z >= g.grid[1] || c.w < 0 ||
+      c.w >= g.grid[2]) {
+    atomicCAS(status, 0, kStatusBadCoord);
+    return;
+  }
+  const unsigned long long key = linear_key(c.x, c.y, c.z, c.w, g.grid);
+  uint32_t slot = mix64(key) & cap_mask;
+  for (uint32_t probe = 0; probe <= cap_mask; ++probe) {
+    const unsigned long long prev = atomicCAS(keys + slot, kEmptyKey, key);
+    if (prev == kEmptyKey || prev == key) {
+      atomicMin(vals + slot, i);  // duplicates resolve to the first row, as a stable sort + search does
+      return;
+    }
+    slot = (slot + 1) & cap_mask;
+  }
+  atomicCAS(status, 0, kStatusTableFull);
+}
+
+__device__ __forceinline__ int hash_find(const unsigned long long *__restrict__ keys, const int *__restrict__ vals,
+                                         uint32_t cap_mask, unsigned long long key) {
+  uint32_t slot = mix64(key) & cap_mask;
+  for (uint32_t probe = 0; probe <= cap_mask; ++probe) {
+    const unsigned long long k = __ldg(keys + slot);
+    if (k == key)
+      return __ldg(vals + slot);
+    if (k == kEmptyKey)
+      return -1;
+    slot = (slot + 1) & cap_mask;
+  }
+  return -1;
+}
+
+// ---------------------------------------------------------------- active outputs of a strided conv
+// One thread per (input voxel, filter offset): the output position that reads this input
+// through this offset, if there is one.  New positions are appended (unordered) to `list`.
+__global__ void __launch_bounds__(256) out_candidates_kernel(const int32_t *__restrict__ coords, int n, Geometry g,
+                                                             unsigned long long *set_keys, uint32_t cap_mask,
+                                                             unsigned long long *list, int list_cap, int *counter,
+                                                             int *status) {
+  const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= static_cast<long long>(n) * g.kv)
+    return;
+  const int i = static_cast<int>(t / g.kv), f = static_cast<int>(t % g.kv);
+  const int4 c = reinterpret_cast<const int4 *>(coords)[i];
+  const int r[3] = {f / (g.ksize[1] * g.ksize[2]), (f / g.ksize[2]) % g.ksize[1], f % g.ksize[2]};
+  const int in[3] = {c.y, c.z, c.w};
+  int q[3];
+#pragma unroll
+  for (int a = 0; a < 3; ++a) {
+    const int num = in[a] + g.pad[a] - r[a] * g.dil[a];
+    if (num < 0 || num % g.stride[a] != 0)
+      return;
+    q[a] = num / g.stride[a];
+    if (q[a] >= g.ogrid[a])
+      return;
+  }
+  if (c.x < 0 || c.x >= g.batch_size)
+    return;  // reported by the insert kernel
+  const unsigned long long key = linear_key(c.x, q[0], q[1], q[2], g.ogrid);
+  uint32_t slot = mix64(key) & cap_mask;
+  for (uint32_t probe = 0; probe <= cap_mask; ++probe) {
+    const unsigned long long prev = atomicCAS(set_keys + slot, kEmptyKey, key);
+    if (prev == key)
+      return;
+    if (prev == kEmptyKey) {
+      const int at = atomicAdd(counter, 1);
+      if (at < list_cap)
+        list[at] = key;
+      else
+        atomicCAS(status, 0, kStatusTableFull);
+      return;
+    }
+    slot = (slot + 1) & cap_mask;
+  }
+  atomicCAS(status, 0, kStatusTableFull);
+}
+
+__global__ void __launch_bounds__(256) decode_out_coords_kernel(const unsigned long long *__restrict__ keys, int n,
+                                                                Geometry g, int32_t *out_coords) {
+  const int o = blockIdx.x * blockDim.x + threadIdx.x;
+  if (o >= n)
+    return;
+  unsigned long long k = keys[o];
+  const int x = static_cast<int>(k % g.ogrid[2]);
+  k /= g.ogrid[2];
+  const int y = static_cast<int>(k % g.ogrid[1]);
+  k /= g.ogrid[1];
+  const int z = static_cast<int>(k % g.ogrid[0]);
+  k /= g.ogrid[0];
+  reinterpret_cast<int4 *>(out_coords)[o] = make_int4(static_cast<int>(k), z, y, x);
+}
+
+// ---------------------------------------------------------------- indices[f, o] and masks
+// One thread per output voxel; consecutive threads write consecutive columns of every row of
+// the table.  Also writes the row number (the value array of the sort that follows).
+__global__ void __launch_bounds__(256) probe_kernel(const int32_t *__restrict__ out_coords, int n_out, Geometry g,
+                                                    const unsigned long long *__restrict__ keys,
+                                                    const int *__restrict__ vals, uint32_t cap_mask,
+                                                    int32_t *indices, uint32_t *mask, int32_t *iota) {
+  const int o = blockIdx.x * blockDim.x + threadIdx.x;
+  if (o >= n_out)
+    return;
+  const int4 c = reinterpret_cast<const int4 *>(out_coords)[o];
+  uint32_t m = 0;
+  int f = 0;
+  for (int rz = 0; rz < g.ksize[0]; ++rz) {
+    const int z = c.y * g.stride[0] - g.pad[0] + rz * g.dil[0];
+    for (int ry = 0; ry < g.ksize[1]; ++ry) {
+      const int y = c.z * g.stride[1] - g.pad[1] + ry * g.dil[1];
+      for (int rx = 0; rx < g.ksize[2]; ++rx, ++f) {
+        const int x = c.w * g.stride[2] - g.pad[2] + rx * g.dil[2];
+        int idx = -1;
+        if (z >= 0 && z < g.grid[0] && y >= 0 && y < g.grid[1] && x >= 0 && x < g.grid[2])
+          idx = hash_find(keys, vals, cap_mask, linear_key(c.x, z, y, x, g.grid));
+        indices[static_cast<long long>(f) * n_out + o] = idx;
+        if (idx >= 0 && f < 32)
+          m |= 1u << f;
+      }
+    }
+  }
+  mask[o] = m;
+  iota[o] = o;
+}
+
+// indices_bwd[f, i] = o for every indices[f, o] = i (the table the input gradient walks)
+__global__ void __launch_bounds__(256) invert_table_kernel(const int32_t *__restrict__ indices, int n_out, int kv,
+                                                           int n_in, int32_t *indices_bwd) {
+  const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= static_cast<long long>(n_out) * kv)
+    return;
+  const int f = static_cast<int>(t / n_out), o = static_cast<int>(t % n_out);
+  const int i = indices[t];
+  if (i >= 0 && i < n_in)
+    indices_bwd[static_cast<long long>(f) * n_in + i] = o;
+}
+
+__global__ void __launch_bounds__(256) mask_from_table_kernel(const int32_t *__restrict__ table, int n, int kv,
+                                                              uint32_t *mask, int32_t *iota) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= n)
+    return;
+  uint32_t m = 0;
+  for (int f = 0; f < kv && f < 32; ++f)
+    if (table[static_cast<long long>(f) * n + j] >= 0)
+      m |= 1u << f;
+  mask[j] = m;
+  iota[j] = j;
+}
+
+// ---------------------------------------------------------------- stable LSD radix sort, 8 bits per pass
+// Three kernels per pass: per-tile digit histograms, one exclusive scan over the (digit, tile)
+// matrix, and a scatter in which the warps of a block take turns (in element order) to claim
+// their digits' positions, so equal keys keep their order.
+constexpr int kSortThreads = 256;
+constexpr int kSortItems = 8;
+constexpr int kSortTile = kSortThreads * kSortItems;
+
+template <typename K>
+__global__ void __launch_bounds__(kSortThreads) sort_hist_kernel(const K *__restrict__ keys, int n, int shift,
+                                                                 int *hist, int ntiles) {
+  __shared__ int h[256];
+  h[threadIdx.x] = 0;
+  __syncthreads();
+  const int base = blockIdx.x * kSortTile;
+#pragma unroll
+  for (int it = 0; it < kSortItems; ++it) {
+    const int idx = base + it * kSortThreads + threadIdx.x;
+    if (idx < n)
+      atomicAdd(&h[static_cast<int>((keys[idx] >> shift) & 0xff)], 1);
+  }
+  __syncthreads();
+  hist[threadIdx.x * ntiles + blockIdx.x] = h[threadIdx.x];
+}
+
+// exclusive scan of `total` ints in place, one block
+__global__ void __launch_bounds__(1024) sort_scan_kernel(int *data, int total) {
+  __shared__ int s_sum[1024];
+  const int per = (total + 1023) / 1024;
+  const int lo = threadIdx.x * per, hi = min(lo + per, total);
+  int sum = 0;
+  for (int i = lo; i < hi; ++i)
+    sum += data[i];
+  s_sum[threadIdx.x] = sum;
+  __syncthreads();
+  for (int d = 1; d < 1024; d <<= 1) {
+    const int v = threadIdx.x >= d ? s_sum[threadIdx.x - d] : 0;
+    __syncthreads();
+    s_sum[threadIdx.x] += v;
+    __syncthreads();
+  }
+  int run = s_sum[threadIdx.x] - sum;
+  for (int i = lo; i < hi; ++i) {
+    const int v = data[i];
+    data[i] = run;
+    run += v;
+  }
+}
+
+template <typename K, bool HAS_VAL>
+__global__ void __launch_bounds__(kSortThreads) sort_scatter_kernel(const K *__restrict__ kin, const int *__restrict__ vin,
+                                                                    K *kout, int *vout, int n, int shift,
+                                                                    const int *__restrict__ offsets, int ntiles) {
+  __shared__ int cnt[256];
+  cnt[threadIdx.x] = offsets[threadIdx.x * ntiles + blockIdx.x];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int base = blockIdx.x * kSortTile;
+  for (int it = 0; it < kSortItems; ++it) {
+    const int idx = base + it * kSortThreads + threadIdx.x;
+    const bool valid = idx < n;
+    K key = 0;
+    int val = 0;
+    if (valid) {
+      key = kin[idx];
+      if (HAS_VAL)
+        val = vin[idx];
+    }
+    const unsigned digit = valid ? static_cast<unsigned>((key >> shift) & 0xff) : 0x100u + lane;  // invalid: unique
+    const unsigned peers = __match_any_sync(0xffffffffu, digit);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    const int leader = __ffs(peers) - 1;
+    int claimed = 0;
+    for (int w = 0; w < kSortThreads / 32; ++w) {
+      __syncthreads();
+      if (warp == w && valid && rank == 0) {
+        claimed = cnt[digit];
+        cnt[digit] = claimed + __popc(peers);
+      }
+    }
+    claimed = __shfl_sync(0xffffffffu, claimed, leader);
+    if (valid) {
+      kout[claimed + rank] = key;
+      if (HAS_VAL)
+        vout[claimed + rank] = val;
+    }
+  }
+}
+
+} // namespace cb2pg

@@ -179,6 +179,50 @@ int cb2_conv_backward_weight_static(const cb2_conv_args *args, void *stream);
 size_t cb2_static_scratch_bytes(void);
 int cb2_static_status(int *status);
 
+/*
+ * Neighbour tables of a sparse convolution, built on the GPU -- the step before the calls above.
+ * (No counterpart inside the reference: its callers build these tables on top of its hash
+ * headers, include/tensorview/hash/hash.cu.h:43-263, ops.h:24-150.  The layout produced is the
+ * one cb2_conv_args consumes, include/tensorview/gemm/core/nvrtc_params.h:38-65.)
+ *
+ * Convention: filter offsets in (z, y, x) row-major order; indices [kv, n_out] int32 in original
+ * row order, -1 = no neighbour; bit f of a row's mask set iff indices[f, row] >= 0; mask [n_out]
+ * holds the masks in ascending order and mask_argsort the rows in that order (stable: equal
+ * masks keep their row order); the active outputs of a strided convolution are ordered by their
+ * linearised (batch, z, y, x).  The backward arrays are the same for the transposed relation
+ * (indices_bwd [kv, n_in], indices_bwd[f, i] = o iff indices[f, o] = i) and may be null.
+ *
+ * Submanifold (subm != 0): outputs are the inputs, n_out = n_in, one call of cb2_pairgen_run.
+ * Otherwise call cb2_pairgen_count_outputs first (it finds and sorts the active outputs inside
+ * the workspace, synchronises the stream and returns their number), size the output arrays,
+ * set n_out and call cb2_pairgen_run with the same workspace.
+ * Kernels report through the status word of cb2_device_status(): 3 = a hash table overflowed
+ * (cannot happen with a workspace of the stated size), 4 = a coordinate outside the grid or
+ * batch.
+ */
+typedef struct cb2_pairgen_args {
+  const int32_t *in_coords; /* [n_in, 4]: batch, z, y, x */
+  int n_in;
+  int batch_size;           /* coordinates' batch index is in [0, batch_size) */
+  int grid[3];              /* input grid extent (z, y, x) */
+  int ksize[3], stride[3], pad[3], dil[3];
+  int subm;
+  int n_out;                /* subm: ignored (= n_in) */
+  int32_t *out_coords;      /* [n_out, 4]; not written when subm */
+  int32_t *indices;         /* [kv, n_out] */
+  uint32_t *mask;           /* [n_out] */
+  int32_t *mask_argsort;    /* [n_out] */
+  int32_t *indices_bwd;     /* [kv, n_in] or null */
+  uint32_t *mask_bwd;       /* [n_in] or null */
+  int32_t *mask_argsort_bwd;/* [n_in] or null */
+  void *workspace;          /* at least cb2_pairgen_workspace_size() bytes, 256-byte aligned */
+  size_t workspace_bytes;
+} cb2_pairgen_args;
+
+size_t cb2_pairgen_workspace_size(const cb2_pairgen_args *args);
+int cb2_pairgen_count_outputs(const cb2_pairgen_args *args, int *n_out, void *stream);
+int cb2_pairgen_run(const cb2_pairgen_args *args, void *stream);
+
 /* Rows of one output tile, i.e. the granularity of mask_out_ptr and the mask_width to
  * hand to backward weight (the reference uses the forward kernel's tile_shape[0],
  * cumm/conv/main_real_spconv.py:176-177). */
@@ -190,7 +234,7 @@ const char *cb2_last_error(void);
 /* Kernels never spin without bound: a wait that runs out, or a row index outside
  * rows_A / rows_B, sets a per-device status word instead.  This call synchronises the
  * current device, returns the word (0 = ok, 1 = wait timed out, 2 = row index out of
- * range) in *status and clears it. */
+ * range; 3 and 4: see cb2_pairgen_args) in *status and clears it. */
 int cb2_device_status(int *status);
 
 /* Number of kernels this library has launched from the calling process (all threads). */
