@@ -533,10 +533,38 @@ def single_scene_configs(torch, dev, stream, reps=20, warm=3):
     res["int8_forward_stride2"] = {"us": us, "eff_tops": ops / us / 1e6, "gbs": b3 / us / 1e3,
                                    "frac_hbm_measured": b3 / us / 1e3 / hbm_peak, "gvoxels_per_s": tb3.n_out / us / 1e3,
                                    "us_warm_l2": warm_us}
+    res["table_generation"] = time_table_generation(torch, dev, stream, coords)
     res["l2"] = f"rotating {NSETS} buffer sets per configuration (> 126 MB L2)"
     res["timing"] = f"CUDA graph of {NSETS} back-to-back launches (one per buffer set), events around a replay, / {NSETS}"
     res["status_word"] = _lib.device_status()
     return res
+
+
+def time_table_generation(torch, dev, stream, coords):
+    """Neighbour tables of the 150 000-voxel scene built on the GPU (hash build, probe, masks,
+    stable sort, backward tables): device time by CUDA events around the whole call, which
+    includes its allocations and, for the strided case, the one synchronisation that returns
+    the number of active outputs."""
+    from cumm_b200 import workloads as W
+    from cumm_b200.pairgen import build_tables_gpu
+    out = {}
+    with torch.cuda.stream(stream):
+        cd = torch.from_numpy(coords).to(dev)
+        for name, kw in (("submanifold", {}), ("stride2", {"stride": (2, 2, 2), "subm": False})):
+            ts = []
+            for i in range(6):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                t = build_tables_gpu(cd, 1, W.GRID, stream=stream.cuda_stream, **kw)
+                b.record(stream)
+                stream.synchronize()
+                if i:
+                    ts.append(a.elapsed_time(b) * 1e3)
+            # int32 traffic the tables amount to: coordinates in, both index tables, masks and orders out
+            nbytes = 16 * t.n_in + 4 * 27 * (t.n_in + t.n_out) + 8 * (t.n_in + t.n_out)
+            us = float(np.median(ts))
+            out[name] = {"us": us, "n_out": t.n_out, "table_bytes": nbytes, "gbs": nbytes / us / 1e3}
+    return out
 
 
 def config1_gather_gemm(torch, dev, stream, coords, time_calls, hbm_peak, nsets):

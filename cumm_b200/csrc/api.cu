@@ -543,7 +543,19 @@ int pairgen_layout(const cb2_pairgen_args *a, PairgenLayout *L) {
   L->g.kv = static_cast<int>(kv);
   L->g.batch_size = a->batch_size;
   L->cap_in = pow2_at_least(2ull * static_cast<unsigned long long>(a->n_in));
-  L->list_cap = a->subm ? 0 : std::min<long long>(static_cast<long long>(a->n_in) * kv, cells);
+  // outputs an input can feed: per axis, the offsets r with (in + pad - r * dil) divisible by the stride
+  long long per_input = 1;
+  for (int i = 0; i < 3; ++i) {
+    int gcd = a->stride[i], b = a->dil[i];
+    while (b) {
+      const int t = gcd % b;
+      gcd = b;
+      b = t;
+    }
+    const int period = a->stride[i] / gcd;  // r takes every period-th value
+    per_input *= std::min(a->ksize[i], (a->ksize[i] + period - 1) / period);
+  }
+  L->list_cap = a->subm ? 0 : std::min<long long>(static_cast<long long>(a->n_in) * per_input, cells);
   CB2_CHECK_RT(L->list_cap < (1ll << 30), "too many candidate outputs (%lld)", L->list_cap);
   L->cap_set = a->subm ? 0 : pow2_at_least(2ull * static_cast<unsigned long long>(L->list_cap));
   L->nmax = std::max<long long>(a->subm ? a->n_in : L->list_cap, a->n_in);
@@ -571,34 +583,27 @@ int pairgen_layout(const cb2_pairgen_args *a, PairgenLayout *L) {
 }
 
 // Stable ascending sort of n keys (and values) on `bits` low bits, 8 per pass, ping-ponging
-// between (k0, v0) and (k1, v1); the result is left in (k1, v1): an extra pass over zero
-// bits (the identity, since the sort is stable) makes the number of passes odd.
+// between the result buffers and the scratch buffers.  The unsorted input has to be where
+// sort_source() says -- the scratch pair for an odd number of passes, the result pair for an
+// even number -- so that the last pass lands in the result buffers.
+inline int sort_passes(int bits) { return bits <= 8 ? 1 : (bits + 7) / 8; }
+template <typename T> T *sort_source(T *result, T *scratch, int bits) {
+  return sort_passes(bits) % 2 ? scratch : result;
+}
 template <typename K, bool HAS_VAL>
-int radix_sort_into_second(K *k0, int *v0, K *k1, int *v1, int n, int bits, int *hist, cudaStream_t s) {
+int radix_sort(K *k_result, int *v_result, K *k_scratch, int *v_scratch, int n, int bits, int *hist, cudaStream_t s) {
   if (n <= 0)
     return CB2_OK;
-  int passes = (bits + 7) / 8;
-  if (passes < 1)
-    passes = 1;
-  if (passes % 2 == 0)
-    ++passes;
+  const int passes = sort_passes(bits);
   const int ntiles = (n + cb2pg::kSortTile - 1) / cb2pg::kSortTile;
-  K *ks = k0, *kd = k1;
-  int *vs = v0, *vd = v1;
+  K *ks = sort_source(k_result, k_scratch, bits), *kd = (ks == k_result) ? k_scratch : k_result;
+  int *vs = sort_source(v_result, v_scratch, bits), *vd = (vs == v_result) ? v_scratch : v_result;
   for (int p = 0; p < passes; ++p) {
-    const int shift = 8 * p;
-    if (shift >= static_cast<int>(sizeof(K)) * 8) {
-      // nothing left to sort on: the identity permutation
-      CB2_CUDA(cudaMemcpyAsync(kd, ks, sizeof(K) * n, cudaMemcpyDeviceToDevice, s));
-      if (HAS_VAL)
-        CB2_CUDA(cudaMemcpyAsync(vd, vs, sizeof(int) * n, cudaMemcpyDeviceToDevice, s));
-    } else {
-      cb2pg::sort_hist_kernel<K><<<ntiles, cb2pg::kSortThreads, 0, s>>>(ks, n, shift, hist, ntiles);
-      cb2pg::sort_scan_kernel<<<1, 1024, 0, s>>>(hist, 256 * ntiles);
-      cb2pg::sort_scatter_kernel<K, HAS_VAL><<<ntiles, cb2pg::kSortThreads, 0, s>>>(ks, vs, kd, vd, n, shift, hist, ntiles);
-      CB2_CUDA(cudaGetLastError());
-      g_launches.fetch_add(3);
-    }
+    cb2pg::sort_hist_kernel<K><<<ntiles, cb2pg::kSortThreads, 0, s>>>(ks, n, 8 * p, hist, ntiles);
+    cb2pg::sort_scan_kernel<<<1, 1024, 0, s>>>(hist, ntiles);
+    cb2pg::sort_scatter_kernel<K, HAS_VAL><<<ntiles, cb2pg::kSortThreads, 0, s>>>(ks, vs, kd, vd, n, 8 * p, hist, ntiles);
+    CB2_CUDA(cudaGetLastError());
+    g_launches.fetch_add(3);
     std::swap(ks, kd);
     std::swap(vs, vd);
   }
@@ -651,15 +656,16 @@ int cb2_pairgen_count_outputs(const cb2_pairgen_args *a, int *n_out, void *strea
   CB2_CUDA(cudaMemsetAsync(set_keys, 0xFF, static_cast<size_t>(L.cap_set) * 8, stream));
   const long long threads = static_cast<long long>(a->n_in) * L.g.kv;
   cb2pg::out_candidates_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(
-      a->in_coords, a->n_in, L.g, set_keys, L.cap_set - 1, list_b, static_cast<int>(L.list_cap), counter, dev->status);
+      a->in_coords, a->n_in, L.g, set_keys, L.cap_set - 1, sort_source(list_a, list_b, L.key_bits),
+      static_cast<int>(L.list_cap), counter, dev->status);
   CB2_CUDA(cudaGetLastError());
   g_launches.fetch_add(1);
   int count = 0;
   CB2_CUDA(cudaMemcpyAsync(&count, counter, sizeof(int), cudaMemcpyDeviceToHost, stream));
   CB2_CUDA(cudaStreamSynchronize(stream));
   CB2_CHECK_RT(count >= 0 && count <= L.list_cap, "active-output count %d out of range", count);
-  rc = radix_sort_into_second<unsigned long long, false>(list_b, nullptr, list_a, nullptr, count, L.key_bits,
-                                                         reinterpret_cast<int *>(ws + L.off_hist), stream);
+  rc = radix_sort<unsigned long long, false>(list_a, nullptr, list_b, nullptr, count, L.key_bits,
+                                             reinterpret_cast<int *>(ws + L.off_hist), stream);
   if (rc)
     return rc;
   *n_out = count;
@@ -701,10 +707,11 @@ int cb2_pairgen_run(const cb2_pairgen_args *a, void *stream_v) {
     g_launches.fetch_add(1);
   }
   cb2pg::probe_kernel<<<(n_out + 255) / 256, 256, 0, stream>>>(out_coords, n_out, L.g, in_keys, in_vals, L.cap_in - 1,
-                                                                a->indices, m_tmp, v_tmp);
+                                                                a->indices, sort_source(a->mask, m_tmp, L.g.kv),
+                                                                sort_source(a->mask_argsort, v_tmp, L.g.kv));
   CB2_CUDA(cudaGetLastError());
   g_launches.fetch_add(2);
-  rc = radix_sort_into_second<uint32_t, true>(m_tmp, v_tmp, a->mask, a->mask_argsort, n_out, L.g.kv, hist, stream);
+  rc = radix_sort<uint32_t, true>(a->mask, a->mask_argsort, m_tmp, v_tmp, n_out, L.g.kv, hist, stream);
   if (rc)
     return rc;
   if (bwd) {
@@ -712,11 +719,12 @@ int cb2_pairgen_run(const cb2_pairgen_args *a, void *stream_v) {
     const long long threads = static_cast<long long>(n_out) * L.g.kv;
     cb2pg::invert_table_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(
         a->indices, n_out, L.g.kv, n_in, a->indices_bwd);
-    cb2pg::mask_from_table_kernel<<<(n_in + 255) / 256, 256, 0, stream>>>(a->indices_bwd, n_in, L.g.kv, m_tmp, v_tmp);
+    cb2pg::mask_from_table_kernel<<<(n_in + 255) / 256, 256, 0, stream>>>(
+        a->indices_bwd, n_in, L.g.kv, sort_source(a->mask_bwd, m_tmp, L.g.kv),
+        sort_source(a->mask_argsort_bwd, v_tmp, L.g.kv));
     CB2_CUDA(cudaGetLastError());
     g_launches.fetch_add(2);
-    rc = radix_sort_into_second<uint32_t, true>(m_tmp, v_tmp, a->mask_bwd, a->mask_argsort_bwd, n_in, L.g.kv, hist,
-                                                stream);
+    rc = radix_sort<uint32_t, true>(a->mask_bwd, a->mask_argsort_bwd, m_tmp, v_tmp, n_in, L.g.kv, hist, stream);
     if (rc)
       return rc;
   }

@@ -90,41 +90,55 @@ __global__ void __launch_bounds__(256) out_candidates_kernel(const int32_t *__re
                                                              unsigned long long *list, int list_cap, int *counter,
                                                              int *status) {
   const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (t >= static_cast<long long>(n) * g.kv)
-    return;
-  const int i = static_cast<int>(t / g.kv), f = static_cast<int>(t % g.kv);
-  const int4 c = reinterpret_cast<const int4 *>(coords)[i];
-  const int r[3] = {f / (g.ksize[1] * g.ksize[2]), (f / g.ksize[2]) % g.ksize[1], f % g.ksize[2]};
-  const int in[3] = {c.y, c.z, c.w};
-  int q[3];
+  bool fresh = false;  // this thread found a position nobody had claimed yet
+  unsigned long long key = 0;
+  if (t < static_cast<long long>(n) * g.kv) {
+    const int i = static_cast<int>(t / g.kv), f = static_cast<int>(t % g.kv);
+    const int4 c = reinterpret_cast<const int4 *>(coords)[i];
+    const int r[3] = {f / (g.ksize[1] * g.ksize[2]), (f / g.ksize[2]) % g.ksize[1], f % g.ksize[2]};
+    const int in[3] = {c.y, c.z, c.w};
+    int q[3];
+    bool ok = c.x >= 0 && c.x < g.batch_size;  // a bad batch index is reported by the insert kernel
 #pragma unroll
-  for (int a = 0; a < 3; ++a) {
-    const int num = in[a] + g.pad[a] - r[a] * g.dil[a];
-    if (num < 0 || num % g.stride[a] != 0)
-      return;
-    q[a] = num / g.stride[a];
-    if (q[a] >= g.ogrid[a])
-      return;
+    for (int a = 0; a < 3; ++a) {
+      const int num = in[a] + g.pad[a] - r[a] * g.dil[a];
+      ok = ok && num >= 0 && num % g.stride[a] == 0;
+      q[a] = num / g.stride[a];
+      ok = ok && q[a] < g.ogrid[a];
+    }
+    if (ok) {
+      key = linear_key(c.x, q[0], q[1], q[2], g.ogrid);
+      uint32_t slot = mix64(key) & cap_mask;
+      bool done = false;
+      for (uint32_t probe = 0; probe <= cap_mask && !done; ++probe) {
+        const unsigned long long prev = atomicCAS(set_keys + slot, kEmptyKey, key);
+        if (prev == key)
+          done = true;
+        else if (prev == kEmptyKey)
+          done = fresh = true;
+        else
+          slot = (slot + 1) & cap_mask;
+      }
+      if (!done)
+        atomicCAS(status, 0, kStatusTableFull);
+    }
   }
-  if (c.x < 0 || c.x >= g.batch_size)
-    return;  // reported by the insert kernel
-  const unsigned long long key = linear_key(c.x, q[0], q[1], q[2], g.ogrid);
-  uint32_t slot = mix64(key) & cap_mask;
-  for (uint32_t probe = 0; probe <= cap_mask; ++probe) {
-    const unsigned long long prev = atomicCAS(set_keys + slot, kEmptyKey, key);
-    if (prev == key)
-      return;
-    if (prev == kEmptyKey) {
-      const int at = atomicAdd(counter, 1);
+  // one counter update per warp: a single address takes about one atomic per clock
+  const unsigned won = __ballot_sync(0xffffffffu, fresh);
+  if (won) {
+    const int lane = threadIdx.x & 31, leader = __ffs(won) - 1;
+    int base = 0;
+    if (lane == leader)
+      base = atomicAdd(counter, __popc(won));
+    base = __shfl_sync(0xffffffffu, base, leader);
+    if (fresh) {
+      const int at = base + __popc(won & ((1u << lane) - 1u));
       if (at < list_cap)
         list[at] = key;
       else
         atomicCAS(status, 0, kStatusTableFull);
-      return;
     }
-    slot = (slot + 1) & cap_mask;
   }
-  atomicCAS(status, 0, kStatusTableFull);
 }
 
 __global__ void __launch_bounds__(256) decode_out_coords_kernel(const unsigned long long *__restrict__ keys, int n,
@@ -224,27 +238,65 @@ __global__ void __launch_bounds__(kSortThreads) sort_hist_kernel(const K *__rest
   hist[threadIdx.x * ntiles + blockIdx.x] = h[threadIdx.x];
 }
 
-// exclusive scan of `total` ints in place, one block
-__global__ void __launch_bounds__(1024) sort_scan_kernel(int *data, int total) {
-  __shared__ int s_sum[1024];
-  const int per = (total + 1023) / 1024;
-  const int lo = threadIdx.x * per, hi = min(lo + per, total);
-  int sum = 0;
-  for (int i = lo; i < hi; ++i)
-    sum += data[i];
-  s_sum[threadIdx.x] = sum;
-  __syncthreads();
-  for (int d = 1; d < 1024; d <<= 1) {
-    const int v = threadIdx.x >= d ? s_sum[threadIdx.x - d] : 0;
-    __syncthreads();
-    s_sum[threadIdx.x] += v;
-    __syncthreads();
+// Exclusive scan, in place, of the (digit, tile) count matrix in digit-major order (all tiles of
+// digit 0, then digit 1, ...).  One block of 32 warps; a warp owns 8 digit rows: row sums (coalesced
+// reads), a scan of the 256 sums, then a coalesced running scan along each row.
+__global__ void __launch_bounds__(1024) sort_scan_kernel(int *data, int ntiles) {
+  __shared__ int row_base[256];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int r = 0; r < 8; ++r) {
+    const int digit = warp * 8 + r;
+    const int *row = data + static_cast<long long>(digit) * ntiles;
+    int sum = 0;
+    for (int i = lane; i < ntiles; i += 32)
+      sum += row[i];
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1)
+      sum += __shfl_xor_sync(0xffffffffu, sum, d);
+    if (lane == 0)
+      row_base[digit] = sum;
   }
-  int run = s_sum[threadIdx.x] - sum;
-  for (int i = lo; i < hi; ++i) {
-    const int v = data[i];
-    data[i] = run;
-    run += v;
+  __syncthreads();
+  if (warp == 0) {  // exclusive scan of the 256 row sums: 8 per lane
+    int v[8], mine = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      v[k] = row_base[lane * 8 + k];
+      mine += v[k];
+    }
+    int incl = mine;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d)
+        incl += t;
+    }
+    int run = incl - mine;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      row_base[lane * 8 + k] = run;
+      run += v[k];
+    }
+  }
+  __syncthreads();
+  for (int r = 0; r < 8; ++r) {
+    const int digit = warp * 8 + r;
+    int *row = data + static_cast<long long>(digit) * ntiles;
+    int run = row_base[digit];
+    for (int i0 = 0; i0 < ntiles; i0 += 32) {
+      const int i = i0 + lane;
+      const int v = i < ntiles ? row[i] : 0;
+      int incl = v;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d)
+          incl += t;
+      }
+      if (i < ntiles)
+        row[i] = run + incl - v;
+      run += __shfl_sync(0xffffffffu, incl, 31);
+    }
   }
 }
 
