@@ -38,12 +38,6 @@ WORKLOAD = "scale-out: 8 scenes x 120k voxels, grid [41,1600,1408], seed 4, fwd+
 L2_BYTES = 126 * 1024 * 1024
 
 
-def scene_tables(scene_ids):
-    from cumm_b200 import workloads as W
-    tabs = [W.build_tables(W.sample_coords(VOXELS_PER_SCENE, [4, b], batch=b)) for b in scene_ids]
-    return W.concat_scenes(tabs) if len(tabs) > 1 else tabs[0]
-
-
 def host_features(n_in, n_out, seed):
     rng = np.random.default_rng(seed)
     x = rng.standard_normal((n_in, C_IN), dtype=np.float32).astype(np.float16)
@@ -212,7 +206,16 @@ def main():
         ids = [b for b in range(N_SCENES) if b % world == rank]
     else:
         ids = list(range(rank * per, (rank + 1) * per))
-    tb = scene_tables(ids)
+    # neighbour tables of this rank's scenes, built on the GPU (bit-identical to the host generator:
+    # tests/test_gpu_pairgen.py); the batch index keeps neighbours inside their scene
+    from types import SimpleNamespace
+    from cumm_b200 import workloads as W
+    from cumm_b200.pairgen import build_tables_gpu
+    coords_h = np.concatenate([W.sample_coords(VOXELS_PER_SCENE, [4, b], batch=b) for b in ids])
+    tg = build_tables_gpu(torch.from_numpy(coords_h).to(dev), N_SCENES, W.GRID)
+    torch.cuda.synchronize()
+    tb = SimpleNamespace(n_in=tg.n_in, n_out=tg.n_out, num_pairs=int((tg.indices >= 0).sum().item()))
+    tg.num_pairs = tb.num_pairs
     x_h, dout_h, w_h = host_features(tb.n_in, tb.n_out, [4, 100, rank])
     _, _, w_h = host_features(8, 8, [4, 100])  # identical weights on every rank
     num_tiles = (tb.n_out + 127) // 128
@@ -226,7 +229,7 @@ def main():
     with torch.cuda.stream(stream):
         w_d = torch.from_numpy(w_h).to(dev)
         for i in range(nsets):
-            t = DeviceTables.from_host(tb, dev)
+            t = tg.clone()  # every buffer set reads its own copy of the tables
             x = torch.from_numpy(x_h).to(dev)
             dout = torch.from_numpy(dout_h).to(dev)
             out = torch.zeros((tb.n_out, C_OUT), dtype=torch.float16, device=dev)
@@ -332,8 +335,9 @@ def main():
     barrier()
     clocks = sampler.finish()
     ms_total = e0.elapsed_time(e1)
-    # graph replays do not pass through the library's launch counter: 4 kernels per step
-    gpu_launches = 4 * args.steps
+    # graph replays do not pass through the library's launch counter: per step forward, backward
+    # input, and the three kernels of the weight gradient (plan, main, reduce)
+    gpu_launches = 5 * args.steps
     del launches0
 
     # per-op durations, live, events between the launches (not graph-captured)

@@ -71,6 +71,14 @@ class DeviceTables:
     mask_output: "torch.Tensor"
     num_pairs: int
 
+    def clone(self) -> "DeviceTables":
+        """A copy with its own device tensors (benchmarks rotate over such copies)."""
+        def c(t):
+            return None if t is None else t.clone()
+        return DeviceTables(self.n_in, self.n_out, self.kv, c(self.indices), c(self.mask), c(self.mask_argsort),
+                            c(self.indices_bwd), c(self.mask_bwd), c(self.mask_argsort_bwd), c(self.mask_output),
+                            self.num_pairs)
+
     @staticmethod
     def from_host(tb: ConvTables, device) -> "DeviceTables":
         import torch
