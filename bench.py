@@ -256,11 +256,36 @@ def main():
         if events:
             events[3].record(stream)
 
+    # The one exchange step of the path: sum the fp32 weight-gradient partials over ranks and cast.
+    # Default: this library's one-shot sum through NVLink peer memory (cb2_peer_allreduce); with
+    # CUMM_B200_ALLREDUCE=nccl, or if the peer buffers cannot be set up, NCCL all-reduce + cast.
+    peer_ar, exchange_kind = None, "nccl all-reduce + cast"
+    if world > 1:
+        ok = 0
+        if os.environ.get("CUMM_B200_ALLREDUCE", "peer") == "peer":
+            try:
+                from cumm_b200.peer_allreduce import PeerAllReduce
+                peer_ar = PeerAllReduce.over_process_group(C_OUT * KV * C_IN, dev)
+                ok = 1
+            except Exception as e:  # noqa: BLE001 - any set-up failure means: use NCCL, and say so
+                print(f"[rank {rank}] peer-memory sum unavailable ({e!r}); using NCCL", file=sys.stderr, flush=True)
+        agreed = torch.tensor([ok], dtype=torch.int32, device=dev)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+        if int(agreed[0]) == 1:
+            exchange_kind = "one-shot sum through NVLink peer memory (own kernel), fp16 cast fused"
+        else:
+            peer_ar = None
+
+    def exchange(s, cuda_stream):
+        if peer_ar is not None:
+            peer_ar(s["dw32"], out_f16=s["dw16"], stream=cuda_stream)
+        else:
+            if world > 1:
+                dist.all_reduce(s["dw32"])
+            s["dw16"].copy_(s["dw32"])
+
     def step_tail(s, events=None):
-        # the one exchange step of the path: sum the fp32 weight-gradient partials over ranks
-        if world > 1:
-            dist.all_reduce(s["dw32"])
-        s["dw16"].copy_(s["dw32"])
+        exchange(s, stream.cuda_stream)
         if events:
             events[4].record(stream)
 
@@ -275,12 +300,15 @@ def main():
     stream.synchronize()
     assert _lib.device_status() == 0, "kernel status word set during warm-up"
 
-    # Single GPU: the whole step is one graph.  Several GPUs: graph A = forward + weight
-    # gradient, then the all-reduce + cast run eagerly on a side stream (NCCL stays out of
-    # capture) while graph B = input gradient runs on the main stream, so the exchange is
-    # hidden behind compute; the step ends when both streams are done.
+    # Single GPU: the whole step is one graph.  Several GPUs with the peer-memory sum: still one
+    # graph -- forward, weight gradient, then the sum on a forked stream beside the input gradient
+    # -- so a step costs the host one launch (at 8 GPUs a step is ~0.1 ms of GPU work: an eager
+    # sequence of launches and events per step was slower than one GPU).  With NCCL: graph A =
+    # forward + weight gradient, the all-reduce + cast eagerly on a side stream (NCCL stays out
+    # of capture), graph B = input gradient on the main stream.
     graphs, graphs_b = [], []
     side = torch.cuda.Stream(device=dev)
+    one_graph = world == 1 or peer_ar is not None
     with torch.cuda.stream(stream):
         for s in sets:
             g = torch.cuda.CUDAGraph()
@@ -288,11 +316,19 @@ def main():
                 if world == 1:
                     step_kernels(s)
                     step_tail(s)
+                elif one_graph:
+                    s["layer"].fwd.launch()
+                    s["layer"].wgrad.launch()
+                    side.wait_stream(stream)
+                    with torch.cuda.stream(side):
+                        exchange(s, side.cuda_stream)
+                    s["layer"].dgrad.launch()
+                    stream.wait_stream(side)
                 else:
                     s["layer"].fwd.launch()
                     s["layer"].wgrad.launch()
             graphs.append(g)
-            if world > 1:
+            if not one_graph:
                 gb = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(gb, stream=stream):
                     s["layer"].dgrad.launch()
@@ -304,12 +340,11 @@ def main():
     def replay(i):
         k = i % nsets
         graphs[k].replay()
-        if world > 1:
+        if not one_graph:
             ev_a[k].record(stream)
             with torch.cuda.stream(side):
                 side.wait_event(ev_a[k])
-                dist.all_reduce(sets[k]["dw32"])
-                sets[k]["dw16"].copy_(sets[k]["dw32"])
+                exchange(sets[k], side.cuda_stream)
                 ev_b[k].record(side)
             graphs_b[k].replay()
             stream.wait_event(ev_b[k])
@@ -419,7 +454,8 @@ def main():
             "config": {"workload": WORKLOAD, "scenes_per_rank": len(ids), "rows_per_rank": tb.n_out,
                        "pairs_total": pairs_total, "parallelism": f"scene-sharded x{world}, wgrad fp32 all-reduce",
                        "l2": f"rotating {nsets} buffer sets ({nsets * step_bytes / 1e6:.0f} MB touched) > 126 MB L2",
-                       "timed_region": "N=1: one CUDA graph per step; N>1: graph(fwd+wgrad), then NCCL all-reduce + cast on a side stream overlapped with graph(dgrad)"},
+                       "timed_region": "one CUDA graph per step (N>1: the exchange on a forked stream beside dgrad)" if one_graph else "graph(fwd+wgrad), then NCCL all-reduce + cast eagerly on a side stream overlapped with graph(dgrad)",
+                       "exchange": exchange_kind if world > 1 else "none (one GPU)"},
             "voxels_per_s": 3 * rows_total / (ms_step * 1e-3),
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

@@ -32,6 +32,8 @@ EXPORTED_SYMBOLS = (
     "cb2_pairgen_workspace_size",
     "cb2_pairgen_count_outputs",
     "cb2_pairgen_run",
+    "cb2_peer_allreduce_buffer_size",
+    "cb2_peer_allreduce",
 )
 
 
@@ -115,6 +117,19 @@ class PairgenArgs(ctypes.Structure):
     ]
 
 
+class PeerAllreduceArgs(ctypes.Structure):
+    """``cb2_peer_allreduce_args``."""
+    _fields_ = [
+        ("peer_buffers", ctypes.POINTER(ctypes.c_void_p)),
+        ("rank", ctypes.c_int), ("world", ctypes.c_int),
+        ("src", ctypes.c_void_p),
+        ("out_f32", ctypes.c_void_p),
+        ("out_f16", ctypes.c_void_p),
+        ("numel", ctypes.c_longlong),
+        ("timeout_ns", ctypes.c_ulonglong),
+    ]
+
+
 _lib = None
 
 
@@ -152,6 +167,10 @@ def load() -> ctypes.CDLL:
     L.cb2_pairgen_count_outputs.argtypes = [ctypes.POINTER(PairgenArgs), ctypes.POINTER(ctypes.c_int), ctypes.c_void_p]
     L.cb2_pairgen_run.restype = ctypes.c_int
     L.cb2_pairgen_run.argtypes = [ctypes.POINTER(PairgenArgs), ctypes.c_void_p]
+    L.cb2_peer_allreduce_buffer_size.restype = ctypes.c_size_t
+    L.cb2_peer_allreduce_buffer_size.argtypes = [ctypes.c_longlong, ctypes.c_int]
+    L.cb2_peer_allreduce.restype = ctypes.c_int
+    L.cb2_peer_allreduce.argtypes = [ctypes.POINTER(PeerAllreduceArgs), ctypes.c_void_p]
     _lib = L
     return L
 

@@ -6,6 +6,7 @@
 #include "rowconv_kernel.cuh"
 #include "wgrad_kernel.cuh"
 #include "pairgen_kernels.cuh"
+#include "peer_reduce_kernel.cuh"
 
 #include <algorithm>
 #include <atomic>
@@ -728,6 +729,52 @@ int cb2_pairgen_run(const cb2_pairgen_args *a, void *stream_v) {
     if (rc)
       return rc;
   }
+  return CB2_OK;
+}
+
+// ---------------------------------------------------------------- sum over GPUs through peer memory
+size_t cb2_peer_allreduce_buffer_size(long long numel, int world) {
+  if (numel <= 0 || world < 1 || world > cb2::kPeerMaxWorld)
+    return 0;
+  const size_t slot = align256(static_cast<size_t>(numel) * 4);
+  return cb2::kPeerControlBytes + 2 * static_cast<size_t>(world) * slot;
+}
+
+int cb2_peer_allreduce(const cb2_peer_allreduce_args *a, void *stream_v) {
+  CB2_CHECK_ARG(a != nullptr, "null arguments");
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  DeviceState *dev;
+  int rc = get_device(&dev);
+  if (rc)
+    return rc;
+  CB2_CHECK_ARG(a->world >= 1 && a->world <= cb2::kPeerMaxWorld && a->rank >= 0 && a->rank < a->world,
+                "bad rank / world (%d, %d)", a->rank, a->world);
+  CB2_CHECK_ARG(a->numel > 0 && a->numel % 4 == 0, "numel must be a positive multiple of 4");
+  CB2_CHECK_RT(a->peer_buffers && a->src && (a->out_f32 || a->out_f16), "buffers, source and an output must not empty");
+  CB2_CHECK_ARG(aligned16(a->src) && aligned16(a->out_f32) && (reinterpret_cast<uintptr_t>(a->out_f16) & 7u) == 0,
+                "source and outputs must be 16-byte (fp16: 8-byte) aligned");
+  cb2::PeerReduceParams p;
+  memset(&p, 0, sizeof(p));
+  for (int r = 0; r < a->world; ++r) {
+    CB2_CHECK_RT(a->peer_buffers[r] != nullptr && reinterpret_cast<uintptr_t>(a->peer_buffers[r]) % 256 == 0,
+                 "peer buffer %d is null or not 256-byte aligned", r);
+    p.peer[r] = reinterpret_cast<unsigned char *>(a->peer_buffers[r]);
+  }
+  p.src = a->src;
+  p.out32 = a->out_f32;
+  p.out16 = reinterpret_cast<__half *>(a->out_f16);
+  p.numel = a->numel;
+  p.slot_bytes = static_cast<long long>(align256(static_cast<size_t>(a->numel) * 4));
+  p.rank = a->rank;
+  p.world = a->world;
+  p.timeout_ns = a->timeout_ns ? a->timeout_ns : 1000000000ull;
+  p.status = dev->status;
+  // every CTA waits for flags that the grid's own last CTA stores: keep the grid resident at once
+  int grid = static_cast<int>(std::min<long long>((a->numel / 4 + 511) / 512, 32));
+  grid = std::max(1, std::min(grid, dev->num_sms / 4));
+  cb2::peer_reduce_kernel<<<grid, 512, 0, stream>>>(p);
+  CB2_CUDA(cudaGetLastError());
+  g_launches.fetch_add(1);
   return CB2_OK;
 }
 

@@ -223,6 +223,33 @@ size_t cb2_pairgen_workspace_size(const cb2_pairgen_args *args);
 int cb2_pairgen_count_outputs(const cb2_pairgen_args *args, int *n_out, void *stream);
 int cb2_pairgen_run(const cb2_pairgen_args *args, void *stream);
 
+/*
+ * Sum of one fp32 array per GPU over NVLink peer memory, for the weight gradient of a
+ * convolution whose rows are sharded over the GPUs of a node.  (No counterpart in the
+ * reference, which is single-GPU.)  Every GPU makes the same sequence of calls with the same
+ * `numel`; each gets the same, bit-identical sum, as fp32 and/or fp16.  The call number that
+ * pairs the calls of the GPUs is kept inside the buffers, so a call can be captured in a CUDA
+ * graph and replayed.
+ * `peer_buffers`: a HOST array of `world` device pointers, the buffer of every GPU as mapped
+ * in the calling process (peer_buffers[rank] is the caller's own), each of
+ * cb2_peer_allreduce_buffer_size() bytes, zero-filled once before the first call.  The kernel
+ * writes its array into every buffer with plain stores and waits, for at most `timeout_ns`
+ * (0 = one second), for the other GPUs' arrays to arrive; a wait that runs out sets status
+ * word 1 (cb2_device_status) and leaves the outputs untouched.
+ */
+typedef struct cb2_peer_allreduce_args {
+  void *const *peer_buffers;
+  int rank, world; /* world <= 16 */
+  const float *src;
+  float *out_f32;  /* may be null */
+  void *out_f16;   /* may be null */
+  long long numel; /* multiple of 4 */
+  unsigned long long timeout_ns;
+} cb2_peer_allreduce_args;
+
+size_t cb2_peer_allreduce_buffer_size(long long numel, int world);
+int cb2_peer_allreduce(const cb2_peer_allreduce_args *args, void *stream);
+
 /* Rows of one output tile, i.e. the granularity of mask_out_ptr and the mask_width to
  * hand to backward weight (the reference uses the forward kernel's tile_shape[0],
  * cumm/conv/main_real_spconv.py:176-177). */

@@ -37,7 +37,7 @@ def test_library_exports_every_declared_symbol():
 def test_struct_layout_matches_header_field_order():
     header = (ROOT / "include" / "cumm_b200.h").read_text()
     for cname, cls in (("cb2_gemm_args", _lib.GemmArgs), ("cb2_conv_args", _lib.ConvArgs),
-                       ("cb2_pairgen_args", _lib.PairgenArgs)):
+                       ("cb2_pairgen_args", _lib.PairgenArgs), ("cb2_peer_allreduce_args", _lib.PeerAllreduceArgs)):
         body = header[header.index("typedef struct " + cname):header.index("} " + cname)]
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
         names = []
