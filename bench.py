@@ -455,7 +455,8 @@ def main():
                        "pairs_total": pairs_total, "parallelism": f"scene-sharded x{world}, wgrad fp32 all-reduce",
                        "l2": f"rotating {nsets} buffer sets ({nsets * step_bytes / 1e6:.0f} MB touched) > 126 MB L2",
                        "timed_region": "one CUDA graph per step (N>1: the exchange on a forked stream beside dgrad)" if one_graph else "graph(fwd+wgrad), then NCCL all-reduce + cast eagerly on a side stream overlapped with graph(dgrad)",
-                       "exchange": exchange_kind if world > 1 else "none (one GPU)"},
+                       "exchange": exchange_kind if world > 1 else "none (one GPU)",
+                       "exchange_last_call_ns_rank0": peer_ar.last_call_ns() if peer_ar is not None else None},
             "voxels_per_s": 3 * rows_total / (ms_step * 1e-3),
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

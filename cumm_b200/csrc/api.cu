@@ -770,8 +770,13 @@ int cb2_peer_allreduce(const cb2_peer_allreduce_args *a, void *stream_v) {
   p.timeout_ns = a->timeout_ns ? a->timeout_ns : 1000000000ull;
   p.status = dev->status;
   // every CTA waits for flags that the grid's own last CTA stores: keep the grid resident at once
-  int grid = static_cast<int>(std::min<long long>((a->numel / 4 + 511) / 512, 32));
-  grid = std::max(1, std::min(grid, dev->num_sms / 4));
+  static const int max_grid = [] {
+    const char *v = getenv("CUMM_B200_PEER_GRID");
+    const int g = v ? atoi(v) : 32;
+    return g >= 1 ? g : 32;
+  }();
+  int grid = static_cast<int>(std::min<long long>((a->numel / 4 + 511) / 512, max_grid));
+  grid = std::max(1, std::min(grid, dev->num_sms / 2));
   cb2::peer_reduce_kernel<<<grid, 512, 0, stream>>>(p);
   CB2_CUDA(cudaGetLastError());
   g_launches.fetch_add(1);

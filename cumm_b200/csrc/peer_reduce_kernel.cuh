@@ -28,7 +28,8 @@
 namespace cb2 {
 
 constexpr int kPeerMaxWorld = 16;
-constexpr int kPeerControlBytes = 4096;   // flags: one int per GPU at 128-byte pitch; CTA counter at 2048; call number at 2304
+constexpr int kPeerControlBytes = 4096;   // flags: one int per GPU at 128-byte pitch; CTA counter at 2048; call number at 2304;
+                                          // at 2560 four 64-bit global-timer readings of CTA 0 in the last call: start, pushed, flags seen, done
 
 struct PeerReduceParams {
   unsigned char *peer[kPeerMaxWorld];  // every GPU's buffer as mapped here; peer[rank] is this GPU's own
@@ -60,6 +61,9 @@ __global__ void __launch_bounds__(512) peer_reduce_kernel(const PeerReduceParams
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   const long long first = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const float4 *src4 = reinterpret_cast<const float4 *>(p.src);
+  unsigned long long *stamps = reinterpret_cast<unsigned long long *>(p.peer[p.rank] + 2560);
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    stamps[0] = global_timer_ns();
   // ---- push: this GPU's array into its slot on every GPU, nearest neighbour in the ring first
   for (int k = 0; k < p.world; ++k) {
     const int dst = (p.rank + 1 + k) % p.world;
@@ -71,6 +75,8 @@ __global__ void __launch_bounds__(512) peer_reduce_kernel(const PeerReduceParams
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
+    if (blockIdx.x == 0)
+      stamps[1] = global_timer_ns();
     int *counter = reinterpret_cast<int *>(p.peer[p.rank] + 2048);
     const int done = atomicAdd(counter, 1);
     if (done == static_cast<int>(gridDim.x) - 1) {
@@ -99,6 +105,8 @@ __global__ void __launch_bounds__(512) peer_reduce_kernel(const PeerReduceParams
         }
       }
     }
+    if (blockIdx.x == 0)
+      stamps[2] = global_timer_ns();
     if (!ok && p.status)
       atomicCAS(p.status, 0, kStatusWaitTimeout);
     __threadfence_system();
@@ -126,6 +134,8 @@ __global__ void __launch_bounds__(512) peer_reduce_kernel(const PeerReduceParams
           make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
     }
   }
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    stamps[3] = global_timer_ns();
 }
 
 } // namespace cb2

@@ -61,3 +61,12 @@ class PeerAllReduce:
         a.out_f16 = out_f16.data_ptr() if out_f16 is not None else None
         a.numel, a.timeout_ns = self.numel, self._timeout_ns
         _lib.raise_for(self._L.cb2_peer_allreduce(ctypes.byref(a), ctypes.c_void_p(int(stream))))
+
+    def last_call_ns(self):
+        """Global-timer readings of the last call on this rank, relative to its start: when its
+        pushes were done, when every rank's flag had been seen, when it finished (synchronises)."""
+        import torch
+        buf = self._keep[0] if isinstance(self._keep, tuple) else self._keep
+        torch.cuda.synchronize(buf.device)
+        st = buf[2560:2560 + 32].view(torch.int64).cpu().tolist()
+        return {"pushed": st[1] - st[0], "flags_seen": st[2] - st[0], "done": st[3] - st[0]}
