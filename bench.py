@@ -171,6 +171,8 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--scenes", type=int, default=N_SCENES,
+                    help="scenes in the batch (default: the 8 of the benchmark configuration; other values are for experiments)")
     ap.add_argument("--no-extras", action="store_true", help="skip the single-scene configurations and CPU baseline")
     ap.add_argument("--single-scene-only", action="store_true",
                     help="run only the 150k-voxel single-scene configurations (few launches: the profiling case)")
@@ -201,9 +203,10 @@ def main():
         return
 
     # ---- shard scenes over ranks
-    per = N_SCENES // world if N_SCENES % world == 0 else None
+    n_scenes = args.scenes
+    per = n_scenes // world if n_scenes % world == 0 else None
     if per is None:
-        ids = [b for b in range(N_SCENES) if b % world == rank]
+        ids = [b for b in range(n_scenes) if b % world == rank]
     else:
         ids = list(range(rank * per, (rank + 1) * per))
     # neighbour tables of this rank's scenes, built on the GPU (bit-identical to the host generator:
@@ -212,7 +215,7 @@ def main():
     from cumm_b200 import workloads as W
     from cumm_b200.pairgen import build_tables_gpu
     coords_h = np.concatenate([W.sample_coords(VOXELS_PER_SCENE, [4, b], batch=b) for b in ids])
-    tg = build_tables_gpu(torch.from_numpy(coords_h).to(dev), N_SCENES, W.GRID)
+    tg = build_tables_gpu(torch.from_numpy(coords_h).to(dev), n_scenes, W.GRID)
     torch.cuda.synchronize()
     tb = SimpleNamespace(n_in=tg.n_in, n_out=tg.n_out, num_pairs=int((tg.indices >= 0).sum().item()))
     tg.num_pairs = tb.num_pairs
@@ -363,6 +366,12 @@ def main():
     launches0 = _lib.launch_count()
     e0, e1 = ev(), ev()
     with torch.cuda.stream(stream):
+        if world > 1:
+            # The ranks leave the host barrier up to milliseconds apart, and a step ends in a
+            # rendezvous of all GPUs: one more untimed step lines the GPUs' timelines up (its
+            # exchange completes at the same moment everywhere), so the start events are
+            # simultaneous and the K timed steps do not include one rank waiting for another's host.
+            replay(args.warmup)
         e0.record(stream)
         for i in range(args.steps):
             replay(i)
@@ -385,6 +394,11 @@ def main():
             stream.synchronize()
             op_ms += [evs[j].elapsed_time(evs[j + 1]) for j in range(4)]
     op_ms /= reps
+    if peer_ar is not None:
+        # Between events the exchange also holds the wait for the slowest rank's eager launches;
+        # the kernel's own clock readings (start to finish of the last call on this rank) are the
+        # figure that belongs beside the other kernels.
+        op_ms[3] = peer_ar.last_call_ns()["done"] * 1e-6
     status = _lib.device_status()
 
     ms_step = ms_total / args.steps
