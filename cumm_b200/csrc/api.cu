@@ -601,7 +601,7 @@ int radix_sort(K *k_result, int *v_result, K *k_scratch, int *v_scratch, int n, 
   int *vs = sort_source(v_result, v_scratch, bits), *vd = (vs == v_result) ? v_scratch : v_result;
   for (int p = 0; p < passes; ++p) {
     cb2pg::sort_hist_kernel<K><<<ntiles, cb2pg::kSortThreads, 0, s>>>(ks, n, 8 * p, hist, ntiles);
-    cb2pg::sort_scan_kernel<<<1, 1024, 0, s>>>(hist, ntiles);
+    cb2pg::sort_scan_kernel<<<1, 1024, 0, s>>>(reinterpret_cast<int4 *>(hist), (256 * ntiles + 3) / 4);
     cb2pg::sort_scatter_kernel<K, HAS_VAL><<<ntiles, cb2pg::kSortThreads, 0, s>>>(ks, vs, kd, vd, n, 8 * p, hist, ntiles);
     CB2_CUDA(cudaGetLastError());
     g_launches.fetch_add(3);
@@ -655,8 +655,7 @@ int cb2_pairgen_count_outputs(const cb2_pairgen_args *a, int *n_out, void *strea
   unsigned long long *list_b = reinterpret_cast<unsigned long long *>(ws + L.off_list_b);
   CB2_CUDA(cudaMemsetAsync(counter, 0, 256, stream));
   CB2_CUDA(cudaMemsetAsync(set_keys, 0xFF, static_cast<size_t>(L.cap_set) * 8, stream));
-  const long long threads = static_cast<long long>(a->n_in) * L.g.kv;
-  cb2pg::out_candidates_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(
+  cb2pg::out_candidates_kernel<<<(a->n_in + 255) / 256, 256, 0, stream>>>(
       a->in_coords, a->n_in, L.g, set_keys, L.cap_set - 1, sort_source(list_a, list_b, L.key_bits),
       static_cast<int>(L.list_cap), counter, dev->status);
   CB2_CUDA(cudaGetLastError());

@@ -83,60 +83,63 @@ __device__ __forceinline__ int hash_find(const unsigned long long *__restrict__ 
 }
 
 // ---------------------------------------------------------------- active outputs of a strided conv
-// One thread per (input voxel, filter offset): the output position that reads this input
-// through this offset, if there is one.  New positions are appended (unordered) to `list`.
+// One thread per input voxel: the output positions that read it, one per filter offset whose
+// (in + pad - r * dil) is a multiple of the stride on every axis (for stride 2 that is 8 of the
+// 27 offsets; the loops prune whole planes and rows of offsets at once).  New positions are
+// appended (unordered) to `list`, one counter update per group of lanes that found one together.
 __global__ void __launch_bounds__(256) out_candidates_kernel(const int32_t *__restrict__ coords, int n, Geometry g,
                                                              unsigned long long *set_keys, uint32_t cap_mask,
                                                              unsigned long long *list, int list_cap, int *counter,
                                                              int *status) {
-  const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  bool fresh = false;  // this thread found a position nobody had claimed yet
-  unsigned long long key = 0;
-  if (t < static_cast<long long>(n) * g.kv) {
-    const int i = static_cast<int>(t / g.kv), f = static_cast<int>(t % g.kv);
-    const int4 c = reinterpret_cast<const int4 *>(coords)[i];
-    const int r[3] = {f / (g.ksize[1] * g.ksize[2]), (f / g.ksize[2]) % g.ksize[1], f % g.ksize[2]};
-    const int in[3] = {c.y, c.z, c.w};
-    int q[3];
-    bool ok = c.x >= 0 && c.x < g.batch_size;  // a bad batch index is reported by the insert kernel
-#pragma unroll
-    for (int a = 0; a < 3; ++a) {
-      const int num = in[a] + g.pad[a] - r[a] * g.dil[a];
-      ok = ok && num >= 0 && num % g.stride[a] == 0;
-      q[a] = num / g.stride[a];
-      ok = ok && q[a] < g.ogrid[a];
-    }
-    if (ok) {
-      key = linear_key(c.x, q[0], q[1], q[2], g.ogrid);
-      uint32_t slot = mix64(key) & cap_mask;
-      bool done = false;
-      for (uint32_t probe = 0; probe <= cap_mask && !done; ++probe) {
-        const unsigned long long prev = atomicCAS(set_keys + slot, kEmptyKey, key);
-        if (prev == key)
-          done = true;
-        else if (prev == kEmptyKey)
-          done = fresh = true;
-        else
-          slot = (slot + 1) & cap_mask;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n)
+    return;
+  const int4 c = reinterpret_cast<const int4 *>(coords)[i];
+  if (c.x < 0 || c.x >= g.batch_size)
+    return;  // reported by the insert kernel
+  const int lane = threadIdx.x & 31;
+  for (int rz = 0; rz < g.ksize[0]; ++rz) {
+    const int nz = c.y + g.pad[0] - rz * g.dil[0];
+    if (nz < 0 || nz % g.stride[0] != 0 || nz / g.stride[0] >= g.ogrid[0])
+      continue;
+    for (int ry = 0; ry < g.ksize[1]; ++ry) {
+      const int ny = c.z + g.pad[1] - ry * g.dil[1];
+      if (ny < 0 || ny % g.stride[1] != 0 || ny / g.stride[1] >= g.ogrid[1])
+        continue;
+      for (int rx = 0; rx < g.ksize[2]; ++rx) {
+        const int nx = c.w + g.pad[2] - rx * g.dil[2];
+        if (nx < 0 || nx % g.stride[2] != 0 || nx / g.stride[2] >= g.ogrid[2])
+          continue;
+        const unsigned long long key =
+            linear_key(c.x, nz / g.stride[0], ny / g.stride[1], nx / g.stride[2], g.ogrid);
+        uint32_t slot = mix64(key) & cap_mask;
+        bool done = false, fresh = false;
+        for (uint32_t probe = 0; probe <= cap_mask && !done; ++probe) {
+          const unsigned long long prev = atomicCAS(set_keys + slot, kEmptyKey, key);
+          if (prev == key)
+            done = true;
+          else if (prev == kEmptyKey)
+            done = fresh = true;
+          else
+            slot = (slot + 1) & cap_mask;
+        }
+        if (!done)
+          atomicCAS(status, 0, kStatusTableFull);
+        if (fresh) {
+          // the lanes that got here together share one counter update
+          const unsigned together = __activemask();
+          const int leader = __ffs(together) - 1;
+          int base = 0;
+          if (lane == leader)
+            base = atomicAdd(counter, __popc(together));
+          base = __shfl_sync(together, base, leader);
+          const int at = base + __popc(together & ((1u << lane) - 1u));
+          if (at < list_cap)
+            list[at] = key;
+          else
+            atomicCAS(status, 0, kStatusTableFull);
+        }
       }
-      if (!done)
-        atomicCAS(status, 0, kStatusTableFull);
-    }
-  }
-  // one counter update per warp: a single address takes about one atomic per clock
-  const unsigned won = __ballot_sync(0xffffffffu, fresh);
-  if (won) {
-    const int lane = threadIdx.x & 31, leader = __ffs(won) - 1;
-    int base = 0;
-    if (lane == leader)
-      base = atomicAdd(counter, __popc(won));
-    base = __shfl_sync(0xffffffffu, base, leader);
-    if (fresh) {
-      const int at = base + __popc(won & ((1u << lane) - 1u));
-      if (at < list_cap)
-        list[at] = key;
-      else
-        atomicCAS(status, 0, kStatusTableFull);
     }
   }
 }
@@ -239,64 +242,54 @@ __global__ void __launch_bounds__(kSortThreads) sort_hist_kernel(const K *__rest
 }
 
 // Exclusive scan, in place, of the (digit, tile) count matrix in digit-major order (all tiles of
-// digit 0, then digit 1, ...).  One block of 32 warps; a warp owns 8 digit rows: row sums (coalesced
-// reads), a scan of the 256 sums, then a coalesced running scan along each row.
-__global__ void __launch_bounds__(1024) sort_scan_kernel(int *data, int ntiles) {
-  __shared__ int row_base[256];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int r = 0; r < 8; ++r) {
-    const int digit = warp * 8 + r;
-    const int *row = data + static_cast<long long>(digit) * ntiles;
-    int sum = 0;
-    for (int i = lane; i < ntiles; i += 32)
-      sum += row[i];
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1)
-      sum += __shfl_xor_sync(0xffffffffu, sum, d);
-    if (lane == 0)
-      row_base[digit] = sum;
+// digit 0, then digit 1, ...), `total4` int4 in all (the tail beyond 256 * ntiles is padding whose
+// values nobody reads).  One block; every thread owns a contiguous run of int4 that it reads
+// twice with several loads in flight: the kernel is a handful of memory latencies long.
+__global__ void __launch_bounds__(1024) sort_scan_kernel(int4 *data, int total4) {
+  __shared__ int s_sum[1024];
+  const int per = (total4 + 1023) / 1024;
+  const int lo = min(threadIdx.x * per, total4), hi = min(lo + per, total4);
+  int sum = 0;
+#pragma unroll 8
+  for (int i = lo; i < hi; ++i) {
+    const int4 v = data[i];
+    sum += v.x + v.y + v.z + v.w;
   }
-  __syncthreads();
-  if (warp == 0) {  // exclusive scan of the 256 row sums: 8 per lane
-    int v[8], mine = 0;
+  // block-wide exclusive scan of the 1024 sums: warp scans, then a scan of the 32 warp totals
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int incl = sum;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      v[k] = row_base[lane * 8 + k];
-      mine += v[k];
-    }
-    int incl = mine;
+  for (int d = 1; d < 32; d <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= d)
+      incl += t;
+  }
+  if (lane == 31)
+    s_sum[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    const int w = s_sum[lane];
+    int wi = w;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
-      const int t = __shfl_up_sync(0xffffffffu, incl, d);
+      const int t = __shfl_up_sync(0xffffffffu, wi, d);
       if (lane >= d)
-        incl += t;
+        wi += t;
     }
-    int run = incl - mine;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      row_base[lane * 8 + k] = run;
-      run += v[k];
-    }
+    s_sum[lane] = wi - w;
   }
   __syncthreads();
-  for (int r = 0; r < 8; ++r) {
-    const int digit = warp * 8 + r;
-    int *row = data + static_cast<long long>(digit) * ntiles;
-    int run = row_base[digit];
-    for (int i0 = 0; i0 < ntiles; i0 += 32) {
-      const int i = i0 + lane;
-      const int v = i < ntiles ? row[i] : 0;
-      int incl = v;
-#pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        const int t = __shfl_up_sync(0xffffffffu, incl, d);
-        if (lane >= d)
-          incl += t;
-      }
-      if (i < ntiles)
-        row[i] = run + incl - v;
-      run += __shfl_sync(0xffffffffu, incl, 31);
-    }
+  int run = s_sum[warp] + incl - sum;
+#pragma unroll 8
+  for (int i = lo; i < hi; ++i) {
+    const int4 v = data[i];
+    int4 o;
+    o.x = run;
+    o.y = run + v.x;
+    o.z = o.y + v.y;
+    o.w = o.z + v.z;
+    run = o.w + v.w;
+    data[i] = o;
   }
 }
 

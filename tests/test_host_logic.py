@@ -199,3 +199,38 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "nope.so")
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         _lib.load()
+
+
+def test_table_builder_workspace_size_is_a_host_function():
+    """cb2_pairgen_workspace_size needs no GPU: geometry checks and the size arithmetic only."""
+    L = ctypes.CDLL(str(_lib.LIB_PATH))
+    L.cb2_pairgen_workspace_size.restype = ctypes.c_size_t
+    L.cb2_pairgen_workspace_size.argtypes = [ctypes.POINTER(_lib.PairgenArgs)]
+
+    def size(n_in, subm, stride=(1, 1, 1), ksize=(3, 3, 3), grid=(41, 1600, 1408), batch=1):
+        a = _lib.PairgenArgs()
+        a.n_in, a.batch_size, a.subm = n_in, batch, int(subm)
+        for name, vals in (("grid", grid), ("ksize", ksize), ("stride", stride), ("pad", (1, 1, 1)), ("dil", (1, 1, 1))):
+            for i in range(3):
+                getattr(a, name)[i] = vals[i]
+        return L.cb2_pairgen_workspace_size(ctypes.byref(a))
+
+    s1, s2 = size(150000, True), size(300000, True)
+    assert 0 < s1 < s2
+    assert size(150000, False, stride=(2, 2, 2)) > s1  # the strided case also holds the output set and lists
+    assert size(150000, True, stride=(2, 2, 2)) == 0   # a submanifold convolution has stride 1
+    assert size(150000, True, ksize=(3, 3, 5)) == 0    # kernel volume 45 > 32 mask bits
+    assert size(150000, True, grid=(0, 10, 10)) == 0
+    assert size(150000, True, batch=0) == 0
+
+
+def test_peer_allreduce_buffer_size_is_a_host_function():
+    L = ctypes.CDLL(str(_lib.LIB_PATH))
+    L.cb2_peer_allreduce_buffer_size.restype = ctypes.c_size_t
+    L.cb2_peer_allreduce_buffer_size.argtypes = [ctypes.c_longlong, ctypes.c_int]
+    numel = 128 * 27 * 128
+    one = L.cb2_peer_allreduce_buffer_size(numel, 1)
+    assert one == 4096 + 2 * numel * 4
+    assert L.cb2_peer_allreduce_buffer_size(numel, 8) == 4096 + 2 * 8 * numel * 4
+    assert L.cb2_peer_allreduce_buffer_size(numel, 17) == 0
+    assert L.cb2_peer_allreduce_buffer_size(0, 2) == 0
