@@ -1,13 +1,15 @@
 // Row-gather implicit-GEMM kernel for sm_100a: forward and input-gradient of the
 // mask-based sparse convolution, and the gather-GEMM-scatter GEMM (one filter offset with
-// explicit row lists).  One persistent CTA per SM walks 128-row tiles of the (sorted)
-// output rows; for every filter offset present in the tile's OR-ed neighbour mask it
-// gathers the 128 operand rows into a 128-byte-swizzled shared-memory tile with 16-byte
-// cp.async (missing neighbours are zero-filled), brings the matching weight slice in by
-// TMA, and one thread issues tcgen05.mma into a TMEM accumulator.  Four epilogue warps
-// read the accumulator back, apply alpha/beta/bias/activation (or the int8
-// requantisation), stage the tile through shared memory and write whole rows to their
-// scattered destinations.  No atomics: every output row is owned by exactly one tile.
+// explicit row lists).  One persistent CTA per SM takes 128-row tiles of the (sorted)
+// output rows from a scheduler warp (global ticket counter, ring of tiles in shared memory);
+// for every filter offset present in the tile's OR-ed neighbour mask it gathers the 128
+// operand rows into a 128-byte-swizzled shared-memory tile (TMA tile::gather4 for rows of up
+// to 128 bytes, 16-byte cp.async for wider ones; missing neighbours read as zeros), brings the
+// matching weight slice in by TMA, and one thread issues tcgen05.mma into a TMEM accumulator.
+// Eight (fp16) or sixteen (int8) epilogue warps read the accumulator back, apply
+// alpha/beta/bias/activation (or the int8 requantisation), stage the tile through shared
+// memory and write whole rows to their scattered destinations.  No atomics on data: every
+// output row is owned by exactly one tile.
 //
 // What it computes follows the reference kernel's control flow
 // (cumm/conv/kernel.py:825-920, cumm/conv/sparse_iters.py:317-356,
