@@ -164,8 +164,10 @@ size_t cb2_conv_workspace_size(const cb2_conv_args *args);
  * part of the library image (cb2_static_scratch_bytes()).  Every GPU that loads the library
  * holds that array until the process exits.
  *
- *  - Problems whose scratch does not fit (roughly K * C > 128 * 128 on a 148-SM part) are
- *    refused with CB2_ERR_RUNTIME and a message naming both sizes; nothing is launched.
+ *  - Problems whose scratch does not fit (roughly K * C > 128 * 128 on a 148-SM part, or more
+ *    than about five million rows at K = C = 128: the scratch also holds the per-offset lists of
+ *    row tiles) are refused with CB2_ERR_RUNTIME and a message naming both sizes; nothing is
+ *    launched.
  *  - The first call on each device resolves the array's device address.  That one call
  *    should be made before any stream capture begins on that device.
  *  - All calls share the one array and it keeps the previous call's contents; the kernels
