@@ -289,7 +289,16 @@ __device__ __forceinline__ void cp_async_4(uint32_t dst, const void *src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
 
-__device__ __forceinline__ void scheduler_run(const RowConvParams &p, const RingView &rv, int ntiles, int kpasses) {
+// The first batch of tickets is requested at kernel entry (first_ticket_request), long before the
+// scheduler can use it: the counter's round trip, and an L2 prefetch of the first tile's words,
+// run while the CTA sets up its barriers and tensor memory.
+__device__ __forceinline__ int first_ticket_count(int ntiles) {
+  const int b = ntiles / ((int)gridDim.x * 4);
+  return b < 1 ? 1 : (b > CB2_ROWCONV_TICKET_BATCH ? CB2_ROWCONV_TICKET_BATCH : b);
+}
+
+__device__ __forceinline__ void scheduler_run(const RowConvParams &p, const RingView &rv, int ntiles, int kpasses,
+                                              int first_base, int first_cnt) {
   constexpr int STEP_BUDGET = CB2_ROWCONV_STEP_BUDGET;  // steps a CTA may hold (drawn, not finished)
   const int lane = (int)lane_id();
   const bool dynamic = p.tickets != nullptr && gridDim.y == 1;
@@ -306,8 +315,10 @@ __device__ __forceinline__ void scheduler_run(const RowConvParams &p, const Ring
     if (lane == 0)
       next_base = atomicAdd(p.tickets, next_cnt);
   };
-  if (dynamic)
-    request(0);
+  if (dynamic) {
+    next_base = first_base;  // requested at kernel entry (lane 0 holds the counter's answer)
+    next_cnt = first_cnt;
+  }
   auto draw = [&]() -> int {
     int t;
     if (dynamic) {
@@ -485,6 +496,14 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
   const int kpasses = (p.red + Cfg::KRED - 1) / Cfg::KRED;
   const int n0 = blockIdx.y * BLOCK_N;
 
+  // Scheduler warp: ask for the first tickets now; their round trip overlaps the set-up below.
+  int early_base = 0, early_cnt = 0;
+  if (warp == Cfg::SCHED_WARP && p.tickets != nullptr && gridDim.y == 1) {
+    early_cnt = first_ticket_count(ntiles);
+    if (lane == 0)
+      early_base = atomicAdd(p.tickets, early_cnt);
+  }
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::SA; ++s) {
       mbar_init(full_a(s), Cfg::FULL_A_COUNT);
@@ -519,6 +538,18 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
   if (warp == Cfg::MMA_WARP) {
     tmem_alloc(sbase + Cfg::OFF_MISC, Cfg::TMEM_COLS);
     tmem_relinquish();
+  }
+  if (warp == Cfg::SCHED_WARP && early_cnt > 0 && p.mode == kModeMaskConv) {
+    // the first tile's sort order and masks: 128 ints each, four 128-byte lines each
+    const int first = __shfl_sync(0xffffffffu, early_base, 0);
+    const int tile = ntiles - 1 - first;
+    if (tile >= 0 && lane < 8) {
+      const int r = tile * 128 + (lane & 3) * 32;
+      if (r < p.n_rows) {
+        const void *line = (lane < 4) ? static_cast<const void *>(p.argsort + r) : static_cast<const void *>(p.mask + r);
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(line));
+      }
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -927,7 +958,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
     __syncwarp();
   } else if (warp == Cfg::SCHED_WARP) {
     // ======================= scheduler: draws tiles, publishes their masks and row numbers
-    scheduler_run(p, rv, ntiles, kpasses);
+    scheduler_run(p, rv, ntiles, kpasses, early_base, early_cnt);
   } else {
     // ======================= operand-row gather: group g owns stage g
     if constexpr (TMA_GATHER) {
