@@ -458,8 +458,9 @@ def main():
         dom = int(np.argmax(op_ms[:3]))
         dom_bytes = [fwd_bytes, fwd_bytes, wgrad_bytes][dom]
         # DRAM bytes per output row from the ncu launch list of this command
-        # (profiles/bench_step_launch_list.md): 468.9 MB and 523.6 MB per launch at 960 000 rows
-        traffic = [488.4, 488.4, 545.4][dom] * tb.n_out
+        # (profiles/bench_step_launch_list.md): 459.9 MB (forward), 460.1 MB (backward input) and
+        # 534.7 MB (backward weight: plan + main + reduce) per launch at 960 000 rows
+        traffic = [479.1, 479.3, 557.0][dom] * tb.n_out
         achieved = dom_bytes / (op_ms[dom] * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
