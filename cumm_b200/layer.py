@@ -70,6 +70,7 @@ class DeviceTables:
     mask_argsort_bwd: "torch.Tensor"
     mask_output: "torch.Tensor"
     num_pairs: int
+    keep: object = None  # memory that kernels still in flight read (the builder's workspace)
 
     def clone(self) -> "DeviceTables":
         """A copy with its own device tensors (benchmarks rotate over such copies)."""
