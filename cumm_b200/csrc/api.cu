@@ -152,8 +152,8 @@ int gather_mode() {
 // Launch with programmatic stream serialisation: the kernel may be scheduled while its
 // predecessor on the stream is still running and synchronises with it through
 // griddepcontrol.wait in its own code.  `level` 1 (on by default): the chain of the three
-// weight-gradient kernels and the gather-GEMM-scatter calls; level 2 (only with
-// CUMM_B200_PDL=2): the convolution row kernels.  CUMM_B200_PDL=0 launches everything the
+// weight-gradient kernels, the gather-GEMM-scatter calls and the int8 convolutions; level 2
+// (only with CUMM_B200_PDL=2): the fp16 convolution row kernels.  CUMM_B200_PDL=0 launches everything the
 // ordinary way.
 template <class Kern, class... Args>
 cudaError_t launch_after(int level, Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
@@ -190,10 +190,12 @@ int launch_rowconv_inst(const CUtensorMap &map, const CUtensorMap &map_a, const 
     configured.fetch_or(1ull << dev);
   }
   // A gather-GEMM-scatter call is one of a run of small kernels (one per filter offset), where
-  // overlapping each kernel's set-up with its predecessor's tail nearly halves the run; for the
-  // one-kernel convolutions it measured neutral to slightly worse.
-  CB2_CUDA(launch_after(p.mode == kModeMaskConv ? 2 : 1, kern, dim3(grid_x, grid_y), dim3(Cfg::THREADS),
-                        Cfg::SMEM_BYTES, stream, map, map_a, p));
+  // overlapping each kernel's set-up with its predecessor's tail nearly halves the run.  For the
+  // convolutions it measured +4 % for the int8 kernels (long epilogue tail) and neutral to
+  // slightly worse for fp16, so only the former take part by default.
+  const int pdl_level = p.mode != kModeMaskConv ? 1 : (KIND == 1 ? 1 : 2);
+  CB2_CUDA(launch_after(pdl_level, kern, dim3(grid_x, grid_y), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, stream, map,
+                        map_a, p));
   g_launches.fetch_add(1);
   return CB2_OK;
 }
