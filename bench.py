@@ -9,14 +9,19 @@ a [41,1600,1408] grid (seed 4, one generator stream per scene), 3x3x3 submanifol
 C_in = C_out = 128, fp16 with fp32 accumulation.  A step is forward + input gradient +
 weight gradient over the batch.  Scenes are sharded over the ranks (weights replicated, no
 collective for forward / input gradient); the fp32 weight-gradient partials [128,27,128]
-are summed by one NCCL all-reduce and cast to fp16.  Total work is fixed: strong scaling.
+are summed over the ranks (one exchange step) and cast to fp16.  Total work is fixed: strong
+scaling.
 
-The timed loop replays CUDA graphs of the step over rotating buffer sets whose footprint
-exceeds the 126 MB L2, so HBM figures are cold-cache.  One JSON line is printed by rank 0.
+The three operators of a step are independent of each other, so a step is one CUDA graph with
+three branches (each kernel bounded to a share of the SMs, `max_ctas`) unless
+`--schedule sequential` asks for one after the other.  The timed loop replays the graphs over
+rotating buffer sets whose footprint exceeds the 126 MB L2, so HBM figures are cold-cache; it
+is repeated `--repeats` times and the median is the headline.  One JSON line is printed by rank 0.
 """
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
 import os
 import sys
@@ -36,6 +41,9 @@ KV = 27
 METRIC = "sparse-conv effective TFLOP/s (fwd+dgrad+wgrad, fp16, C=K=128, 3x3x3 subm)"
 WORKLOAD = "scale-out: 8 scenes x 120k voxels, grid [41,1600,1408], seed 4, fwd+dgrad+wgrad fp16 C=K=128"
 L2_BYTES = 126 * 1024 * 1024
+# SM shares of the three kernels when they run side by side (forward, backward input, backward
+# weight); the weight gradient moves the same bytes with more steps per row tile.
+SHARES = (48, 48, 52)
 
 
 def host_features(n_in, n_out, seed):
@@ -51,6 +59,39 @@ def op_bytes(n_rows, num_tiles, C=C_IN, K=C_OUT, es=2):
     fwd = n_rows * C * es + n_rows * K * es + KV * C * K * es + 4 * KV * n_rows + 8 * n_rows
     wgrad = n_rows * C * es + n_rows * K * es + KV * C * K * es + 4 * KV * n_rows + 4 * n_rows + 4 * num_tiles
     return fwd, wgrad
+
+
+def base_config(world, scenes, rows_per_rank, pairs_total):
+    return {"workload": WORKLOAD, "scenes": scenes, "scenes_per_rank": scenes // max(world, 1),
+            "rows_per_rank": rows_per_rank, "pairs_total": pairs_total,
+            "parallelism": f"scene-sharded x{world}, wgrad fp32 partial sums exchanged"}
+
+
+def hbm_peak():
+    pk = ROOT / "MEASURED_PEAKS.json"
+    if pk.exists():
+        peaks = json.loads(pk.read_text())
+        if "hbm_gbs" in peaks:
+            return float(peaks["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback 6650 GB/s"
+
+
+def csrc_digest():
+    h = hashlib.sha256()
+    for f in sorted((ROOT / "cumm_b200" / "csrc").glob("*.cu*")):
+        h.update(f.name.encode())
+        h.update(f.read_bytes())
+    return h.hexdigest()[:16]
+
+
+def measured_traffic():
+    """DRAM bytes per output row of each kernel, from the ncu capture recorded in
+    profiles/traffic.json, and whether the kernel sources have changed since that capture."""
+    p = ROOT / "profiles" / "traffic.json"
+    if not p.exists():
+        return None, None
+    t = json.loads(p.read_text())
+    return t, t.get("csrc_sha256") != csrc_digest()
 
 
 class ClockSampler(threading.Thread):
@@ -93,7 +134,7 @@ class ClockSampler(threading.Thread):
                         self.reasons.add(name)
             except Exception:
                 pass
-            time.sleep(0.005)
+            time.sleep(0.002)
 
     def finish(self):
         self._halt.set()
@@ -114,36 +155,43 @@ def physical_gpu_index(local_rank):
 
 
 # ----------------------------------------------------------------------------------------
-# CPU arm: the reference's numpy statement of the op on the host cores
+# CPU arm: the reference's numpy statement of the op on the host cores, over the whole batch
 # ----------------------------------------------------------------------------------------
-def cpu_sample_step(O, x, dout, w, indices):
-    t = time.perf_counter()
-    O.np_forward(x, w, indices)
-    O.np_dgrad(dout, w, indices, x.shape[0])
-    O.np_wgrad(dout, x, indices)
-    return time.perf_counter() - t
-
-
-def cpu_setup(voxels):
+def cpu_setup(scenes=N_SCENES, voxels=VOXELS_PER_SCENE):
     from cumm_b200 import workloads as W
     from oracle import oracle as O
-    tb = W.build_tables(W.sample_coords(voxels, [4, 0]))
-    x, dout, w = host_features(tb.n_in, tb.n_out, [4, 100])
-    return O, tb, x, dout, w
+    tabs = [W.build_tables(W.sample_coords(voxels, [4, b], batch=b)) for b in range(scenes)]
+    _, _, w = host_features(8, 8, [4, 100])
+    feats = [host_features(voxels, voxels, [4, 100, b])[:2] for b in range(scenes)]
+    return O, tabs, feats, w
+
+
+def cpu_batch_step(O, tabs, feats, w):
+    """forward + input gradient + weight gradient of every scene of the batch; returns seconds."""
+    t = time.perf_counter()
+    dw = None
+    for tb, (x, dout) in zip(tabs, feats):
+        O.np_forward(x, w, tb.indices)
+        O.np_dgrad(dout, w, tb.indices, x.shape[0])
+        d = O.np_wgrad(dout, x, tb.indices)
+        dw = d if dw is None else dw + d
+    return time.perf_counter() - t
 
 
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    voxels = VOXELS_PER_SCENE
-    O, tb, x, dout, w = cpu_setup(voxels)
-    flops = 3 * 2 * tb.num_pairs * C_IN * C_OUT
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    O, tabs, feats, w = cpu_setup(args.scenes)
+    pairs = float(sum(tb.num_pairs for tb in tabs))
+    rows = sum(tb.n_out for tb in tabs)
+    flops = 3 * 2 * pairs * C_IN * C_OUT
     for _ in range(max(args.warmup, 1)):
-        cpu_sample_step(O, x, dout, w, tb.indices)
+        cpu_batch_step(O, tabs, feats, w)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        cpu_sample_step(O, x, dout, w, tb.indices)
+        cpu_batch_step(O, tabs, feats, w)
     dt = (time.perf_counter() - t0) / args.steps
     val = flops / dt / 1e12
     cores = os.cpu_count()
@@ -151,15 +199,30 @@ def run_reference_arm(args):
         "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD},
+        "config": base_config(world, args.scenes, rows // world, pairs),
         "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-                         "sample": f"one scene of {voxels} voxels per step (1/8 of the batch), numpy gather-"
-                                   "matmul-scatter with the BLAS thread pool; the reference's own kernels and CPU "
+                         "sample": f"the whole batch per step ({args.scenes} scenes x {VOXELS_PER_SCENE} voxels), numpy "
+                                   "gather-matmul-scatter with the BLAS thread pool; the reference's own kernels and CPU "
                                    "simulator need its code generator, which is not installable offline"},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "voxels_per_s": 3 * tb.n_out / dt,
+        "voxels_per_s": 3 * rows / dt,
     }
     print(json.dumps(line), flush=True)
+
+
+def cpu_baseline(scenes=N_SCENES):
+    """The numpy statement of the batch's step on the host cores, a bounded sample."""
+    O, tabs, feats, w = cpu_setup(scenes)
+    cpu_batch_step(O, tabs, feats, w)
+    n, t_total = 0, 0.0
+    while t_total < 12.0 and n < 10:
+        t_total += cpu_batch_step(O, tabs, feats, w)
+        n += 1
+    dt = t_total / n
+    flops = 3 * 2 * float(sum(tb.num_pairs for tb in tabs)) * C_IN * C_OUT
+    return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"{n} steps over the whole batch ({scenes} scenes x {VOXELS_PER_SCENE} voxels), numpy "
+                      "gather-matmul-scatter, BLAS thread pool", "ms_per_sample_step": dt * 1e3}
 
 
 # ----------------------------------------------------------------------------------------
@@ -168,9 +231,13 @@ def run_reference_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--repeats", type=int, default=10, help="how many times the K-step timed loop is run (median reported)")
+    ap.add_argument("--schedule", default=os.environ.get("CUMM_B200_BENCH_SCHEDULE", "concurrent"),
+                    choices=["concurrent", "sequential"],
+                    help="the three operators of a step side by side on SM shares, or one after the other")
     ap.add_argument("--scenes", type=int, default=N_SCENES,
                     help="scenes in the batch (default: the 8 of the benchmark configuration; other values are for experiments)")
     ap.add_argument("--no-extras", action="store_true", help="skip the single-scene configurations and CPU baseline")
@@ -186,7 +253,8 @@ def main():
     import torch
     import torch.distributed as dist
     from cumm_b200 import _lib
-    from cumm_b200.layer import DeviceTables, SparseConvLayer
+    from cumm_b200.layer import SparseConvLayer
+    from cumm_b200.tensorview.gemm import ConvOpType
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -211,23 +279,28 @@ def main():
         ids = list(range(rank * per, (rank + 1) * per))
     # neighbour tables of this rank's scenes, built on the GPU (bit-identical to the host generator:
     # tests/test_gpu_pairgen.py); the batch index keeps neighbours inside their scene
-    from types import SimpleNamespace
     from cumm_b200 import workloads as W
     from cumm_b200.pairgen import build_tables_gpu
     coords_h = np.concatenate([W.sample_coords(VOXELS_PER_SCENE, [4, b], batch=b) for b in ids])
     tg = build_tables_gpu(torch.from_numpy(coords_h).to(dev), n_scenes, W.GRID)
     torch.cuda.synchronize()
-    tb = SimpleNamespace(n_in=tg.n_in, n_out=tg.n_out, num_pairs=int((tg.indices >= 0).sum().item()))
-    tg.num_pairs = tb.num_pairs
-    x_h, dout_h, w_h = host_features(tb.n_in, tb.n_out, [4, 100, rank])
+    n_in, n_out = tg.n_in, tg.n_out
+    num_pairs = int((tg.indices >= 0).sum().item())
+    tg.num_pairs = num_pairs
+    feats = [host_features(VOXELS_PER_SCENE, VOXELS_PER_SCENE, [4, 100, b])[:2] for b in ids]
+    x_h = np.concatenate([f[0] for f in feats])
+    dout_h = np.concatenate([f[1] for f in feats])
     _, _, w_h = host_features(8, 8, [4, 100])  # identical weights on every rank
-    num_tiles = (tb.n_out + 127) // 128
-    fwd_bytes, wgrad_bytes = op_bytes(tb.n_out, num_tiles)
+    num_tiles = (n_out + 127) // 128
+    fwd_bytes, wgrad_bytes = op_bytes(n_out, num_tiles)
     step_bytes = 2 * fwd_bytes + wgrad_bytes
     nsets = max(2, int(np.ceil(2.2 * L2_BYTES / step_bytes)))
     nsets = min(nsets, 12)
+    concurrent = args.schedule == "concurrent"
+    shares = {ConvOpType.Forward: SHARES[0], ConvOpType.BackwardInput: SHARES[1], ConvOpType.BackwardWeight: SHARES[2]}
 
     stream = torch.cuda.Stream(device=dev)
+    s_dgrad, s_wgrad = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
     sets = []
     with torch.cuda.stream(stream):
         w_d = torch.from_numpy(w_h).to(dev)
@@ -235,32 +308,21 @@ def main():
             t = tg.clone()  # every buffer set reads its own copy of the tables
             x = torch.from_numpy(x_h).to(dev)
             dout = torch.from_numpy(dout_h).to(dev)
-            out = torch.zeros((tb.n_out, C_OUT), dtype=torch.float16, device=dev)
-            din = torch.zeros((tb.n_in, C_IN), dtype=torch.float16, device=dev)
-            dw32 = torch.zeros((C_OUT, KV, C_IN), dtype=torch.float32, device=dev)
+            out = torch.zeros((n_out, C_OUT), dtype=torch.float16, device=dev)
+            din = torch.zeros((n_in, C_IN), dtype=torch.float16, device=dev)
             dw16 = torch.zeros((C_OUT, KV, C_IN), dtype=torch.float16, device=dev)
-            layer = SparseConvLayer(t, w_d, x, out, dout, din, dw32, stream=stream.cuda_stream)
-            sets.append(dict(t=t, x=x, dout=dout, out=out, din=din, dw32=dw32, dw16=dw16, layer=layer))
+            # one GPU: the weight gradient writes fp16 itself; several: fp32 partials for the exchange
+            dw32 = torch.zeros((C_OUT, KV, C_IN), dtype=torch.float32, device=dev) if world > 1 else None
+            dw = dw32 if world > 1 else dw16
+            alone = SparseConvLayer(t, w_d, x, out, dout, din, dw, stream=stream.cuda_stream)
+            shared = SparseConvLayer(t, w_d, x, out, dout, din, dw, stream=stream.cuda_stream, cta_shares=shares)
+            sets.append(dict(t=t, x=x, dout=dout, out=out, din=din, dw32=dw32, dw16=dw16, alone=alone, shared=shared))
     stream.synchronize()
 
     ev = lambda: torch.cuda.Event(enable_timing=True)
 
-    def step_kernels(s, events=None):
-        L = s["layer"]
-        if events:
-            events[0].record(stream)
-        L.fwd.launch()
-        if events:
-            events[1].record(stream)
-        L.dgrad.launch()
-        if events:
-            events[2].record(stream)
-        L.wgrad.launch()
-        if events:
-            events[3].record(stream)
-
     # The one exchange step of the path: sum the fp32 weight-gradient partials over ranks and cast.
-    # Default: this library's one-shot sum through NVLink peer memory (cb2_peer_allreduce); with
+    # Default: this library's sum through NVLink peer memory (cb2_peer_allreduce); with
     # CUMM_B200_ALLREDUCE=nccl, or if the peer buffers cannot be set up, NCCL all-reduce + cast.
     peer_ar, exchange_kind = None, "nccl all-reduce + cast"
     if world > 1:
@@ -275,40 +337,65 @@ def main():
         agreed = torch.tensor([ok], dtype=torch.int32, device=dev)
         dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
         if int(agreed[0]) == 1:
-            exchange_kind = "one-shot sum through NVLink peer memory (own kernel), fp16 cast fused"
+            exchange_kind = "sum through NVLink peer memory (own kernel: reduce-scatter + all-gather by plain peer stores), fp16 cast fused"
         else:
             peer_ar = None
 
     def exchange(s, cuda_stream):
+        if world == 1:
+            return
         if peer_ar is not None:
             peer_ar(s["dw32"], out_f16=s["dw16"], stream=cuda_stream)
         else:
-            if world > 1:
-                dist.all_reduce(s["dw32"])
-            s["dw16"].copy_(s["dw32"])
+            red = s["dw32"].clone()
+            dist.all_reduce(red)
+            s["dw16"].copy_(red)
 
-    def step_tail(s, events=None):
+    def step_sequential(s, events=None):
+        """Eager, one operator after the other on the main stream, full grids (per-op timings)."""
+        L = s["alone"]
+        for i, call in enumerate((L.fwd, L.dgrad, L.wgrad)):
+            if events:
+                events[i].record(stream)
+            call.launch()
+        if events:
+            events[3].record(stream)
         exchange(s, stream.cuda_stream)
         if events:
             events[4].record(stream)
 
-    def step_ops(s, events=None):
-        step_kernels(s, events)
-        step_tail(s, events)
+    def step_branches(s):
+        """The step as three branches: forward on the main stream, input gradient and weight
+        gradient (followed by the exchange) on two others, joined at the end."""
+        L = s["shared"]
+        s_dgrad.wait_stream(stream)
+        s_wgrad.wait_stream(stream)
+        L.fwd.launch()
+        with torch.cuda.stream(s_wgrad):
+            L.wgrad.launch(s_wgrad.cuda_stream)
+            exchange(s, s_wgrad.cuda_stream)
+        with torch.cuda.stream(s_dgrad):
+            L.dgrad.launch(s_dgrad.cuda_stream)
+        stream.wait_stream(s_dgrad)
+        stream.wait_stream(s_wgrad)
 
-    # warm-up outside graphs (first-call set-up: attributes, status buffer, NCCL channels)
+    # warm-up outside graphs (first-call set-up: attributes, status buffer, plans, NCCL channels)
     with torch.cuda.stream(stream):
         for s in sets:
-            step_ops(s)
-    stream.synchronize()
+            step_sequential(s)
+            step_branches(s)
+    torch.cuda.synchronize()
     assert _lib.device_status() == 0, "kernel status word set during warm-up"
+    l0 = _lib.launch_count()
+    with torch.cuda.stream(stream):
+        step_branches(sets[0]) if concurrent else step_sequential(sets[0])
+    torch.cuda.synchronize()
+    launches_per_step = _lib.launch_count() - l0
 
-    # Single GPU: the whole step is one graph.  Several GPUs with the peer-memory sum: still one
-    # graph -- forward, weight gradient, then the sum on a forked stream beside the input gradient
-    # -- so a step costs the host one launch (at 8 GPUs a step is ~0.1 ms of GPU work: an eager
-    # sequence of launches and events per step was slower than one GPU).  With NCCL: graph A =
-    # forward + weight gradient, the all-reduce + cast eagerly on a side stream (NCCL stays out
-    # of capture), graph B = input gradient on the main stream.
+    # Graph capture.  One GPU, or several with the peer-memory sum: the whole step is one graph.
+    # With NCCL the all-reduce stays outside capture (a captured NCCL all-reduce hung a 2-GPU run
+    # here): graph A = forward + weight gradient, the all-reduce + cast eagerly on a side stream,
+    # graph B = input gradient.
     graphs, graphs_b = [], []
     side = torch.cuda.Stream(device=dev)
     one_graph = world == 1 or peer_ar is not None
@@ -316,25 +403,28 @@ def main():
         for s in sets:
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=stream):
-                if world == 1:
-                    step_kernels(s)
-                    step_tail(s)
-                elif one_graph:
-                    s["layer"].fwd.launch()
-                    s["layer"].wgrad.launch()
-                    side.wait_stream(stream)
-                    with torch.cuda.stream(side):
-                        exchange(s, side.cuda_stream)
-                    s["layer"].dgrad.launch()
-                    stream.wait_stream(side)
+                if one_graph:
+                    if concurrent:
+                        step_branches(s)
+                    else:
+                        L = s["alone"]
+                        L.fwd.launch()
+                        L.wgrad.launch()
+                        if world > 1:
+                            side.wait_stream(stream)
+                            with torch.cuda.stream(side):
+                                exchange(s, side.cuda_stream)
+                        L.dgrad.launch()
+                        if world > 1:
+                            stream.wait_stream(side)
                 else:
-                    s["layer"].fwd.launch()
-                    s["layer"].wgrad.launch()
+                    s["alone"].fwd.launch()
+                    s["alone"].wgrad.launch()
             graphs.append(g)
             if not one_graph:
                 gb = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(gb, stream=stream):
-                    s["layer"].dgrad.launch()
+                    s["alone"].dgrad.launch()
                 graphs_b.append(gb)
     stream.synchronize()
     ev_a = [torch.cuda.Event() for _ in range(nsets)]
@@ -361,36 +451,47 @@ def main():
         for i in range(args.warmup):
             replay(i)
     barrier()
+
+    # ---- the exchange's result, checked against the rank-ordered sum (untimed)
+    exchange_verified = None
+    if world > 1:
+        exchange_verified = verify_exchange(torch, dist, dev, stream, sets, exchange, replay, peer_ar is not None, world)
+
+    # ---- timed region: K steps, repeated; device time by CUDA events, max over ranks per repeat
     sampler = ClockSampler(physical_gpu_index(local_rank))
     sampler.start()
-    launches0 = _lib.launch_count()
-    e0, e1 = ev(), ev()
-    with torch.cuda.stream(stream):
-        if world > 1:
-            # The ranks leave the host barrier up to milliseconds apart, and a step ends in a
-            # rendezvous of all GPUs: one more untimed step lines the GPUs' timelines up (its
-            # exchange completes at the same moment everywhere), so the start events are
-            # simultaneous and the K timed steps do not include one rank waiting for another's host.
-            replay(args.warmup)
-        e0.record(stream)
-        for i in range(args.steps):
-            replay(i)
-        e1.record(stream)
-    barrier()
+    rep_ms = []
+    for r in range(max(1, args.repeats)):
+        barrier()
+        e0, e1 = ev(), ev()
+        with torch.cuda.stream(stream):
+            if world > 1:
+                # The ranks leave the host barrier up to milliseconds apart, and a step ends in a
+                # rendezvous of all GPUs: one more untimed step lines the GPUs' timelines up, so the
+                # start events are simultaneous and the K timed steps do not include one rank
+                # waiting for another's host.
+                replay(args.warmup)
+            e0.record(stream)
+            for i in range(args.steps):
+                replay(i)
+            e1.record(stream)
+        barrier()
+        rep_ms.append(e0.elapsed_time(e1) / args.steps)
     clocks = sampler.finish()
-    ms_total = e0.elapsed_time(e1)
-    # graph replays do not pass through the library's launch counter: per step forward, backward
-    # input, and the three kernels of the weight gradient (plan, main, reduce)
-    gpu_launches = 5 * args.steps
-    del launches0
+    rep_t = torch.tensor(rep_ms, dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(rep_t, op=dist.ReduceOp.MAX)
+    rep_ms = rep_t.cpu().numpy()
+    ms_step = float(np.median(rep_ms))
+    gpu_launches = int(launches_per_step) * args.steps * len(rep_ms)
 
-    # per-op durations, live, events between the launches (not graph-captured)
+    # per-op durations, live, events between eager launches with full grids (each operator alone)
     op_ms = np.zeros(4)
     reps = max(5, min(args.steps, 20))
     with torch.cuda.stream(stream):
         for i in range(reps):
             evs = [ev() for _ in range(5)]
-            step_ops(sets[i % nsets], evs)
+            step_sequential(sets[i % nsets], evs)
             stream.synchronize()
             op_ms += [evs[j].elapsed_time(evs[j + 1]) for j in range(4)]
     op_ms /= reps
@@ -401,30 +502,34 @@ def main():
         op_ms[3] = peer_ar.last_call_ns()["done"] * 1e-6
     status = _lib.device_status()
 
-    ms_step = ms_total / args.steps
-    t = torch.tensor([ms_step, float(tb.num_pairs), float(tb.n_out), float(status)], dtype=torch.float64, device=dev)
+    t = torch.tensor([float(num_pairs), float(n_out), float(status)], dtype=torch.float64, device=dev)
     if world > 1:
-        tmax = t.clone()
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
         tsum = t.clone()
         dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
-        ms_step, pairs_total, rows_total, status = float(tmax[0]), float(tsum[1]), float(tsum[2]), int(tmax[3])
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        pairs_total, rows_total, status = float(tsum[0]), float(tsum[1]), int(tmax[2])
     else:
-        pairs_total, rows_total = float(tb.num_pairs), float(tb.n_out)
+        pairs_total, rows_total = float(num_pairs), float(n_out)
     flops_step = 3 * 2 * pairs_total * C_IN * C_OUT
     value = flops_step / (ms_step * 1e-3) / 1e12
 
-    # ---- end to end through the public API with host buffers (features in, weight gradient out)
+    # ---- end to end through the public API with host buffers: both feature tensors in, all three
+    # results (output rows, input gradient, weight gradient) back, every step
     s0 = sets[0]
     x_pin = torch.from_numpy(x_h).pin_memory()
     dout_pin = torch.from_numpy(dout_h).pin_memory()
+    out_pin = torch.empty((n_out, C_OUT), dtype=torch.float16).pin_memory()
+    din_pin = torch.empty((n_in, C_IN), dtype=torch.float16).pin_memory()
     dw_pin = torch.empty((C_OUT, KV, C_IN), dtype=torch.float16).pin_memory()
     e2e_steps = max(3, min(args.steps, 10))
 
     def e2e_step():
         s0["x"].copy_(x_pin, non_blocking=True)
         s0["dout"].copy_(dout_pin, non_blocking=True)
-        step_ops(s0)
+        replay(0)
+        out_pin.copy_(s0["out"], non_blocking=True)
+        din_pin.copy_(s0["din"], non_blocking=True)
         dw_pin.copy_(s0["dw16"], non_blocking=True)
 
     with torch.cuda.stream(stream):
@@ -444,43 +549,51 @@ def main():
         e2e_ms = float(tt[0])
     e2e_value = flops_step / (e2e_ms * 1e-3) / 1e12
     h2d = x_pin.numel() * 2 + dout_pin.numel() * 2
-    d2h = dw_pin.numel() * 2
+    d2h = (out_pin.numel() + din_pin.numel() + dw_pin.numel()) * 2
 
     line = None
     if rank == 0:
-        peaks = {}
-        pk = ROOT / "MEASURED_PEAKS.json"
-        if pk.exists():
-            peaks = json.loads(pk.read_text())
-        hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
-        peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
-        names = ["forward", "backward_input", "backward_weight(+reduce)", "allreduce+cast"]
+        peak, peak_src = hbm_peak()
+        names = ["forward", "backward_input", "backward_weight", "exchange+cast"]
         dom = int(np.argmax(op_ms[:3]))
         dom_bytes = [fwd_bytes, fwd_bytes, wgrad_bytes][dom]
-        # DRAM bytes per output row from the ncu launch list of this command
-        # (profiles/bench_step_launch_list.md): 459.9 MB (forward), 460.1 MB (backward input) and
-        # 534.7 MB (backward weight: plan + main + reduce) per launch at 960 000 rows
-        traffic = [479.1, 479.3, 557.0][dom] * tb.n_out
         achieved = dom_bytes / (op_ms[dom] * 1e-3) / 1e9
+        tr, stale = measured_traffic()
+        traffic = None
+        if tr is not None:
+            traffic = float(tr["dram_bytes_per_row"][names[dom]]) * n_out
+        cfg = base_config(world, n_scenes, n_out, pairs_total)
+        run = {}
+        run.update({
+            "l2": f"rotating {nsets} buffer sets ({nsets * step_bytes / 1e6:.0f} MB touched) > 126 MB L2",
+            "schedule": (f"one CUDA graph per step, three branches side by side (max_ctas {SHARES[0]}/{SHARES[1]}/{SHARES[2]}: "
+                         "forward / backward input / backward weight)" if concurrent and one_graph else
+                         "one CUDA graph per step, operators one after the other" if one_graph else
+                         "graph(fwd+wgrad), then NCCL all-reduce + cast eagerly on a side stream overlapped with graph(dgrad)"),
+            "exchange": exchange_kind if world > 1 else "none (one GPU)",
+            "exchange_verified": exchange_verified,
+            "exchange_last_call_ns_rank0": peer_ar.last_call_ns() if peer_ar is not None else None,
+            "timed_region": f"{len(rep_ms)} repeats of {args.steps} steps; ms_per_step is the median repeat",
+        })
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "scenes_per_rank": len(ids), "rows_per_rank": tb.n_out,
-                       "pairs_total": pairs_total, "parallelism": f"scene-sharded x{world}, wgrad fp32 all-reduce",
-                       "l2": f"rotating {nsets} buffer sets ({nsets * step_bytes / 1e6:.0f} MB touched) > 126 MB L2",
-                       "timed_region": "one CUDA graph per step (N>1: the exchange on a forked stream beside dgrad)" if one_graph else "graph(fwd+wgrad), then NCCL all-reduce + cast eagerly on a side stream overlapped with graph(dgrad)",
-                       "exchange": exchange_kind if world > 1 else "none (one GPU)",
-                       "exchange_last_call_ns_rank0": peer_ar.last_call_ns() if peer_ar is not None else None},
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": cfg, "run": run,
+            "repeats": {"n": len(rep_ms), "ms_per_step_min": float(rep_ms.min()), "ms_per_step_max": float(rep_ms.max()),
+                        "spread": float((rep_ms.max() - rep_ms.min()) / ms_step)},
             "voxels_per_s": 3 * rows_total / (ms_step * 1e-3),
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms},
             "gpu_launches": gpu_launches,
-            "roofline": {"bound": "hbm", "kernel": names[dom], "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                         "frac": achieved / hbm_peak, "peak_source": peak_src, "traffic": traffic,
-                         "traffic_source": "ncu dram__bytes_read+write per row at 960k rows, scaled by rows",
+            "roofline": {"bound": "hbm", "kernel": names[dom] + " (alone, full grid)", "achieved": achieved, "peak": peak,
+                         "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src, "traffic": traffic,
+                         "traffic_source": None if tr is None else tr.get("source"), "traffic_stale": stale,
                          "algorithmic_bytes_per_launch": dom_bytes, "us_per_launch": op_ms[dom] * 1e3},
+            "roofline_step": {"bound": "hbm", "what": "all three operators of the timed step (this rank's rows)",
+                              "algorithmic_bytes_per_step": step_bytes,
+                              "achieved": step_bytes / (ms_step * 1e-3) / 1e9, "unit": "GB/s",
+                              "frac": step_bytes / (ms_step * 1e-3) / 1e9 / peak},
             "per_op_us": {names[i]: op_ms[i] * 1e3 for i in range(4)},
             "per_op_gbs": {names[i]: [fwd_bytes, fwd_bytes, wgrad_bytes][i] / (op_ms[i] * 1e-3) / 1e9 for i in range(3)},
             "status_word": status,
@@ -488,42 +601,154 @@ def main():
 
     if rank == 0 and world == 1 and not args.no_extras:
         line["single_scene"] = single_scene_configs(torch, dev, stream)
-        line["cpu_baseline"] = cpu_baseline()
+        line["config0"] = config0_dense_gemm(torch, dev, stream)
+        line["cpu_baseline"] = cpu_baseline(n_scenes)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if exchange_verified is False:
+        sys.exit(3)
+
+
+def verify_exchange(torch, dist, dev, stream, sets, exchange, replay, bit_exact, world):
+    """Compares what the exchange delivers with the fp32 partials of all ranks summed in rank
+    order (gathered with NCCL, added on the device), outside the timed region: three eager
+    calls on fresh rank-dependent data (both slot parities of the peer-memory kernel), then the
+    buffers a graph replay left behind.  The peer-memory kernel must match bit for bit and every
+    rank must hold identical fp16 results; the NCCL variant is held to fp32 round-off."""
+    rank = dist.get_rank()
+    ok = True
+
+    def check(s, what):
+        nonlocal ok
+        parts = [torch.empty_like(s["dw32"]) for _ in range(world)]
+        dist.all_gather(parts, s["dw32"])
+        acc = parts[0].clone()
+        for r in range(1, world):
+            acc += parts[r]
+        want16 = acc.to(torch.float16)
+        got16 = s["dw16"]
+        if bit_exact:
+            good = bool(torch.equal(got16.view(torch.int16), want16.view(torch.int16)))
+        else:
+            good = bool(torch.allclose(got16.float(), want16.float(), rtol=2e-3, atol=1e-3))
+        all16 = [torch.empty_like(got16) for _ in range(world)]
+        dist.all_gather(all16, got16)
+        same = all(bool(torch.equal(all16[0].view(torch.int16), a.view(torch.int16))) for a in all16)
+        if not (good and same):
+            ok = False
+            bad = int((got16.float() != want16.float()).sum())
+            print(f"[rank {rank}] exchange check failed ({what}): {bad} entries differ from the rank-ordered sum; "
+                  f"identical on all ranks: {same}", file=sys.stderr, flush=True)
+
+    s = sets[0]
+    keep = s["dw32"].clone()
+    with torch.cuda.stream(stream):
+        for call in range(3):
+            g = torch.Generator(device=dev)
+            g.manual_seed(1000 * call + rank)
+            s["dw32"].copy_(torch.randn(s["dw32"].shape, generator=g, device=dev) * (1.0 + rank))
+            s["dw16"].zero_()
+            exchange(s, stream.cuda_stream)
+            stream.synchronize()
+            check(s, f"eager call {call}")
+        s["dw32"].copy_(keep)
+        for i in range(2):
+            replay(i)
+        stream.synchronize()
+        for i in range(2):
+            check(sets[i % len(sets)], f"after graph replay of set {i % len(sets)}")
+    flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    return bool(int(flag[0]) == 1)
+
+
+def config0_dense_gemm(torch, dev, stream):
+    """The simulator-sized dense GEMM (A [128,64] x B [64,128] fp16, fp32 accumulation, alpha 1,
+    beta 0): its time on the GPU through GemmParams with no index lists, beside a single-core
+    numpy tile-loop restatement of the data flow of the reference's CPU simulator (64x64x32
+    tiles), which stands in for the simulator itself (it needs the reference's code generator)."""
+    from cumm_b200.tensorview import float16, float32
+    from cumm_b200.tensorview.gemm import GemmAlgoDesp, GemmParams, ShuffleStrideType, prepare_gemm
+    from oracle import oracle as O
+    rng = np.random.default_rng(0)
+    a = rng.uniform(-1, 1, (128, 64)).astype(np.float32).astype(np.float16)
+    b = rng.uniform(-1, 1, (64, 128)).astype(np.float32).astype(np.float16)
+    d = GemmAlgoDesp()
+    d.dtype_a = d.dtype_b = d.dtype_c = float16
+    d.dacc = d.dcomp = float32
+    d.trans_a, d.trans_b, d.trans_c = False, False, False
+    d.tile_shape = [128, 128, 64]
+    d.warp_tile_shape = [128, 128, 64]
+    d.tensorop = [128, 128, 16]
+    d.num_stage = 3
+    d.algo = "Blackwell"
+    d.shuffle_type = ShuffleStrideType.NoShuffle
+    d.element_per_access_a = d.element_per_access_b = d.element_per_access_c = 8
+    with torch.cuda.stream(stream):
+        p = GemmParams()
+        p.algo_desp = d
+        p.a, p.b = torch.from_numpy(a).to(dev), torch.from_numpy(b).to(dev)
+        p.c = torch.zeros((128, 128), dtype=torch.float16, device=dev)
+        p.stream = stream.cuda_stream
+        call = prepare_gemm(p)
+        for _ in range(5):
+            call.launch()
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for _ in range(20):
+                call.launch()
+        ts = []
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            g.replay()
+            e1.record(stream)
+            stream.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3 / 20)
+        got = p.c.cpu().numpy()
+    t0 = time.perf_counter()
+    n = 0
+    while time.perf_counter() - t0 < 2.0:
+        want = O.np_dense_gemm_tiled(a, b)
+        n += 1
+    cpu_us = (time.perf_counter() - t0) / n * 1e6
+    err = float(np.abs(got.astype(np.float32) - want.astype(np.float32)).max())
+    flop = 2 * 128 * 128 * 64
+    return {"workload": "dense GEMM 128x128x64 fp16, fp32 accumulation, alpha 1 beta 0, seed 0",
+            "gpu_us_per_call": float(np.median(ts)), "gpu_gflops": flop / float(np.median(ts)) / 1e3,
+            "gpu_timing": "CUDA graph of 20 back-to-back calls, events around a replay, / 20 (launch-bound by construction)",
+            "cpu_us_per_call": cpu_us, "cpu_gflops": flop / cpu_us / 1e3, "cpu_cores": 1,
+            "cpu_kind": "single-core numpy tile loop restating the reference simulator's data flow (64x64x32 tiles); "
+                        "the simulator itself is not importable without the reference's code generator",
+            "max_abs_diff_gpu_vs_cpu": err}
 
 
 def single_scene_configs(torch, dev, stream, reps=20, warm=3):
-    """The 150 000-voxel single-scene configurations, each op timed alone: fp16 C=K=128
-    fwd/dgrad/wgrad and int8 stride-2 fwd.  Launches rotate over buffer sets whose combined
-    footprint exceeds the 126 MB L2, so every launch reads its inputs from HBM."""
+    """The 150 000-voxel single-scene configurations: fp16 C=K=128 forward / input gradient /
+    weight gradient, each alone and the three side by side as one step; the 27-call
+    gather-GEMM-scatter sequence at C=K=64; int8 stride-2 forward.  Launches rotate over
+    buffer sets whose combined footprint exceeds the 126 MB L2, so every launch reads its
+    inputs from HBM."""
     from cumm_b200 import _lib
     from cumm_b200 import workloads as W
     from cumm_b200.layer import DeviceTables, SparseConvLayer
+    from cumm_b200.tensorview.gemm import ConvOpType
     res = {}
     coords = W.sample_coords(150000, 1)
-    hbm_peak = 6531.0
-    pk = ROOT / "MEASURED_PEAKS.json"
-    if pk.exists():
-        hbm_peak = float(json.loads(pk.read_text()).get("hbm_gbs", hbm_peak))
+    peak, _ = hbm_peak()
     NSETS = 4
 
-    def time_calls(calls):
-        """Average duration of one launch: the launches of one pass over the rotating sets
-        are captured in a CUDA graph and replayed back to back, so the figure holds the
-        kernel and the gap to the next kernel on the stream, not the host's launch path."""
+    def time_graph(capture, per):
+        """Median duration of one replay of the captured work, divided by `per`."""
         ts = []
         with torch.cuda.stream(stream):
-            for i in range(warm * len(calls)):
-                calls[i % len(calls)].launch()
-            stream.synchronize()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=stream):
-                for c in calls:
-                    c.launch()
+                capture()
             g.replay()
             stream.synchronize()
             for i in range(reps):
@@ -532,10 +757,25 @@ def single_scene_configs(torch, dev, stream, reps=20, warm=3):
                 g.replay()
                 b.record(stream)
                 stream.synchronize()
-                ts.append(a.elapsed_time(b) / len(calls))
+                ts.append(a.elapsed_time(b) / per)
         return float(np.median(ts)) * 1e3  # us
 
-    layers = []
+    def time_calls(calls):
+        """Average duration of one launch: the launches of one pass over the rotating sets
+        are captured in a CUDA graph and replayed back to back, so the figure holds the
+        kernel and the gap to the next kernel on the stream, not the host's launch path."""
+        with torch.cuda.stream(stream):
+            for i in range(warm * len(calls)):
+                calls[i % len(calls)].launch()
+            stream.synchronize()
+
+        def capture():
+            for c in calls:
+                c.launch()
+        return time_graph(capture, len(calls))
+
+    layers, shared = [], []
+    shares = {ConvOpType.Forward: SHARES[0], ConvOpType.BackwardInput: SHARES[1], ConvOpType.BackwardWeight: SHARES[2]}
     with torch.cuda.stream(stream):
         tb = W.build_tables(coords)
         rng = np.random.default_rng(2)
@@ -550,21 +790,48 @@ def single_scene_configs(torch, dev, stream, reps=20, warm=3):
             dw = torch.zeros((128, 27, 128), dtype=torch.float16, device=dev)
             t = DeviceTables.from_host(tb, dev)
             layers.append(SparseConvLayer(t, w, x, out, dout, din, dw, stream=stream.cuda_stream))
+            shared.append(SparseConvLayer(t, w, x, out, dout, din, dw, stream=stream.cuda_stream, cta_shares=shares))
     stream.synchronize()
     fb, wb = op_bytes(tb.n_out, (tb.n_out + 127) // 128)
     flops = 2 * tb.num_pairs * 128 * 128
-    for L in layers:  # the weight gradient reads the forward pass's tile masks
-        L.fwd.launch()
     for name, calls, nbytes in (("fp16_forward", [L.fwd for L in layers], fb),
                                 ("fp16_backward_input", [L.dgrad for L in layers], fb),
                                 ("fp16_backward_weight", [L.wgrad for L in layers], wb)):
         us = time_calls(calls)
         warm_us = time_calls([calls[0]] * NSETS)  # one buffer set over and over: the 95 MB working set stays in L2
         res[name] = {"us": us, "eff_tflops": flops / us / 1e6, "gbs": nbytes / us / 1e3,
-                     "frac_hbm_measured": nbytes / us / 1e3 / hbm_peak, "gvoxels_per_s": tb.n_out / us / 1e3,
+                     "frac_hbm_measured": nbytes / us / 1e3 / peak, "gvoxels_per_s": tb.n_out / us / 1e3,
                      "us_warm_l2": warm_us}
-    del layers
-    res["gather_gemm_27_calls_c64"] = config1_gather_gemm(torch, dev, stream, coords, time_calls, hbm_peak, NSETS)
+    # the whole layer step (forward + input gradient + weight gradient) as three branches
+    s2, s3 = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+
+    def step_branches(L):
+        s2.wait_stream(stream)
+        s3.wait_stream(stream)
+        L.fwd.launch()
+        with torch.cuda.stream(s3):
+            L.wgrad.launch(s3.cuda_stream)
+        with torch.cuda.stream(s2):
+            L.dgrad.launch(s2.cuda_stream)
+        stream.wait_stream(s2)
+        stream.wait_stream(s3)
+
+    with torch.cuda.stream(stream):
+        for L in shared:
+            step_branches(L)
+        stream.synchronize()
+    us = time_graph(lambda: [step_branches(L) for L in shared], NSETS)
+    sb = 2 * fb + wb
+    res["fp16_step_three_branches"] = {"us": us, "eff_tflops": 3 * flops / us / 1e6, "gbs": sb / us / 1e3,
+                                       "frac_hbm_measured": sb / us / 1e3 / peak,
+                                       "gvoxels_per_s": 3 * tb.n_out / us / 1e3,
+                                       "what": f"forward, backward input and backward weight side by side (max_ctas "
+                                               f"{SHARES[0]}/{SHARES[1]}/{SHARES[2]}), one graph of {NSETS} steps over "
+                                               "rotating buffer sets, per step",
+                                       "sequential_sum_us": sum(res[k]["us"] for k in ("fp16_forward", "fp16_backward_input",
+                                                                                       "fp16_backward_weight"))}
+    del layers, shared
+    res["gather_gemm_27_calls_c64"] = config1_gather_gemm(torch, dev, stream, coords, time_calls, peak, NSETS)
     # int8 stride-2 regular conv, k=3, pad=1
     layers3 = []
     with torch.cuda.stream(stream):
@@ -587,7 +854,7 @@ def single_scene_configs(torch, dev, stream, reps=20, warm=3):
     warm_us = time_calls([layers3[0].fwd] * NSETS)
     ops = 2 * tb3.num_pairs * 128 * 128
     res["int8_forward_stride2"] = {"us": us, "eff_tops": ops / us / 1e6, "gbs": b3 / us / 1e3,
-                                   "frac_hbm_measured": b3 / us / 1e3 / hbm_peak, "gvoxels_per_s": tb3.n_out / us / 1e3,
+                                   "frac_hbm_measured": b3 / us / 1e3 / peak, "gvoxels_per_s": tb3.n_out / us / 1e3,
                                    "us_warm_l2": warm_us}
     res["table_generation"] = time_table_generation(torch, dev, stream, coords)
     res["l2"] = f"rotating {NSETS} buffer sets per configuration (> 126 MB L2)"
@@ -623,7 +890,7 @@ def time_table_generation(torch, dev, stream, coords):
     return out
 
 
-def config1_gather_gemm(torch, dev, stream, coords, time_calls, hbm_peak, nsets):
+def config1_gather_gemm(torch, dev, stream, coords, time_calls, peak, nsets):
     """The native (non-mask) sparse convolution of the 150 000-voxel scene at C = K = 64: one
     gather-GEMM-scatter GemmParams call per filter offset that has pairs, accumulating with
     beta = 1 into a pre-zeroed output, as cumm/gemm/main_real_spconv.py:309-403 does.  The
@@ -683,22 +950,7 @@ def config1_gather_gemm(torch, dev, stream, coords, time_calls, hbm_peak, nsets)
     us = time_calls([Sequence(c) for c in sequences])
     nbytes = tb.n_in * C * 2 + tb.n_out * K * 2 + 27 * C * K * 2 + 8 * n_pairs
     return {"us": us, "calls": len(pairs), "pairs": int(n_pairs), "eff_tflops": 2 * n_pairs * C * K / us / 1e6,
-            "gbs": nbytes / us / 1e3, "frac_hbm_measured": nbytes / us / 1e3 / hbm_peak}
-
-
-def cpu_baseline():
-    """The numpy statement of one scene's step on the host cores, a bounded sample."""
-    O, tb, x, dout, w = cpu_setup(VOXELS_PER_SCENE)
-    cpu_sample_step(O, x, dout, w, tb.indices)
-    n, t_total = 0, 0.0
-    while t_total < 10.0 and n < 20:
-        t_total += cpu_sample_step(O, x, dout, w, tb.indices)
-        n += 1
-    dt = t_total / n
-    flops = 3 * 2 * tb.num_pairs * C_IN * C_OUT
-    return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
-            "sample": f"{n} steps over one scene of {VOXELS_PER_SCENE} voxels (1/8 of the batch), numpy "
-                      "gather-matmul-scatter, BLAS thread pool", "ms_per_sample_step": dt * 1e3}
+            "gbs": nbytes / us / 1e3, "frac_hbm_measured": nbytes / us / 1e3 / peak}
 
 
 if __name__ == "__main__":

@@ -58,6 +58,7 @@ class GemmArgs(ctypes.Structure):
         ("d_is_vector", ctypes.c_int),
         ("rows_A", ctypes.c_int), ("rows_B", ctypes.c_int),
         ("tile_n", ctypes.c_int), ("tile_k", ctypes.c_int),
+        ("sched_scratch", ctypes.c_void_p), ("max_ctas", ctypes.c_int), ("reuse_plan", ctypes.c_int),
     ]
 
 
@@ -92,6 +93,7 @@ class ConvArgs(ctypes.Structure):
         ("rows_A", ctypes.c_int), ("rows_B", ctypes.c_int),
         ("mask_words", ctypes.c_int),
         ("tile_n", ctypes.c_int), ("tile_k", ctypes.c_int),
+        ("sched_scratch", ctypes.c_void_p), ("max_ctas", ctypes.c_int), ("reuse_plan", ctypes.c_int),
     ]
 
 
@@ -114,6 +116,7 @@ class PairgenArgs(ctypes.Structure):
         ("mask_argsort_bwd", ctypes.c_void_p),
         ("workspace", ctypes.c_void_p),
         ("workspace_bytes", ctypes.c_size_t),
+        ("tile_masks", ctypes.c_void_p),
     ]
 
 

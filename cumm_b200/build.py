@@ -10,7 +10,7 @@ _HERE = Path(__file__).resolve().parent
 CSRC = _HERE / "csrc"
 OUT = _HERE / "libcumm_b200.so"
 SOURCES = ["api.cu"]
-HEADERS = ["ptx.cuh", "rowconv_kernel.cuh", "wgrad_kernel.cuh"]
+HEADERS = sorted(p.name for p in CSRC.glob("*.cuh"))
 
 
 def _nvcc() -> str:

@@ -137,7 +137,7 @@ int make_rows_map(CUtensorMap *map, const void *ptr, int es, uint64_t width, uin
   return CB2_OK;
 }
 
-// Which row-gather implementation the kernels use: 0 cp.async, 1 TMA row loads, 2 TMA gather4.
+// Which row-gather implementation the kernels use: 0 cp.async, otherwise TMA gather4.
 int gather_mode() {
   static int mode = -1;
   if (mode < 0) {
@@ -249,9 +249,9 @@ int launch_rowconv(const RowConvPlan &pl, const CUtensorMap &map, const CUtensor
 }
 
 // Common tail of the row-gather launches (forward, backward input, ShuffleAC GEMM).
-int run_rowconv(DeviceState *dev, RowConvParams &p, int kind, bool b_mn, int tile_n, int tile_k, const void *w_ptr,
-                uint64_t w_inner, uint64_t w_mid, uint64_t w_outer, uint64_t w_mid_stride,
-                uint64_t w_outer_stride, cudaStream_t stream) {
+int run_rowconv(DeviceState *dev, RowConvParams &p, int kind, bool b_mn, int tile_n, int tile_k, void *sched_scratch,
+                int max_ctas, const void *w_ptr, uint64_t w_inner, uint64_t w_mid, uint64_t w_outer,
+                uint64_t w_mid_stride, uint64_t w_outer_stride, cudaStream_t stream) {
   RowConvPlan pl;
   int rc = plan_rowconv(kind, p.red, p.nn, b_mn, tile_n, tile_k, &pl);
   if (rc)
@@ -287,23 +287,23 @@ int run_rowconv(DeviceState *dev, RowConvParams &p, int kind, bool b_mn, int til
   }
   p.b_lbo = static_cast<uint32_t>(kred * 128);
   p.b_sbo = 1024;
-  if (const char *v = getenv("CUMM_B200_DEBUG_SWAP_BDESC")) {
-    // Debug aid: exchange the two descriptor offsets of the MN-major weight tile.
-    if (v[0] == '1') {
-      p.b_lbo = 1024;
-      p.b_sbo = static_cast<uint32_t>(kred * 128);
-    }
-  }
   p.status = dev->status;
   // Dynamic tile scheduling draws from a pair of device counters that the kernel itself
-  // returns to zero.  Launches take counter pairs round-robin, so two launches that overlap
-  // on different streams use different pairs unless more than kTicketSlots are in flight.
+  // returns to zero: the caller's (one pair per argument record, so a captured launch never
+  // shares with anybody), else one from the device's pool taken round-robin, so that eager
+  // launches that overlap on different streams use different pairs unless more than
+  // kTicketSlots are in flight.
   static std::atomic<unsigned> next_slot{0};
-  p.tickets = getenv("CUMM_B200_STATIC_TILES") ? nullptr
-                                               : dev->status + 16 + 2 * (next_slot.fetch_add(1) % kTicketSlots);
+  CB2_CHECK_ARG((reinterpret_cast<uintptr_t>(sched_scratch) & 15u) == 0, "sched_scratch must be 16-byte aligned");
+  CB2_CHECK_ARG(max_ctas >= 0, "max_ctas must not be negative");
+  static const bool static_tiles = getenv("CUMM_B200_STATIC_TILES") != nullptr;
+  p.tickets = static_tiles    ? nullptr
+              : sched_scratch ? reinterpret_cast<int *>(sched_scratch)
+                              : dev->status + 16 + 2 * (next_slot.fetch_add(1) % kTicketSlots);
   const int ntiles = (p.n_rows + 127) / 128;
   const int gy = (p.nn + pl.block_n - 1) / pl.block_n;
-  int gx = dev->num_sms / gy;
+  const int sms = (max_ctas > 0 && max_ctas < dev->num_sms) ? max_ctas : dev->num_sms;
+  int gx = sms / gy;
   if (gx < 1)
     gx = 1;
   if (gx > ntiles)
@@ -313,28 +313,33 @@ int run_rowconv(DeviceState *dev, RowConvParams &p, int kind, bool b_mn, int til
 
 // ---------------------------------------------------------------- weight gradient
 struct WgradLayout {
-  int block_n, gy, G, slots, list_stride;
-  size_t off_flags, off_partials, off_lists, total;
+  int block_n, gy, G, list_stride;
+  size_t off_arrivals, off_acc, off_lists, total;
+  long long acc_float4;
+  int n_arrivals;
 };
 
-// Workspace of the weight gradient: 512-byte header (tile counts per offset), unit flags,
-// fp32 partials (one per unit: at most G + kv - 1 <= G + 32), and per offset the list of the
-// row tiles that carry it.
-void wgrad_layout(int num_sms, int m_total, int n_total, long long n_rows, int kv, int tile_n, WgradLayout *L) {
+// Workspace of the weight gradient: 512-byte header (tile counts per offset), the arrival
+// counters [kv][gy], the fp32 sums [kv][gy][128 x block_n], and per offset the list of the row
+// tiles that carry it.  G = CTAs per (m, n) tile of the launch.
+void wgrad_layout(int num_sms, int max_ctas, int m_total, int n_total, long long n_rows, int kv, int tile_n,
+                  WgradLayout *L) {
   L->block_n = (tile_n == 64 || tile_n == 128) ? tile_n : (n_total <= 64 ? 64 : 128);
   const int mt = (m_total + 127) / 128, nt = (n_total + L->block_n - 1) / L->block_n;
   L->gy = mt * nt;
-  L->G = num_sms / L->gy;
+  const int sms = (max_ctas > 0 && max_ctas < num_sms) ? max_ctas : num_sms;
+  L->G = sms / L->gy;
   if (L->G < 1)
     L->G = 1;
-  L->slots = L->G + 32;
-  L->off_flags = 512;
-  size_t flags_bytes = ((size_t)L->slots * L->gy * 4 + 255) / 256 * 256;
-  L->off_partials = L->off_flags + flags_bytes;
-  L->off_lists = L->off_partials + (size_t)L->slots * L->gy * 128 * L->block_n * 4;
+  const int kvs = kv > 0 ? kv : 1;
+  L->n_arrivals = kvs * L->gy;
+  L->acc_float4 = (long long)kvs * L->gy * 32 * L->block_n;
+  L->off_arrivals = 512;
+  L->off_acc = L->off_arrivals + ((size_t)L->n_arrivals * 4 + 255) / 256 * 256;
+  L->off_lists = L->off_acc + (size_t)L->acc_float4 * 16;
   const long long ntiles = (n_rows + 127) / 128;
   L->list_stride = (int)((ntiles + 63) / 64 * 64);
-  L->total = L->off_lists + (size_t)(kv > 0 ? kv : 1) * L->list_stride * 4;
+  L->total = L->off_lists + (size_t)kvs * L->list_stride * 4;
 }
 
 template <int BLOCK_N, int GATHER>
@@ -354,73 +359,48 @@ int launch_wgrad_inst(const CUtensorMap &ma, const CUtensorMap &mb, const WgradP
   return CB2_OK;
 }
 
-int run_wgrad(DeviceState *dev, WgradParams &p, int tile_n, void *workspace, size_t workspace_bytes, void *out,
-              const void *src, long long ldo, long long f_stride, float alpha, float beta, int out_f32,
-              cudaStream_t stream) {
+int run_wgrad(DeviceState *dev, WgradParams &p, int tile_n, int max_ctas, int reuse_plan, void *workspace,
+              size_t workspace_bytes, cudaStream_t stream) {
   CB2_CHECK_RT(tile_n == 0 || tile_n == 64 || tile_n == 128,
                "can't find any suitable algo: tile_shape[1] = %d (kernels exist for 64 and 128)", tile_n);
+  CB2_CHECK_ARG(max_ctas >= 0, "max_ctas must not be negative");
   WgradLayout L;
-  wgrad_layout(dev->num_sms, p.m_total, p.n_total, p.n_rows, p.kv, tile_n, &L);
+  wgrad_layout(dev->num_sms, max_ctas, p.m_total, p.n_total, p.n_rows, p.kv, tile_n, &L);
   CB2_CHECK_RT(workspace != nullptr && workspace_bytes >= L.total, "workspace at least %zu bytes.", L.total);
   CB2_CHECK_ARG(reinterpret_cast<uintptr_t>(workspace) % 256 == 0, "workspace must be 256-byte aligned");
   CB2_CHECK_ARG(p.m_total % 8 == 0 && p.n_total % 8 == 0, "channel counts must be multiples of 8");
   CB2_CHECK_ARG((p.ld_dout * 2) % 16 == 0 && (p.ld_x * 2) % 16 == 0, "row strides must be multiples of 16 bytes");
   CB2_CHECK_ARG(aligned16(p.dout) && aligned16(p.x), "operand pointers must be 16-byte aligned");
+  CB2_CHECK_ARG((reinterpret_cast<uintptr_t>(p.out) & 7u) == 0 && (reinterpret_cast<uintptr_t>(p.src) & 7u) == 0 &&
+                    p.ldo % 4 == 0 && p.f_stride % 4 == 0,
+                "the weight gradient and its row / offset strides must be 8-byte aligned");
   uint8_t *ws = reinterpret_cast<uint8_t *>(workspace);
   p.sched = reinterpret_cast<int *>(ws);
-  p.partials = reinterpret_cast<float *>(ws + L.off_partials);
+  p.arrivals = reinterpret_cast<int *>(ws + L.off_arrivals);
+  p.acc = reinterpret_cast<float *>(ws + L.off_acc);
   p.lists = reinterpret_cast<const int *>(ws + L.off_lists);
   p.list_stride = L.list_stride;
   p.status = dev->status;
-  const int ntiles = (p.n_rows + 127) / 128;
-  int rc;
-  if (ntiles > 0) {
-    wgrad_plan_kernel<<<p.kv, 1024, 0, stream>>>(p, reinterpret_cast<int *>(ws + L.off_lists), L.list_stride);
+  if (!reuse_plan) {
+    // counts and lists of the row tiles per offset; sums and arrival counters to zero
+    wgrad_plan_kernel<<<p.kv, 1024, 0, stream>>>(p, reinterpret_cast<int *>(ws + L.off_lists), L.list_stride,
+                                                 L.acc_float4, L.n_arrivals);
     CB2_CUDA(cudaGetLastError());
     g_launches.fetch_add(1);
-    CUtensorMap ma, mb;
-    rc = make_rows_map(&ma, p.dout, 2, p.m_total, p.a_rows, p.ld_dout);
-    if (rc)
-      return rc;
-    rc = make_rows_map(&mb, p.x, 2, p.n_total, p.b_rows, p.ld_x);
-    if (rc)
-      return rc;
-    const int gm = gather_mode();
-    if (L.block_n == 64)
-      rc = gm == 0 ? launch_wgrad_inst<64, 0>(ma, mb, p, L.G, L.gy, stream)
-                   : gm == 1 ? launch_wgrad_inst<64, 1>(ma, mb, p, L.G, L.gy, stream)
-                             : launch_wgrad_inst<64, 2>(ma, mb, p, L.G, L.gy, stream);
-    else
-      rc = gm == 0 ? launch_wgrad_inst<128, 0>(ma, mb, p, L.G, L.gy, stream)
-                   : gm == 1 ? launch_wgrad_inst<128, 1>(ma, mb, p, L.G, L.gy, stream)
-                             : launch_wgrad_inst<128, 2>(ma, mb, p, L.G, L.gy, stream);
-    if (rc)
-      return rc;
-  } else {
-    CB2_CUDA(cudaMemsetAsync(ws, 0, 512, stream));
   }
-  WgradReduceParams r;
-  r.partials = p.partials;
-  r.sched = p.sched;
-  r.out = out;
-  r.src = src ? src : out;
-  r.ldo = ldo;
-  r.f_stride = f_stride;
-  r.m_total = p.m_total;
-  r.n_total = p.n_total;
-  r.kv = p.kv;
-  r.block_n = L.block_n;
-  r.gy = L.gy;
-  r.G = L.G;
-  r.mask_filter = p.mode == kWgradMaskConv ? p.mask_filter : 1u;
-  r.alpha = alpha;
-  r.beta = beta;
-  r.out_f32 = out_f32;
-  const long long e4 = (long long)L.gy * (L.block_n / 4) * 128;
-  const int bx = (int)((e4 + 31) / 32);
-  CB2_CUDA(launch_after(1, wgrad_reduce_kernel, dim3(bx, p.kv), dim3(256), 0, stream, r));
-  g_launches.fetch_add(1);
-  return CB2_OK;
+  CUtensorMap ma, mb;
+  int rc = make_rows_map(&ma, p.dout, 2, p.m_total, p.a_rows, p.ld_dout);
+  if (rc)
+    return rc;
+  rc = make_rows_map(&mb, p.x, 2, p.n_total, p.b_rows, p.ld_x);
+  if (rc)
+    return rc;
+  const bool tma = gather_mode() != 0;
+  if (L.block_n == 64)
+    return tma ? launch_wgrad_inst<64, kGatherTma4>(ma, mb, p, L.G, L.gy, stream)
+               : launch_wgrad_inst<64, kGatherCpAsync>(ma, mb, p, L.G, L.gy, stream);
+  return tma ? launch_wgrad_inst<128, kGatherTma4>(ma, mb, p, L.G, L.gy, stream)
+             : launch_wgrad_inst<128, kGatherCpAsync>(ma, mb, p, L.G, L.gy, stream);
 }
 
 // ---------------------------------------------------------------- allocation-free variant
@@ -716,6 +696,11 @@ int cb2_pairgen_run(const cb2_pairgen_args *a, void *stream_v) {
   rc = radix_sort<uint32_t, true>(a->mask, a->mask_argsort, m_tmp, v_tmp, n_out, L.g.kv, hist, stream);
   if (rc)
     return rc;
+  if (a->tile_masks) {
+    cb2pg::tile_masks_kernel<<<((n_out + 127) / 128 + 7) / 8, 256, 0, stream>>>(a->mask, n_out, a->tile_masks);
+    CB2_CUDA(cudaGetLastError());
+    g_launches.fetch_add(1);
+  }
   if (bwd) {
     CB2_CUDA(cudaMemsetAsync(a->indices_bwd, 0xFF, static_cast<size_t>(L.g.kv) * n_in * 4, stream));
     const long long threads = static_cast<long long>(n_out) * L.g.kv;
@@ -812,7 +797,7 @@ size_t cb2_gemm_workspace_size(const cb2_gemm_args *a) {
   if (get_device(&dev))
     return 0;
   WgradLayout L;
-  wgrad_layout(dev->num_sms, a->m, a->n, a->k, 1, a->tile_n, &L);
+  wgrad_layout(dev->num_sms, a->max_ctas, a->m, a->n, a->k, 1, a->tile_n, &L);
   return L.total;
 }
 
@@ -823,7 +808,7 @@ size_t cb2_conv_workspace_size(const cb2_conv_args *a) {
   if (get_device(&dev))
     return 0;
   WgradLayout L;
-  wgrad_layout(dev->num_sms, a->K, a->C, a->N, a->kernel_volume, a->tile_n, &L);
+  wgrad_layout(dev->num_sms, a->max_ctas, a->K, a->C, a->N, a->kernel_volume, a->tile_n, &L);
   return L.total;
 }
 
@@ -849,7 +834,7 @@ int cb2_conv_backward_weight_static(const cb2_conv_args *a, void *stream_v) {
   const int need_words = (a->N + a->mask_width - 1) / a->mask_width;
   CB2_CHECK_RT(a->mask_words >= need_words, "reduced mask has %d words, %d needed", a->mask_words, need_words);
   WgradLayout L;
-  wgrad_layout(st->dev.num_sms, a->K, a->C, a->N, a->kernel_volume, a->tile_n, &L);
+  wgrad_layout(st->dev.num_sms, a->max_ctas, a->K, a->C, a->N, a->kernel_volume, a->tile_n, &L);
   CB2_CHECK_RT(L.total <= kStaticScratchBytes,
                "this problem (K=%d, C=%d, N=%d) needs %zu bytes of scratch; the static scratch holds %zu. Use "
                "cb2_conv_run with a caller-provided workspace instead.",
@@ -873,11 +858,16 @@ int cb2_conv_backward_weight_static(const cb2_conv_args *a, void *stream_v) {
   p.rmask_words = a->mask_words;
   p.mask_filter = a->mask_filter;
   p.mode = kWgradMaskConv;
-  // every unit flag and partial the second stage reads is rewritten by the first stage of
-  // the same call, so nothing has to be cleared between calls
-  return run_wgrad(&st->dev, p, a->tile_n, st->scratch, kStaticScratchBytes, a->ptr_C, a->ptr_D,
-                   (long long)a->kernel_volume * a->C, a->C, a->alpha, a->beta, a->dtype_c == CB2_DTYPE_F32 ? 1 : 0,
-                   stream);
+  p.out = a->ptr_C;
+  p.src = a->ptr_D ? a->ptr_D : a->ptr_C;
+  p.ldo = (long long)a->kernel_volume * a->C;
+  p.f_stride = a->C;
+  p.alpha = a->alpha;
+  p.beta = a->beta;
+  p.out_f32 = a->dtype_c == CB2_DTYPE_F32 ? 1 : 0;
+  // the planning kernel of every call clears the sums and counters the main kernel uses, so
+  // whatever an earlier call (of any size) left in the scratch does not matter
+  return run_wgrad(&st->dev, p, a->tile_n, a->max_ctas, 0, st->scratch, kStaticScratchBytes, stream);
 }
 
 int cb2_static_status(int *status) {
@@ -930,8 +920,14 @@ int cb2_gemm_run(const cb2_gemm_args *a, void *stream_v) {
     p.mask_width = 128;
     p.mask_filter = 0xffffffffu;
     p.mode = kWgradPairList;
-    return run_wgrad(dev, p, a->tile_n, a->workspace, a->workspace_bytes, a->ptr_C, a->ptr_D, a->stride_C, 0, a->alpha,
-                     a->beta, 0, stream);
+    p.out = a->ptr_C;
+    p.src = a->ptr_D ? a->ptr_D : a->ptr_C;
+    p.ldo = a->stride_C;
+    p.f_stride = 0;
+    p.alpha = a->alpha;
+    p.beta = a->beta;
+    p.out_f32 = 0;
+    return run_wgrad(dev, p, a->tile_n, a->max_ctas, a->reuse_plan, a->workspace, a->workspace_bytes, stream);
   }
   CB2_CHECK_RT(a->shuffle_type == CB2_SHUFFLE_AC || a->shuffle_type == CB2_SHUFFLE_NONE, "unknown shuffle type %d",
                a->shuffle_type);
@@ -969,7 +965,8 @@ int cb2_gemm_run(const cb2_gemm_args *a, void *stream_v) {
   const bool b_mn = !a->trans_b;
   const uint64_t inner = b_mn ? a->n : a->k;
   const uint64_t outer = b_mn ? a->k : a->n;
-  return run_rowconv(dev, p, 0, b_mn, a->tile_n, a->tile_k, a->ptr_B, inner, 1, outer, a->stride_B, a->stride_B, stream);
+  return run_rowconv(dev, p, 0, b_mn, a->tile_n, a->tile_k, a->sched_scratch, a->max_ctas, a->ptr_B, inner, 1, outer,
+                     a->stride_B, a->stride_B, stream);
 }
 
 int cb2_conv_run(const cb2_conv_args *a, void *stream_v) {
@@ -1023,9 +1020,14 @@ int cb2_conv_run(const cb2_conv_args *a, void *stream_v) {
     p.rmask_words = a->mask_words;
     p.mask_filter = a->mask_filter;
     p.mode = kWgradMaskConv;
-    return run_wgrad(dev, p, a->tile_n, a->workspace, a->workspace_bytes, a->ptr_C, a->ptr_D,
-                     (long long)a->kernel_volume * a->C, a->C, a->alpha, a->beta,
-                     a->dtype_c == CB2_DTYPE_F32 ? 1 : 0, stream);
+    p.out = a->ptr_C;
+    p.src = a->ptr_D ? a->ptr_D : a->ptr_C;
+    p.ldo = (long long)a->kernel_volume * a->C;
+    p.f_stride = a->C;
+    p.alpha = a->alpha;
+    p.beta = a->beta;
+    p.out_f32 = a->dtype_c == CB2_DTYPE_F32 ? 1 : 0;
+    return run_wgrad(dev, p, a->tile_n, a->max_ctas, a->reuse_plan, a->workspace, a->workspace_bytes, stream);
   }
   const bool dgrad = a->op_type == CB2_CONV_BACKWARD_INPUT;
   CB2_CHECK_RT(dgrad || a->op_type == CB2_CONV_FORWARD, "unknown op type %d", a->op_type);
@@ -1066,8 +1068,8 @@ int cb2_conv_run(const cb2_conv_args *a, void *stream_v) {
     p.lds = p.nn;
   }
   // weight [K, kv, C]: forward reduces over C (K-major B), backward input over K (MN-major B)
-  return run_rowconv(dev, p, kind, dgrad, a->tile_n, a->tile_k, a->ptr_B, a->C, a->kernel_volume, a->K, a->C,
-                     (uint64_t)a->kernel_volume * a->C, stream);
+  return run_rowconv(dev, p, kind, dgrad, a->tile_n, a->tile_k, a->sched_scratch, a->max_ctas, a->ptr_B, a->C,
+                     a->kernel_volume, a->K, a->C, (uint64_t)a->kernel_volume * a->C, stream);
 }
 
 } // extern "C"

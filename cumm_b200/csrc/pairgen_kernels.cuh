@@ -224,6 +224,26 @@ constexpr int kSortThreads = 256;
 constexpr int kSortItems = 8;
 constexpr int kSortTile = kSortThreads * kSortItems;
 
+// OR of the neighbour masks of each run of 128 sorted rows: what the forward kernel reports per
+// row tile and the weight gradient reads as its reduced masks.  One warp per tile.
+__global__ void __launch_bounds__(256) tile_masks_kernel(const uint32_t *__restrict__ sorted_mask, int n,
+                                                         uint32_t *__restrict__ tile_masks) {
+  const int tile = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (tile * 128 >= n)
+    return;
+  uint32_t m = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = tile * 128 + i * 32 + lane;
+    if (r < n)
+      m |= sorted_mask[r];
+  }
+  m = __reduce_or_sync(0xffffffffu, m);
+  if (lane == 0)
+    tile_masks[tile] = m;
+}
+
 template <typename K>
 __global__ void __launch_bounds__(kSortThreads) sort_hist_kernel(const K *__restrict__ keys, int n, int shift,
                                                                  int *hist, int ntiles) {

@@ -182,21 +182,24 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src, uint3
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
                : "memory");
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 // Asynchronous arrive on `bar`, triggered when all cp.async issued so far by this thread
 // have completed.  .noinc: the arrival is one of the barrier's expected count.
 __device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
 
 // Makes generic-proxy writes to shared memory (st.shared, completed cp.async) visible to
 // the async proxy (tcgen05.mma operand reads, TMA).
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// ---------------------------------------------------------------- reductions to global memory
+// Adds four floats to four consecutive floats in global memory (16-byte aligned); performed
+// in L2, no value returned.
+__device__ __forceinline__ void red_add_f32x4(void *addr, float a, float b, float c, float d) {
+  asm volatile("red.global.v4.f32.add [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
 // ---------------------------------------------------------------- TMA (no multicast)
@@ -211,13 +214,6 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void *tmap, uint
                : "memory");
 }
 
-// One row of a 2-D tensor (box {128 bytes, 1 row}); rows outside the tensor read as zeros.
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, uint32_t bar, int c0, int c1) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-               "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
-               "l"(tmap), "r"(bar), "r"(c0), "r"(c1)
-               : "memory");
-}
 // Four rows r0..r3 of a 2-D tensor, gathered into four consecutive 128-byte rows of `dst`.
 __device__ __forceinline__ void tma_gather4(uint32_t dst, const void *tmap, uint32_t bar, int c0, int r0, int r1,
                                             int r2, int r3) {
@@ -285,36 +281,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
-}
-// 16 consecutive 32-bit columns of this thread's TMEM lane.
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
-                 "=r"(r[15])
-               : "r"(taddr)
-               : "memory");
-}
-// Wait for outstanding tcgen05.ld; the registers are named as operands so that no use of
-// them can be scheduled ahead of the wait.
-__device__ __forceinline__ void tmem_ld_wait_regs16(uint32_t (&r)[16]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
-                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
-                 "+r"(r[15])
-               :
-               : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait_regs(uint32_t (&r)[32]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
-                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
-                 "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
-                 "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
-                 "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
-               :
-               : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 

@@ -71,15 +71,6 @@ struct RowConvParams {
 #ifndef CB2_ROWCONV_EPI_PARTS
 #define CB2_ROWCONV_EPI_PARTS 4
 #endif
-#ifndef CB2_ROWCONV_XU_SHARE
-#define CB2_ROWCONV_XU_SHARE 2
-#endif
-#ifndef CB2_ROWCONV_EPI_PIPE
-#define CB2_ROWCONV_EPI_PIPE 0
-#endif
-#ifndef CB2_ROWCONV_NUM_ACC
-#define CB2_ROWCONV_NUM_ACC 2
-#endif
 
 // TMA_GATHER: operand rows are fetched by the TMA unit (tile::gather4, four rows per request,
 // one warp per group) instead of 16-byte cp.async issued by 128 threads per group.  The copy
@@ -104,7 +95,7 @@ template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN, bool TMA_GATHER> struct
                                      2 * BLOCK_N * 4 + RING * RING_SLOT_INTS * 4 + (32 + 3 * RING) * 8 + 64 + 1024;
   static constexpr int SB_FIT = (232448 - FIXED_BYTES) / B_SLOT_BYTES;
   static constexpr int SB = SB_FIT < 2 ? 2 : (SB_FIT > 6 ? 6 : SB_FIT);
-  static constexpr int NUM_ACC = CB2_ROWCONV_NUM_ACC;
+  static constexpr int NUM_ACC = 2;                       // TMEM accumulators: one fills while one drains
   static constexpr int TMEM_COLS = NUM_ACC * BLOCK_N;     // 128 or 256: power of two >= 32
   // Epilogue: several threads per tile row, each converting its share of the columns.  The
   // conversion is a chain of dependent fixed-latency instructions, so its rate is set by how
@@ -614,26 +605,14 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
           const bool use_src = (p.src_mode != kSrcNone) && (p.beta != 0.f);
           // fast path: out = cvt(acc); everything else goes through the general epilogue
           const bool plain = !use_src && p.act_type == 0 && p.alpha == 1.f;
-          // With registers to spare (the variants with few threads) the next 32 columns are
-          // already on their way from TMEM while the current ones are converted.
           constexpr int ROUNDS = COLS_PER_HALF / 32;
-          constexpr bool PIPE = CB2_ROWCONV_EPI_PIPE && Cfg::THREADS <= 512 && ROUNDS > 1;
-          uint32_t vbuf[PIPE ? 2 : 1][32];
-          if (PIPE && has_work)
-            tmem_ld32(trow + half * COLS_PER_HALF, vbuf[0]);
-#pragma unroll PIPE ? ROUNDS : 1
+#pragma unroll 1
           for (int round = 0; round < ROUNDS; ++round) {
-            uint32_t(&v)[32] = vbuf[PIPE ? (round & 1) : 0];
+            uint32_t v[32];
             const int col0 = half * COLS_PER_HALF + round * 32;
             if (has_work) {
-              if constexpr (PIPE) {
-                tmem_ld_wait_regs(v);
-                if (round + 1 < ROUNDS)
-                  tmem_ld32(trow + col0 + 32, vbuf[(round + 1) & 1]);
-              } else {
-                tmem_ld32(trow + col0, v);
-                tmem_ld_wait();
-              }
+              tmem_ld32(trow + col0, v);
+              tmem_ld_wait();
             } else {
 #pragma unroll
               for (int i = 0; i < 32; ++i)
@@ -749,16 +728,8 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
               }
 #pragma unroll
               for (int i = 0; i < 32; i += 4)
-#if CB2_ROWCONV_XU_SHARE == 2
                 packed[i / 4] = pack_low_bytes(cvt_sat_s8(t[i]), cvt_sat_s8_xu(t[i + 1]), cvt_sat_s8(t[i + 2]),
                                                cvt_sat_s8_xu(t[i + 3]));
-#elif CB2_ROWCONV_XU_SHARE == 1
-                packed[i / 4] = pack_low_bytes(cvt_sat_s8(t[i]), cvt_sat_s8(t[i + 1]), cvt_sat_s8(t[i + 2]),
-                                               cvt_sat_s8_xu(t[i + 3]));
-#else
-                packed[i / 4] = pack_low_bytes(cvt_sat_s8(t[i]), cvt_sat_s8(t[i + 1]), cvt_sat_s8(t[i + 2]),
-                                               cvt_sat_s8(t[i + 3]));
-#endif
 #pragma unroll
               for (int q = 0; q < 2; ++q) {
                 const int c = (col0 / 32) * CH_PER_ROUND + q;

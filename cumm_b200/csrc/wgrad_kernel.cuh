@@ -6,10 +6,12 @@
 // The reduction runs over (sorted) rows, so both tcgen05 operands are gathered rows held
 // "MN-major": a gathered row is 128-byte-swizzled along its channels and the 128 rows of a
 // tile are the K dimension of the MMA.  Work is cut into units (filter offset f, range of
-// row tiles); a unit accumulates in TMEM and leaves one fp32 partial [128 x BLOCK_N] in
-// the workspace.  A second kernel adds the partials of each f in a fixed order, applies
-// alpha/beta and converts: no atomics and no inter-CTA waits (the reference serialises
-// split-K slices through a spinning semaphore, cumm/conv/kernel.py:960-1083).
+// row tiles); a unit accumulates in TMEM and adds its fp32 result [128 x BLOCK_N] into the
+// offset's accumulator in the workspace (vector reductions that complete in L2), then counts
+// itself in; the CTA whose unit completes an offset applies alpha/beta, converts, writes dW and
+// puts the accumulator and the counter back to zero.  One launch, and nobody waits for anybody
+// (the reference serialises split-K slices through a spinning semaphore,
+// cumm/conv/kernel.py:960-1083).
 //
 // Semantics follow cumm/gemm/blockmma/mma.py:608-648,722-740 (a row takes part for
 // offset f iff the reduced-mask word covering it has bit f), cumm/conv/sparse_iters.py
@@ -22,10 +24,9 @@
 namespace cb2 {
 
 enum : int { kWgradMaskConv = 0, kWgradPairList = 1 };
-// Row-gather implementations: 16-byte cp.async per chunk; one TMA tile load per (row, 128-byte
-// column block) where a row coordinate of -1 is out of bounds and reads as zeros; TMA
-// tile::gather4, four rows per request.
-enum : int { kGatherCpAsync = 0, kGatherTmaRow = 1, kGatherTma4 = 2 };
+// Row-gather implementations: 16-byte cp.async per chunk, or TMA tile::gather4, four rows per
+// request (a row coordinate of -1 is out of bounds and reads as zeros).
+enum : int { kGatherCpAsync = 0, kGatherTma4 = 2 };
 
 struct WgradParams {
   const void *dout;        // A rows [*, m_total]  (fp16)
@@ -35,12 +36,18 @@ struct WgradParams {
   const int32_t *argsort;  // [n_rows]
   const int32_t *a_inds;   // pair-list mode
   const int32_t *b_inds;   //   "
-  float *partials;         // workspace: [unit][m_tile][n_tile][128][BLOCK_N] fp32
-  int *sched;              // workspace header: [0,32) number of row tiles carrying offset f; [32,64) units of
-                           // offset f and [64,96) the first of them (written by the first stage for the second)
+  float *acc;              // workspace: [f][m_tile][n_tile][128 x BLOCK_N] fp32 sums, zero between calls
+  int *arrivals;           // workspace: [f][m_tile][n_tile] units that have added their share, zero between calls
+  int *sched;              // workspace header: [0,32) number of row tiles carrying offset f
   const int *lists;        // workspace: per offset, the ordered list of those tiles
   int list_stride;         // ints between two offsets' lists
   int *status;
+  void *out;               // dW
+  const void *src;         // source for beta (dW itself unless the caller gave another)
+  long long ldo;           // elements between consecutive m rows of out
+  long long f_stride;      // elements between consecutive f slices
+  float alpha, beta;
+  int out_f32;
   long long ld_dout, ld_x;
   int n_rows;
   int a_rows, b_rows;
@@ -58,11 +65,11 @@ template <int BLOCK_N, int GATHER> struct WgradCfg {
   static constexpr int B_BYTES = 128 * 2 * BLOCK_N;         // 128 rows x BLOCK_N fp16
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TMEM_COLS = 2 * BLOCK_N;
-  static constexpr int THREADS = 128 + 64 + SA * 128;       // epilogue, mma + spare, 3 gather groups
+  static constexpr int THREADS = 128 + 32 + SA * 128;       // epilogue, mma, 3 gather groups
   static constexpr int FULL_COUNT = GATHER == kGatherCpAsync ? 128 : 1;
   static constexpr int OFF_STAGES = 0;
   static constexpr int OFF_ROWIDX = SA * STAGE_BYTES;       // SA x 2 buffers x 2 operands x 128 ints
-  static constexpr int OFF_SCHED = OFF_ROWIDX + SA * 2 * 2 * 128 * 4;  // this CTA's units
+  static constexpr int OFF_SCHED = OFF_ROWIDX + SA * 2 * 2 * 128 * 4;  // this CTA's units, then units per offset
   static constexpr int TILE_CAP = 2048;                      // tiles of one CTA staged in shared memory
   static constexpr int OFF_TILES = OFF_SCHED + 256 * 4;
   static constexpr int OFF_BARS = OFF_TILES + TILE_CAP * 4;
@@ -96,8 +103,11 @@ __device__ __forceinline__ uint32_t wgrad_tile_mask(const WgradParams &p, int ti
 // and leaves one fp32 partial.  The units of an offset are consecutive in this numbering, and
 // there are at most G + kv - 1 of them.
 //
-// A first small kernel (one block per offset) writes, per offset, the count and the ordered
-// list of its tiles; both later kernels derive everything else from the kv counts.
+// A small planning kernel (one block per offset) writes, per offset, the count and the ordered
+// list of its tiles, and clears the accumulators and arrival counters; the main kernel derives
+// everything else from the kv counts.  The plan depends only on the reduced masks, the row
+// count and the mask filter, so a caller that runs the same layer again (the next training
+// step) may keep it: see `reuse_plan` in the C ABI.
 //   sched[f]                      tiles carrying offset f
 //   lists[f * list_stride + k]    the k-th of them
 
@@ -138,13 +148,23 @@ __device__ __forceinline__ void wgrad_plan_warp(int cnt, int G, int &P, int &T, 
 // One block per filter offset: count and list the tiles that carry it.  Warp w owns a
 // contiguous span of tiles, so the list comes out in ascending order with one block-wide
 // synchronisation per batch of 1024 * K tiles.
-__global__ void __launch_bounds__(1024) wgrad_plan_kernel(const WgradParams p, int *lists, int list_stride) {
+__global__ void __launch_bounds__(1024) wgrad_plan_kernel(const WgradParams p, int *lists, int list_stride,
+                                                           long long acc_float4, int n_arrivals) {
   constexpr int K = 4;  // 4096 tiles per batch
   __shared__ int s_w[32];
   const int f = blockIdx.x;
+  // sums and arrival counters start from zero (every later call leaves them at zero again)
+  {
+    float4 *a4 = reinterpret_cast<float4 *>(p.acc);
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < acc_float4;
+         i += (long long)gridDim.x * blockDim.x)
+      a4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_arrivals; i += gridDim.x * blockDim.x)
+      p.arrivals[i] = 0;
+  }
   const int ntiles = (p.n_rows + 127) / 128;
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  grid_dep_launch();  // the first stage may set itself up meanwhile; it waits before reading the lists
+  grid_dep_launch();  // the main kernel may set itself up meanwhile; it waits before reading the lists
   int *list = lists + (long long)f * list_stride;
   int running = 0;
   for (int base = 0; base < ntiles; base += 1024 * K) {
@@ -186,7 +206,9 @@ __global__ void __launch_bounds__(1024) wgrad_plan_kernel(const WgradParams p, i
 // Per CTA, in shared memory: s_plan[0] = number of units of this CTA, then five ints per unit
 // {f, first list index, one past the last, unit number, offset of its tiles in s_tiles};
 // s_tiles = the CTA's tiles in step order (when they fit; otherwise the walk reads the lists).
-constexpr int kWgradPlanInts = 8 + 5 * 32;
+// After the unit records: s_plan[kWgradPlanUnits + f] = units of offset f over all CTAs.
+constexpr int kWgradPlanUnits = 8 + 5 * 32;
+constexpr int kWgradPlanInts = kWgradPlanUnits + 32;
 template <int TILE_CAP>
 __device__ __forceinline__ void wgrad_load_plan(const WgradParams &p, const int *lists, int list_stride, int *s_plan,
                                                 int *s_tiles) {
@@ -196,10 +218,7 @@ __device__ __forceinline__ void wgrad_load_plan(const WgradParams &p, const int 
     const int cnt = (f < p.kv) ? __ldg(p.sched + f) : 0;
     int P, T, c_first, S, U;
     wgrad_plan_warp(cnt, G, P, T, c_first, S, U);
-    if (c == 0 && blockIdx.y == 0) {
-      p.sched[32 + f] = S;
-      p.sched[64 + f] = U;
-    }
+    s_plan[kWgradPlanUnits + f] = S;
     const int b0 = (int)(((long long)c * T) / G), b1 = (int)(((long long)(c + 1) * T) / G);
     const bool has = cnt > 0 && c >= c_first && c < c_first + S;
     int k0 = 0, k1 = 0;
@@ -318,7 +337,7 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
   }
   if (threadIdx.x == 0)
     CB2_TRACE_EVENT(5, 10, 0);
-  grid_dep_launch();  // lets the second stage be scheduled as soon as SMs free up
+  grid_dep_launch();  // lets the next kernel on the stream be scheduled as soon as SMs free up
   grid_dep_wait();    // counts and lists come from the planning kernel
   wgrad_load_plan<Cfg::TILE_CAP>(p, p.lists, p.list_stride, s_plan, s_tiles);  // contains __syncthreads
   if (threadIdx.x == 0)
@@ -336,52 +355,106 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
   const int gy = gridDim.y;
 
   if (warp < 4) {
-    // ======================= epilogue: one fp32 partial per unit
+    // ======================= epilogue: add each unit's result into its offset's sums; the unit
+    // that completes an offset turns the sums into dW
     const int et = threadIdx.x;
+    const int *s_units = s_plan + kWgradPlanUnits;
+    const long long tile_f4 = 32ll * BLOCK_N;  // float4 per [128 x BLOCK_N] tile
+    // sums layout: float4 (col/4, row) at index (col/4) * 128 + row, so that the 32 rows of a
+    // warp touch 512 contiguous bytes
+    auto sums_of = [&](int f) { return reinterpret_cast<float4 *>(p.acc) + ((long long)f * gy + blockIdx.y) * tile_f4; };
+    // dW[m0 + row, f, n0 + 4 * q .. + 3] from four sums
+    auto write_out = [&](int f, int row, int q, float4 v) {
+      const int m = m0 + row, n = n0 + 4 * q;
+      if (m >= p.m_total || n >= p.n_total)
+        return;
+      const long long off = (long long)m * p.ldo + (long long)f * p.f_stride + n;
+      float r[4] = {v.x, v.y, v.z, v.w};
+      if (p.out_f32) {
+        float *o = reinterpret_cast<float *>(p.out);
+        const float *sp = reinterpret_cast<const float *>(p.src);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          o[off + j] = (p.beta != 0.f) ? __fmaf_rn(p.alpha, r[j], __fmul_rn(p.beta, sp[off + j])) : __fmul_rn(p.alpha, r[j]);
+      } else {
+        __half *o = reinterpret_cast<__half *>(p.out);
+        const __half *sp = reinterpret_cast<const __half *>(p.src);
+        __half h[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float t = (p.beta != 0.f) ? __fmaf_rn(p.alpha, r[j], __fmul_rn(p.beta, __half2float(sp[off + j])))
+                                          : __fmul_rn(p.alpha, r[j]);
+          h[j] = __float2half_rn(t);
+        }
+        *reinterpret_cast<uint2 *>(o + off) = *reinterpret_cast<const uint2 *>(h);
+      }
+    };
+    // Offsets inside the filter that no row tile carries get alpha * 0 + beta * source; CTA c
+    // takes those with f = c (mod G).
+    for (int f = blockIdx.x; f < p.kv; f += gridDim.x)
+      if (((p.mask_filter >> f) & 1u) && s_units[f] == 0)
+        for (int q = 0; q < BLOCK_N / 4; ++q)
+          write_out(f, et, q, make_float4(0.f, 0.f, 0.f, 0.f));
     int acc_use = 0;
     wgrad_walk(
         p.lists, p.list_stride, s_plan, s_tiles, [&](int, int) -> bool { return true; },
         [&](int, int, bool) -> bool { return true; },
         [&](int u, int f, int active) -> bool {
-          if (active == 0) {
-            // a unit without tiles (fewer steps than CTAs) still owns a partial: all zeros
-            uint4 *dst = reinterpret_cast<uint4 *>(p.partials + ((long long)u * gy + blockIdx.y) * 128 * BLOCK_N) + et;
-            for (int q = 0; q < BLOCK_N / 4; ++q)
-              dst[q * 128] = make_uint4(0u, 0u, 0u, 0u);
-            return true;
+          float4 *sums = sums_of(f) + et;
+          if (active > 0) {
+            const int buf = acc_use & 1;
+            if (et == 0) {
+              CB2_TRACE_EVENT(4, 7, u);
+              bool ok = mbar_wait(acc_full(buf), (acc_use >> 1) & 1, abort_flag);
+              CB2_TRACE_EVENT(4, 8, u);  // accumulator complete
+              misc[2] = ok ? 1 : 0;
+              if (!ok)
+                fail(kStatusWaitTimeout);
+            }
+            named_bar_sync(1, 128);
+            if (misc[2] == 0)
+              return false;
+            tc_fence_after();
+            const uint32_t trow = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
+                                  static_cast<uint32_t>(buf * BLOCK_N);
+#pragma unroll 1
+            for (int round = 0; round < BLOCK_N / 32; ++round) {
+              uint32_t v[32];
+              tmem_ld32(trow + round * 32, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                red_add_f32x4(sums + (round * 8 + q) * 128, __uint_as_float(v[q * 4]), __uint_as_float(v[q * 4 + 1]),
+                              __uint_as_float(v[q * 4 + 2]), __uint_as_float(v[q * 4 + 3]));
+            }
+            tc_fence_before();
+            mbar_arrive(acc_empty(buf));
+            ++acc_use;
+            __threadfence();  // this thread's additions are performed before the unit is counted in
           }
-          const int buf = acc_use & 1;
+          // a unit without tiles (fewer steps than CTAs) is still counted: the offset is complete
+          // when all of its units have arrived
+          named_bar_sync(1, 128);
           if (et == 0) {
-            CB2_TRACE_EVENT(4, 7, u);
-            bool ok = mbar_wait(acc_full(buf), (acc_use >> 1) & 1, abort_flag);
-            CB2_TRACE_EVENT(4, 8, u);  // accumulator complete
-            misc[2] = ok ? 1 : 0;
-            if (!ok)
-              fail(kStatusWaitTimeout);
+            int *counter = p.arrivals + (long long)f * gy + blockIdx.y;
+            const int before = atomicAdd(counter, 1);
+            misc[6] = (before == s_units[f] - 1) ? 1 : 0;
+            if (before == s_units[f] - 1) {
+              *counter = 0;       // ready for the next call on this workspace
+              __threadfence();    // order the reads below after everybody's additions
+            }
           }
           named_bar_sync(1, 128);
-          if (misc[2] == 0)
-            return false;
-          tc_fence_after();
-          const uint32_t trow = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
-                                static_cast<uint32_t>(buf * BLOCK_N);
-          // partial layout: float4 (col/4, row) at index (col/4) * 128 + row, so that the 32
-          // rows of a warp store 512 contiguous bytes
-          uint4 *dst = reinterpret_cast<uint4 *>(p.partials + ((long long)u * gy + blockIdx.y) * 128 * BLOCK_N) + et;
-#pragma unroll 1
-          for (int round = 0; round < BLOCK_N / 32; ++round) {
-            uint32_t v[32];
-            tmem_ld32(trow + round * 32, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-              dst[(round * 8 + q) * 128] = make_uint4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+          if (misc[6]) {
+#pragma unroll 4
+            for (int q = 0; q < BLOCK_N / 4; ++q) {
+              const float4 v = __ldcg(sums + q * 128);
+              __stcg(sums + q * 128, make_float4(0.f, 0.f, 0.f, 0.f));
+              write_out(f, et, q, v);
+            }
           }
-          tc_fence_before();
-          mbar_arrive(acc_empty(buf));
-          ++acc_use;
           if (et == 0)
-            CB2_TRACE_EVENT(4, 9, u);  // partial written
+            CB2_TRACE_EVENT(4, 9, u);  // unit added
           return true;
         });
   } else if (warp == 4) {
@@ -449,12 +522,10 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
         fail(kStatusWaitTimeout);
     }
     __syncwarp();
-  } else if (warp == 5) {
-    // spare warp (keeps the role layout aligned with the row-conv kernel)
   } else {
     // ======================= gather both operands: group g owns stage g
-    const int g = (warp - 6) >> 2;
-    const int gt = threadIdx.x - (6 * 32 + g * 128);
+    const int g = (warp - 5) >> 2;
+    const int gt = threadIdx.x - (5 * 32 + g * 128);
     int *group_rowidx = rowidx + g * 512;
     volatile int *my_flag = misc + 3 + g;
     int step = 0;
@@ -550,15 +621,8 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
               CB2_TRACE_EVENT(g, 2, step - 1);  // stage free
               mbar_arrive_expect_tx(full_s(g), Cfg::STAGE_BYTES);
             }
-            // one 128-byte row slot per thread and column block; row -1 reads as zeros
-            if constexpr (GATHER == kGatherTmaRow) {
-#pragma unroll
-              for (int ka = 0; ka < 2; ++ka)
-                tma_load_2d(a_stage + ka * (128 * 128) + gt * 128, &tmap_dout, full_s(g), m0 + ka * 64, ia);
-#pragma unroll
-              for (int kb = 0; kb < BLOCK_N / 64; ++kb)
-                tma_load_2d(b_stage + kb * (128 * 128) + gt * 128, &tmap_x, full_s(g), n0 + kb * 64, ib);
-            } else {
+            // four rows per request and column block; row -1 reads as zeros
+            {
               const int a1 = __shfl_down_sync(0xffffffffu, ia, 1), a2 = __shfl_down_sync(0xffffffffu, ia, 2),
                         a3 = __shfl_down_sync(0xffffffffu, ia, 3);
               const int b1 = __shfl_down_sync(0xffffffffu, ib, 1), b2 = __shfl_down_sync(0xffffffffu, ib, 2),
@@ -589,110 +653,6 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
   if (warp == 4) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
-  }
-}
-
-// Second stage: out[m, f, n] = alpha * sum_units partial + beta * prev, fixed unit order.
-// OUT_F32 selects fp32 output (multi-GPU partial sums) instead of fp16.
-struct WgradReduceParams {
-  const float *partials;
-  const int *sched;
-  void *out;
-  const void *src;
-  long long ldo;       // elements between consecutive m rows of out
-  long long f_stride;  // elements between consecutive f slices
-  int m_total, n_total, kv;
-  int block_n;
-  int gy;              // m_tiles * n_tiles of the first stage
-  int G;               // CTAs per (m, n) tile of the first stage: fixes the unit numbering
-  uint32_t mask_filter;
-  float alpha, beta;
-  int out_f32;
-};
-
-// The partials of a unit are one contiguous array of E4 = gy * (block_n/4) * 128 float4
-// (index e4 = (by * block_n/4 + col/4) * 128 + row), so the reduction is a sum of S_f such
-// arrays.  Offsets with few units: one thread per float4.  Offsets with many (the centre
-// of a submanifold conv has one per CTA): the 8 warps of a block each add every 8th unit
-// for 32 float4, and the 8 sums are combined in a fixed order.  No atomics: deterministic.
-__global__ void __launch_bounds__(256) wgrad_reduce_kernel(const WgradReduceParams p) {
-  __shared__ float4 s_part[8][32];
-  // blocks are dispatched in blockIdx order: start with the centre offset, which carries by
-  // far the most units in a submanifold convolution, so its blocks are not left for the tail
-  const int f = (blockIdx.y + p.kv / 2) % p.kv;
-  if (!((p.mask_filter >> f) & 1u))
-    return;
-  grid_dep_wait();  // partials and unit ranges come from the first stage
-  const int S = p.sched[32 + f], base = p.sched[64 + f];
-  const int bn4 = p.block_n >> 2;
-  const long long E4 = (long long)p.gy * bn4 * 128;
-  const bool split = S > 8;
-  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  long long e4;
-  if (split) {
-    e4 = (long long)blockIdx.x * 32 + lane;
-  } else {
-    e4 = (long long)blockIdx.x * 256 + threadIdx.x;
-    if ((long long)blockIdx.x * 256 >= E4)
-      return;
-  }
-  const bool in_range = e4 < E4;
-  const int by = in_range ? (int)(e4 / (bn4 * 128)) : 0;
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (in_range) {
-    // every unit owns a partial (all zeros if it had no tiles), so the sum is a plain strided read
-    const float4 *src = reinterpret_cast<const float4 *>(p.partials) + (long long)base * E4 + e4;
-    const int first = split ? wid : 0, stride = split ? 8 : 1;
-#pragma unroll 8
-    for (int s = first; s < S; s += stride) {
-      const float4 v = __ldg(src + (long long)s * E4);
-      acc.x += v.x;
-      acc.y += v.y;
-      acc.z += v.z;
-      acc.w += v.w;
-    }
-  }
-  float r[4] = {acc.x, acc.y, acc.z, acc.w};
-  if (split) {
-    s_part[wid][lane] = acc;
-    __syncthreads();
-    if (wid != 0)
-      return;
-    r[0] = r[1] = r[2] = r[3] = 0.f;
-#pragma unroll
-    for (int w = 0; w < 8; ++w) {
-      const float4 v = s_part[w][lane];
-      r[0] += v.x;
-      r[1] += v.y;
-      r[2] += v.z;
-      r[3] += v.w;
-    }
-  }
-  if (!in_range)
-    return;
-  const int n_tiles_n = (p.n_total + p.block_n - 1) / p.block_n;
-  const int rem = (int)(e4 % (bn4 * 128));
-  const int col4 = rem >> 7, row = rem & 127;
-  const int m = (by / n_tiles_n) * 128 + row;
-  const int n = (by % n_tiles_n) * p.block_n + col4 * 4;
-  if (m >= p.m_total || n >= p.n_total)
-    return;
-  const long long off = (long long)m * p.ldo + (long long)f * p.f_stride + n;
-  if (p.out_f32) {
-    float *o = reinterpret_cast<float *>(p.out);
-    const float *sp = reinterpret_cast<const float *>(p.src);
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-      o[off + j] = (p.beta != 0.f) ? __fmaf_rn(p.alpha, r[j], __fmul_rn(p.beta, sp[off + j])) : __fmul_rn(p.alpha, r[j]);
-  } else {
-    __half *o = reinterpret_cast<__half *>(p.out);
-    const __half *sp = reinterpret_cast<const __half *>(p.src);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float t = (p.beta != 0.f) ? __fmaf_rn(p.alpha, r[j], __fmul_rn(p.beta, __half2float(sp[off + j])))
-                                      : __fmul_rn(p.alpha, r[j]);
-      o[off + j] = __float2half_rn(t);
-    }
   }
 }
 

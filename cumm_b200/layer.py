@@ -89,7 +89,9 @@ class DeviceTables:
                 a = a.view(np.int32)
             return torch.from_numpy(np.ascontiguousarray(a)).to(device)
 
-        mo = torch.zeros(((tb.n_out + TILE_M - 1) // TILE_M,), dtype=torch.int32, device=device)
+        # per-tile OR of the sorted masks: what the forward pass reports and the weight gradient reads
+        mo = up(np.bitwise_or.reduceat(tb.mask, np.arange(0, max(tb.n_out, 1), TILE_M))[:(tb.n_out + TILE_M - 1) // TILE_M]
+                if tb.n_out else np.zeros(0, np.uint32))
         return DeviceTables(tb.n_in, tb.n_out, tb.kv, up(tb.indices), up(tb.mask), up(tb.mask_argsort),
                             up(tb.indices_bwd), up(tb.mask_bwd), up(tb.mask_argsort_bwd), mo, tb.num_pairs)
 
@@ -98,10 +100,13 @@ class SparseConvLayer:
     """Prepared forward / backward-input / backward-weight calls over fixed buffers."""
 
     def __init__(self, tables: DeviceTables, weight, x, out, dout=None, din=None, dw=None, stream: int = 0,
-                 tiles=None):
+                 tiles=None, cta_shares=None):
         """``tiles``: optional {ConvOpType: tile_shape} (e.g. from the tuner); ops without an entry
-        use :func:`default_tile`."""
+        use :func:`default_tile`.  ``cta_shares``: optional {ConvOpType: CTAs} bounding each launch
+        (``max_ctas``), for a caller that runs the three ops side by side on three streams.
+        The tables are fixed for the life of the layer, so the weight gradient plans once."""
         self.t = tables
+        shares = dict(cta_shares or {})
         tiles = dict(tiles or {})
         K, C = int(weight.shape[0]), int(weight.shape[2])
         self.fwd: Optional[PreparedCall] = None
@@ -114,16 +119,18 @@ class SparseConvLayer:
         p.indices, p.mask, p.mask_argsort = tables.indices, tables.mask, tables.mask_argsort
         p.mask_output = tables.mask_output
         p.stream = stream
+        p.max_ctas = int(shares.get(ConvOpType.Forward, 0))
         self.fwd_params = p
         if not int8_inf:
-            self.fwd = prepare_conv(p)
+            self.fwd = prepare_conv(p, static_tables=True)
         if dout is not None and din is not None:
             q = ConvParams(3, ConvOpType.BackwardInput)
             q.conv_algo_desp = make_desp(ConvOpType.BackwardInput, False, C, K, tiles.get(ConvOpType.BackwardInput))
             q.input, q.weight, q.output = din, weight, dout
             q.indices, q.mask, q.mask_argsort = tables.indices_bwd, tables.mask_bwd, tables.mask_argsort_bwd
             q.stream = stream
-            self.dgrad = prepare_conv(q)
+            q.max_ctas = int(shares.get(ConvOpType.BackwardInput, 0))
+            self.dgrad = prepare_conv(q, static_tables=True)
         if dout is not None and dw is not None:
             r = ConvParams(3, ConvOpType.BackwardWeight)
             r.conv_algo_desp = make_desp(ConvOpType.BackwardWeight, False, C, K, tiles.get(ConvOpType.BackwardWeight))
@@ -132,8 +139,9 @@ class SparseConvLayer:
             r.mask_width = TILE_M
             r.split_k_slices = 32
             r.stream = stream
-            self.wgrad = prepare_conv(r)
+            r.max_ctas = int(shares.get(ConvOpType.BackwardWeight, 0))
+            self.wgrad = prepare_conv(r, static_tables=True)
 
     def prepare_int8(self, scale, bias) -> None:
         self.fwd_params.scale, self.fwd_params.bias = scale, bias
-        self.fwd = prepare_conv(self.fwd_params)
+        self.fwd = prepare_conv(self.fwd_params, static_tables=True)

@@ -59,8 +59,9 @@ def build_tables_gpu(in_coords, batch_size: int, grid: Sequence[int], ksize=(3, 
             mbwd = torch.empty((n_in,), dtype=torch.int32, device=dev)
             abwd = torch.empty((n_in,), dtype=torch.int32, device=dev)
             a.indices_bwd, a.mask_bwd, a.mask_argsort_bwd = ibwd.data_ptr(), mbwd.data_ptr(), abwd.data_ptr()
-        _lib.raise_for(L.cb2_pairgen_run(ctypes.byref(a), ctypes.c_void_p(stream)))
         mask_output = torch.zeros(((n_out + 127) // 128,), dtype=torch.int32, device=dev)
+        a.tile_masks = mask_output.data_ptr()
+        _lib.raise_for(L.cb2_pairgen_run(ctypes.byref(a), ctypes.c_void_p(stream)))
     # the kernels enqueued above still read the workspace: it lives as long as the tables do
     tables = DeviceTables(n_in, n_out, kv, indices, mask, argsort, ibwd, mbwd, abwd, mask_output, -1, keep=ws)
     return (tables, out_coords) if return_out_coords else tables

@@ -388,6 +388,7 @@ class GemmParams:
         self.stream = 0
         self.timer = timer
         self.nvrtc_params = NVRTCParams()
+        self.max_ctas = 0  # not in the reference: see ConvParams.max_ctas
 
     # setters copy the dtype into the descriptor (params.h:366-388)
     @property
@@ -480,6 +481,9 @@ class ConvParams:
         self.mask_output = None
         self.stream = 0
         self.nvrtc_params = NVRTCParams()
+        # Not in the reference: upper bound on the CTAs of the launch (0 = one per SM), for calls
+        # that run side by side on different streams (``cb2_conv_args.max_ctas``).
+        self.max_ctas = 0
 
 
 # --------------------------------------------------------------------------------------
@@ -491,7 +495,11 @@ _WORKSPACES = {}
 def _workspace_for(device: int, stream: int, nbytes: int, user_ws):
     """The reference's callee allocates scratch when the caller passes none
     (cumm/gemm/nvrtc_code.py:137-140).  Here a per-(device, stream) buffer is cached so no
-    allocation happens on the steady-state path."""
+    allocation happens on the steady-state path.  Calls on one stream that rely on it share
+    the buffer; they are ordered by the stream, and the weight-gradient kernel waits for its
+    predecessor before it touches the workspace, so they do not race.  Callers that run weight
+    gradients on several streams at once pass their own ``workspace`` (or use
+    :func:`prepare_conv`, which gives every call its own)."""
     t = as_view(user_ws)
     if t is not None and t.nbytes() >= nbytes and t.data_ptr() % 256 == 0:
         return t.data_ptr(), t.nbytes()
@@ -585,6 +593,7 @@ def _gemm_args(params: GemmParams) -> _lib.GemmArgs:
                            "kernels work on 128-row tiles)")
     args.tile_n = int(desp.tile_shape[1])
     args.tile_k = int(desp.tile_shape[2]) if desp.shuffle_type != ShuffleStrideType.ShuffleAB else 0
+    args.max_ctas = int(getattr(params, "max_ctas", 0))
     args._device = c.device
     return args
 
@@ -710,6 +719,7 @@ def _conv_args(params: ConvParams) -> _lib.ConvArgs:
                            "kernels work on 128-row tiles)")
     args.tile_n = int(desp.tile_shape[1])
     args.tile_k = int(desp.tile_shape[2]) if op != ConvOpType.BackwardWeight else 0
+    args.max_ctas = int(getattr(params, "max_ctas", 0))
     args._device = c_t.device
     return args
 
@@ -741,14 +751,22 @@ def run_nvrtc_conv_kernel(params: ConvParams) -> None:
 
 class PreparedCall:
     """A validated call with its flat argument record built once, for launch-bound loops
-    (replays, CUDA-graph capture): ``launch()`` only crosses the C ABI."""
+    (replays, CUDA-graph capture): ``launch()`` only crosses the C ABI.  The record owns its
+    tile-ticket counters (``sched_scratch``), so a captured launch shares them with nobody.
+    ``static_tables``: the caller promises that the neighbour tables (for the weight gradient:
+    the reduced masks) keep their contents while the call is in use; the weight gradient then
+    plans its schedule on the first launch only (``reuse_plan``)."""
 
-    def __init__(self, kind: str, args, device: int, stream: int, keep):
+    def __init__(self, kind: str, args, device: int, stream: int, keep, static_tables: bool = False):
+        import torch
         self._kind = kind
         self._args = args
         self._device = device
         self._stream = int(stream)
         self._keep = keep  # tensors whose memory the record points at
+        self._tickets = torch.zeros(4, dtype=torch.int32, device=f"cuda:{device}")
+        args.sched_scratch = self._tickets.data_ptr()
+        self._plan_once = bool(static_tables) and bool(args.workspace)
         L = _lib.load()
         self._fn = L.cb2_conv_run if kind == "conv" else L.cb2_gemm_run
 
@@ -757,42 +775,39 @@ class PreparedCall:
         rc = self._fn(ctypes.byref(self._args), ctypes.c_void_p(s))
         if rc:
             _lib.raise_for(rc)
+        if self._plan_once:
+            self._args.reuse_plan = 1
 
 
-def prepare_conv(params: ConvParams) -> PreparedCall:
+def _attach_workspace(L, args, params, keep, size_fn) -> None:
+    need = size_fn(ctypes.byref(args))
+    if need:
+        t = as_view(params.workspace)
+        if t is None or t.nbytes() < need:
+            import torch
+            ws = torch.empty(need, dtype=torch.uint8, device=f"cuda:{args._device}")
+            keep.append(ws)
+            args.workspace, args.workspace_bytes = ws.data_ptr(), need
+        else:
+            keep.append(params.workspace)
+            args.workspace, args.workspace_bytes = t.data_ptr(), t.nbytes()
+
+
+def prepare_conv(params: ConvParams, static_tables: bool = False) -> PreparedCall:
     """Validate ``params`` like :func:`run_conv` and return a replayable call.  The tensors
-    in ``params`` must stay alive and in place while the call is in use."""
+    in ``params`` must stay alive and in place while the call is in use.  Every prepared call
+    has a workspace of its own (two prepared weight gradients may overlap on the GPU)."""
     L = _lib.load()
     args = _conv_args(params)
-    need = L.cb2_conv_workspace_size(ctypes.byref(args))
     keep = [params.input, params.weight, params.output, params.indices, params.mask, params.mask_argsort,
             params.mask_output, params.bias, params.scale, params.output_add]
-    if need:
-        t = as_view(params.workspace)
-        if t is None or t.nbytes() < need:
-            import torch
-            ws = torch.empty(need, dtype=torch.uint8, device=f"cuda:{args._device}")
-            keep.append(ws)
-            args.workspace, args.workspace_bytes = ws.data_ptr(), need
-        else:
-            keep.append(params.workspace)
-            args.workspace, args.workspace_bytes = t.data_ptr(), t.nbytes()
-    return PreparedCall("conv", args, args._device, params.stream, keep)
+    _attach_workspace(L, args, params, keep, L.cb2_conv_workspace_size)
+    return PreparedCall("conv", args, args._device, params.stream, keep, static_tables)
 
 
-def prepare_gemm(params: GemmParams) -> PreparedCall:
+def prepare_gemm(params: GemmParams, static_tables: bool = False) -> PreparedCall:
     L = _lib.load()
     args = _gemm_args(params)
-    need = L.cb2_gemm_workspace_size(ctypes.byref(args))
     keep = [params.a, params.b, params.c, params.d, params.a_inds, params.b_inds, params.c_inds]
-    if need:
-        t = as_view(params.workspace)
-        if t is None or t.nbytes() < need:
-            import torch
-            ws = torch.empty(need, dtype=torch.uint8, device=f"cuda:{args._device}")
-            keep.append(ws)
-            args.workspace, args.workspace_bytes = ws.data_ptr(), need
-        else:
-            keep.append(params.workspace)
-            args.workspace, args.workspace_bytes = t.data_ptr(), t.nbytes()
-    return PreparedCall("gemm", args, args._device, params.stream, keep)
+    _attach_workspace(L, args, params, keep, L.cb2_gemm_workspace_size)
+    return PreparedCall("gemm", args, args._device, params.stream, keep, static_tables)

@@ -87,6 +87,22 @@ typedef struct cb2_gemm_args {
    * 128) and the reduction elements per pipeline stage (fp16: 64 or 128); 0 = chosen from the problem.
    * This is what a tuner varies.  ShuffleAB uses tile_n only. */
   int tile_n, tile_k;
+  /* Scheduling extensions (no counterpart in the reference; all may be left zero).
+   * sched_scratch: 16 bytes of device memory, zero-filled once, owned by THIS argument record: the
+   *   tile-ticket counters of the launch (the kernel returns them to zero).  Without it the launch
+   *   takes a pair from a per-device pool in round-robin order, which is safe for eager launches
+   *   but lets a captured launch (whose pair is fixed at capture) collide with a later eager one
+   *   running at the same time on another stream.  Give every captured or replayed call its own.
+   * max_ctas: upper bound on the CTAs of the launch (0 = one per SM).  The kernels are persistent
+   *   and sized to one CTA per SM; calls that are meant to run side by side on different streams
+   *   (forward, backward input and backward weight of one layer) each take a share.
+   * reuse_plan (ShuffleAB only): the workspace still holds the plan of an earlier, stream-ordered
+   *   call on the same workspace with the same reduced masks (contents, not just address), row count,
+   *   mask_width, mask_filter, tile_n and max_ctas -- skip the planning kernel.  The plan depends on
+   *   the neighbour tables only, so a training loop plans once per scene. */
+  void *sched_scratch;
+  int max_ctas;
+  int reuse_plan;
 } cb2_gemm_args;
 
 /*
@@ -138,6 +154,22 @@ typedef struct cb2_conv_args {
   /* ConvAlgoDesp::tile_shape[1] and [2], as in cb2_gemm_args; backward weight uses tile_n only.  Int8
    * kernels exist for tile_k = 128. */
   int tile_n, tile_k;
+  /* Scheduling extensions (no counterpart in the reference; all may be left zero).
+   * sched_scratch: 16 bytes of device memory, zero-filled once, owned by THIS argument record: the
+   *   tile-ticket counters of the launch (the kernel returns them to zero).  Without it the launch
+   *   takes a pair from a per-device pool in round-robin order, which is safe for eager launches
+   *   but lets a captured launch (whose pair is fixed at capture) collide with a later eager one
+   *   running at the same time on another stream.  Give every captured or replayed call its own.
+   * max_ctas: upper bound on the CTAs of the launch (0 = one per SM).  The kernels are persistent
+   *   and sized to one CTA per SM; calls that are meant to run side by side on different streams
+   *   (forward, backward input and backward weight of one layer) each take a share.
+   * reuse_plan (backward weight only): the workspace still holds the plan of an earlier, stream-ordered
+   *   call on the same workspace with the same reduced masks (contents, not just address), row count,
+   *   mask_width, mask_filter, tile_n and max_ctas -- skip the planning kernel.  The plan depends on
+   *   the neighbour tables only, so a training loop plans once per scene. */
+  void *sched_scratch;
+  int max_ctas;
+  int reuse_plan;
 } cb2_conv_args;
 
 /* Launches.  `stream` is a cudaStream_t (the reference passes it as uintptr_t,
@@ -219,6 +251,9 @@ typedef struct cb2_pairgen_args {
   int32_t *mask_argsort_bwd;/* [n_in] or null */
   void *workspace;          /* at least cb2_pairgen_workspace_size() bytes, 256-byte aligned */
   size_t workspace_bytes;
+  uint32_t *tile_masks;     /* [ceil(n_out / 128)] or null: OR of the masks of each 128 sorted rows, i.e. what a
+                               forward call with mask_filter = all ones writes to mask_out_ptr and backward
+                               weight reads as mask_ptr with mask_width = 128 */
 } cb2_pairgen_args;
 
 size_t cb2_pairgen_workspace_size(const cb2_pairgen_args *args);

@@ -26,6 +26,7 @@ import numpy as np
 _HERE = Path(__file__).resolve().parent
 _LIB = None
 _REF = None
+_REF_DEV = None
 
 c_i32p = ctypes.POINTER(ctypes.c_int32)
 c_u32p = ctypes.POINTER(ctypes.c_uint32)
@@ -284,6 +285,36 @@ def requant_s8(acc, scale, bias, beta=0.0, src=None, act_type=0, act_alpha=0.0):
                          _p(src, c_i8p), ctypes.c_int(act_type), ctypes.c_float(act_alpha),
                          _p(out, c_i8p))
     return out
+
+
+def lincomb_f16(acc, alpha=1.0, beta=0.0, src=None, act_type=0, act_alpha=0.0):
+    """fp16 output operator on an fp32 accumulator array (any shape); ``src`` fp16 or None."""
+    acc = np.ascontiguousarray(acc, np.float32)
+    out = np.empty(acc.shape, np.float16)
+    sb = None if src is None else _u16(np.ascontiguousarray(src, np.float16))
+    lib().orc_lincomb_f16(ctypes.c_longlong(acc.size), _p(acc, c_f32p), ctypes.c_float(alpha), ctypes.c_float(beta),
+                          _p(sb, c_u16p), ctypes.c_int(act_type), ctypes.c_float(act_alpha),
+                          _p(out.view(np.uint16), c_u16p))
+    return out
+
+
+def ref_device_lib():
+    """The reference's own epilogue functors compiled as device code (``oracle/ref_device_shim.cu``);
+    None when it was not built in this checkout.  Calling into it needs a GPU."""
+    global _REF_DEV
+    if _REF_DEV is None:
+        path = _HERE / "_ref" / "libref_device.so"
+        if not path.exists():
+            return None
+        R = ctypes.CDLL(str(path))
+        R.ref_dev_requant_s8.restype = ctypes.c_int
+        R.ref_dev_requant_s8.argtypes = [ctypes.c_longlong, ctypes.c_int, c_i32p, c_f32p, c_f32p, ctypes.c_float,
+                                         c_i8p, ctypes.c_int, c_i8p]
+        R.ref_dev_lincomb_f16.restype = ctypes.c_int
+        R.ref_dev_lincomb_f16.argtypes = [ctypes.c_longlong, c_f32p, ctypes.c_float, ctypes.c_float, c_u16p,
+                                          ctypes.c_int, c_u16p]
+        _REF_DEV = R
+    return _REF_DEV
 
 
 # --------------------------------------------------------------------------------------

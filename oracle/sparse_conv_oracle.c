@@ -477,6 +477,20 @@ void orc_requant_s8(int rows, int K_out, const int32_t *acc, const float *scale,
     }
 }
 
+/* The fp16 output operator on a caller-provided fp32 accumulator array (used to check the
+ * epilogue separately from the contraction): LinearCombination,
+ * cumm/gemm/output_op/linear.py:105-144.  src / out are raw fp16 bit patterns; src may be
+ * NULL (no beta term). */
+void orc_lincomb_f16(long long n, const float *acc, float alpha, float beta, const uint16_t *src,
+                     int act_type, float act_alpha, uint16_t *out) {
+  for (long long i = 0; i < n; ++i) {
+    int has_src = src != NULL && beta != 0.f;
+    float sv = has_src ? orc_half_to_float(src[i]) : 0.f;
+    float t = orc_act(orc_lincomb(acc[i], alpha, beta, has_src, sv), act_type, act_alpha);
+    out[i] = orc_float_to_half(t);
+  }
+}
+
 /* ------------------------------------------------------------------------------------
  * Pair / mask generation (convention documented here; the reference does not contain
  * this step).

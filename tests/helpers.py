@@ -195,3 +195,20 @@ def assert_close_f16(got, want, what=""):
     bad = err > tol
     assert not bad.any(), (f"{what}: {int(bad.sum())} of {bad.size} elements outside rtol={RTOL} atol={ATOL}; "
                            f"max abs err {float(err.max()):.4g} at {np.unravel_index(err.argmax(), err.shape)}")
+
+
+def assert_close_wgrad(got, want, indices, what="", kv_axis=1):
+    """Weight gradient [K, kv, C] against the oracle, one filter offset at a time.  Both sides
+    accumulate in fp32 and round once, so every offset is held to the plain rtol / atol; the
+    absolute part grows with the square root of the offset's pair count only beyond 4096 pairs
+    (the centre offset of a large scene sums 10^5 products and its entries are of order 10^2)."""
+    got = np.moveaxis(got.astype(np.float32), kv_axis, 0)
+    want = np.moveaxis(want.astype(np.float32), kv_axis, 0)
+    pairs = (np.asarray(indices) >= 0).sum(axis=1)
+    assert got.shape == want.shape and got.shape[0] == len(pairs)
+    for f in range(got.shape[0]):
+        atol = ATOL * max(1.0, float(np.sqrt(pairs[f])) / 64.0)
+        err = np.abs(got[f] - want[f])
+        bad = err > atol + RTOL * np.abs(want[f])
+        assert not bad.any(), (f"{what}: filter offset {f} ({int(pairs[f])} pairs): {int(bad.sum())} of {bad.size} "
+                               f"entries outside rtol={RTOL} atol={atol:.3g}; max abs err {float(err.max()):.4g}")

@@ -34,6 +34,9 @@ def compare(torch, t, oc, ref, subm):
     assert (h(t.indices_bwd) == ref.indices_bwd).all(), "backward indices differ"
     assert (h(t.mask_bwd).view(np.uint32) == ref.mask_bwd).all(), "backward masks differ"
     assert (h(t.mask_argsort_bwd) == ref.mask_argsort_bwd).all(), "backward mask_argsort differs"
+    tiles = (ref.n_out + 127) // 128
+    want_mo = np.array([np.bitwise_or.reduce(ref.mask[i * 128:(i + 1) * 128]) for i in range(tiles)], np.uint32)
+    assert (h(t.mask_output).view(np.uint32) == want_mo).all(), "per-tile masks differ"
 
 
 @pytest.mark.parametrize("n", [1, 37, 3000])

@@ -59,8 +59,17 @@ def test_static_scratch_weight_gradient_matches_regular_entry_point(cuda_lib):
         st = ctypes.c_int(-1)
         assert L.cb2_static_status(ctypes.byref(st)) == 0 and st.value == 0
         got = dw.cpu().numpy()
-        s = float(np.sqrt(n))
-        H.assert_close_f16(got / s, want.astype(np.float32) / s, f"static-scratch wgrad n={n} C={C} K={K}")
+        H.assert_close_wgrad(got, want, tb.indices, f"static-scratch wgrad n={n} C={C} K={K}")
+        # allocates nothing: a repeat of the call (the first one on a device resolves the scratch
+        # address) leaves the device's free memory and torch's allocator where they were
+        torch.cuda.synchronize()
+        free0, alloc0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
+        rc = L.cb2_conv_backward_weight_static(ctypes.byref(args), ctypes.c_void_p(0))
+        assert rc == 0, _lib.last_error()
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free0 and torch.cuda.memory_allocated() == alloc0
+        assert L.cb2_static_status(ctypes.byref(st)) == 0 and st.value == 0
+        H.assert_close_wgrad(dw.cpu().numpy(), want, tb.indices, "static-scratch wgrad, repeated call")
     H.check_status()
 
 
