@@ -320,8 +320,9 @@ struct WgradLayout {
 };
 
 // Workspace of the weight gradient: 512-byte header (tile counts per offset), the arrival
-// counters [kv][gy], the fp32 sums [kv][gy][128 x block_n], and per offset the list of the row
-// tiles that carry it.  G = CTAs per (m, n) tile of the launch.
+// counters and the fp32 sums ([kv][gy] tiles of 128 x block_n, then the replica tiles of the
+// offsets with many units), and per offset the list of the row tiles that carry it.
+// G = CTAs per (m, n) tile of the launch.
 void wgrad_layout(int num_sms, int max_ctas, int m_total, int n_total, long long n_rows, int kv, int tile_n,
                   WgradLayout *L) {
   L->block_n = (tile_n == 64 || tile_n == 128) ? tile_n : (n_total <= 64 ? 64 : 128);
@@ -332,8 +333,10 @@ void wgrad_layout(int num_sms, int max_ctas, int m_total, int n_total, long long
   if (L->G < 1)
     L->G = 1;
   const int kvs = kv > 0 ? kv : 1;
-  L->n_arrivals = kvs * L->gy;
-  L->acc_float4 = (long long)kvs * L->gy * 32 * L->block_n;
+  // per offset one counter and one [128 x block_n] sum, plus the replicas of the heavy offsets
+  const int tiles = kvs * L->gy + kWgradMaxHeavy * L->gy * kWgradMaxReplicas;
+  L->n_arrivals = tiles;
+  L->acc_float4 = (long long)tiles * 32 * L->block_n;
   L->off_arrivals = 512;
   L->off_acc = L->off_arrivals + ((size_t)L->n_arrivals * 4 + 255) / 256 * 256;
   L->off_lists = L->off_acc + (size_t)L->acc_float4 * 16;
@@ -719,11 +722,24 @@ int cb2_pairgen_run(const cb2_pairgen_args *a, void *stream_v) {
 }
 
 // ---------------------------------------------------------------- sum over GPUs through peer memory
+struct PeerLayout {
+  long long shard_f4, shard_bytes, result_bytes;
+  size_t total;
+};
+static void peer_layout(long long numel, int world, PeerLayout *L) {
+  const long long n4 = numel / 4;
+  L->shard_f4 = (n4 + world - 1) / world;
+  L->shard_bytes = static_cast<long long>(align256(static_cast<size_t>(L->shard_f4) * 16));
+  L->result_bytes = static_cast<long long>(align256(static_cast<size_t>(numel) * 4));
+  L->total = cb2::kPeerControlBytes + 2 * static_cast<size_t>(world) * L->shard_bytes + 2 * static_cast<size_t>(L->result_bytes);
+}
+
 size_t cb2_peer_allreduce_buffer_size(long long numel, int world) {
-  if (numel <= 0 || world < 1 || world > cb2::kPeerMaxWorld)
+  if (numel <= 0 || numel % 4 || world < 1 || world > cb2::kPeerMaxWorld)
     return 0;
-  const size_t slot = align256(static_cast<size_t>(numel) * 4);
-  return cb2::kPeerControlBytes + 2 * static_cast<size_t>(world) * slot;
+  PeerLayout L;
+  peer_layout(numel, world, &L);
+  return L.total;
 }
 
 int cb2_peer_allreduce(const cb2_peer_allreduce_args *a, void *stream_v) {
@@ -746,24 +762,29 @@ int cb2_peer_allreduce(const cb2_peer_allreduce_args *a, void *stream_v) {
                  "peer buffer %d is null or not 256-byte aligned", r);
     p.peer[r] = reinterpret_cast<unsigned char *>(a->peer_buffers[r]);
   }
+  PeerLayout L;
+  peer_layout(a->numel, a->world, &L);
   p.src = a->src;
   p.out32 = a->out_f32;
   p.out16 = reinterpret_cast<__half *>(a->out_f16);
   p.numel = a->numel;
-  p.slot_bytes = static_cast<long long>(align256(static_cast<size_t>(a->numel) * 4));
+  p.shard_f4 = L.shard_f4;
+  p.shard_bytes = L.shard_bytes;
+  p.result_bytes = L.result_bytes;
   p.rank = a->rank;
   p.world = a->world;
   p.timeout_ns = a->timeout_ns ? a->timeout_ns : 1000000000ull;
   p.status = dev->status;
-  // every CTA waits for flags that the grid's own last CTA stores: keep the grid resident at once
+  // every CTA waits for flags that the grid's own last CTA stores: the whole grid must be resident
+  // at once, beside whatever else runs (small CTAs: 128 threads, no dynamic shared memory)
   static const int max_grid = [] {
     const char *v = getenv("CUMM_B200_PEER_GRID");
-    const int g = v ? atoi(v) : 32;
-    return g >= 1 ? g : 32;
+    const int g = v ? atoi(v) : 96;
+    return g >= 1 ? g : 96;
   }();
-  int grid = static_cast<int>(std::min<long long>((a->numel / 4 + 511) / 512, max_grid));
-  grid = std::max(1, std::min(grid, dev->num_sms / 2));
-  cb2::peer_reduce_kernel<<<grid, 512, 0, stream>>>(p);
+  int grid = static_cast<int>(std::min<long long>((a->numel / 4 + cb2::kPeerThreads - 1) / cb2::kPeerThreads, max_grid));
+  grid = std::max(1, std::min(grid, dev->num_sms));
+  cb2::peer_reduce_kernel<<<grid, cb2::kPeerThreads, 0, stream>>>(p);
   CB2_CUDA(cudaGetLastError());
   g_launches.fetch_add(1);
   return CB2_OK;

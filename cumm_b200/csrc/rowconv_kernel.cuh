@@ -603,6 +603,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
           const uint32_t trow = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
                                 static_cast<uint32_t>(buf * BLOCK_N);
           const bool use_src = (p.src_mode != kSrcNone) && (p.beta != 0.f);
+          const bool small_acc = KIND == 1 && __popc(kmask_store) * kpasses * Cfg::KRED <= 255;
           // fast path: out = cvt(acc); everything else goes through the general epilogue
           const bool plain = !use_src && p.act_type == 0 && p.alpha == 1.f;
           constexpr int ROUNDS = COLS_PER_HALF / 32;
@@ -688,9 +689,20 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
               uint32_t packed[8];
               float t[32];
               {
+                // int32 -> float.  The conversion instruction runs on the slow conversion unit, which the
+                // float -> int8 step also needs.  When the tile's accumulators are known to stay below
+                // 2^22 in magnitude (one filter offset and at most 255 products of |a|, |b| <= 128 per
+                // element) the same value comes out of an integer add and a float subtract, exactly:
+                // 0x4B400000 + n is the float 1.5 * 2^23 + n.
+                if (small_acc) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                  t[i] = __int2float_rn(static_cast<int>(v[i]));
+                  for (int i = 0; i < 32; ++i)
+                    t[i] = __fadd_rn(__int_as_float(static_cast<int>(v[i]) + 0x4B400000), -12582912.0f);
+                } else {
+#pragma unroll
+                  for (int i = 0; i < 32; ++i)
+                    t[i] = __int2float_rn(static_cast<int>(v[i]));
+                }
                 const float4 *sc4 = reinterpret_cast<const float4 *>(s_scale + col0);
                 const float4 *bi4 = reinterpret_cast<const float4 *>(s_bias + col0);
 #pragma unroll

@@ -9,9 +9,12 @@
 // row tiles); a unit accumulates in TMEM and adds its fp32 result [128 x BLOCK_N] into the
 // offset's accumulator in the workspace (vector reductions that complete in L2), then counts
 // itself in; the CTA whose unit completes an offset applies alpha/beta, converts, writes dW and
-// puts the accumulator and the counter back to zero.  One launch, and nobody waits for anybody
-// (the reference serialises split-K slices through a spinning semaphore,
-// cumm/conv/kernel.py:960-1083).
+// puts the accumulator and the counter back to zero.  Additions to one address are performed one
+// after the other in L2, so an offset that has many units (the centre of a submanifold
+// convolution has one per CTA) spreads them over several replica accumulators, and the unit that
+// completes a replica adds it into the offset's accumulator: two short queues per address instead
+// of one long one.  One launch, and nobody waits for anybody (the reference serialises split-K
+// slices through a spinning semaphore, cumm/conv/kernel.py:960-1083).
 //
 // Semantics follow cumm/gemm/blockmma/mma.py:608-648,722-740 (a row takes part for
 // offset f iff the reduced-mask word covering it has bit f), cumm/conv/sparse_iters.py
@@ -36,8 +39,10 @@ struct WgradParams {
   const int32_t *argsort;  // [n_rows]
   const int32_t *a_inds;   // pair-list mode
   const int32_t *b_inds;   //   "
-  float *acc;              // workspace: [f][m_tile][n_tile][128 x BLOCK_N] fp32 sums, zero between calls
-  int *arrivals;           // workspace: [f][m_tile][n_tile] units that have added their share, zero between calls
+  float *acc;              // workspace: [f][m_tile][n_tile][128 x BLOCK_N] fp32 sums, then the replica sums
+                           // [heavy offset h][m_tile][n_tile][replica][128 x BLOCK_N]; all zero between calls
+  int *arrivals;           // workspace: [f][m_tile][n_tile] arrivals at an offset's sums, then
+                           // [h][m_tile][n_tile][replica] arrivals at a replica; all zero between calls
   int *sched;              // workspace header: [0,32) number of row tiles carrying offset f
   const int *lists;        // workspace: per offset, the ordered list of those tiles
   int list_stride;         // ints between two offsets' lists
@@ -206,9 +211,23 @@ __global__ void __launch_bounds__(1024) wgrad_plan_kernel(const WgradParams p, i
 // Per CTA, in shared memory: s_plan[0] = number of units of this CTA, then five ints per unit
 // {f, first list index, one past the last, unit number, offset of its tiles in s_tiles};
 // s_tiles = the CTA's tiles in step order (when they fit; otherwise the walk reads the lists).
-// After the unit records: s_plan[kWgradPlanUnits + f] = units of offset f over all CTAs.
+// The unit number counts from the offset's first unit.  After the unit records:
+// s_plan[kWgradPlanUnits + f] = units of offset f over all CTAs, s_plan[kWgradPlanHeavy + f] = the
+// offset's place among the "heavy" offsets (those with more than kWgradDirectUnits units, which
+// get replica accumulators; the first kWgradMaxHeavy of them), or -1.
 constexpr int kWgradPlanUnits = 8 + 5 * 32;
-constexpr int kWgradPlanInts = kWgradPlanUnits + 32;
+constexpr int kWgradPlanHeavy = kWgradPlanUnits + 32;
+constexpr int kWgradPlanInts = kWgradPlanHeavy + 32;
+constexpr int kWgradDirectUnits = 8;   // up to this many units add straight into the offset's sums
+constexpr int kWgradMaxHeavy = 4;      // offsets that can have replica sums
+constexpr int kWgradMaxReplicas = 16;  // replica sums per heavy offset
+// Replicas an offset with S units uses: about the square root of S, so that both queues are short.
+__host__ __device__ __forceinline__ int wgrad_replicas(int S) {
+  int r = 1;
+  while (r * r < S && r < kWgradMaxReplicas)
+    ++r;
+  return r;
+}
 template <int TILE_CAP>
 __device__ __forceinline__ void wgrad_load_plan(const WgradParams &p, const int *lists, int list_stride, int *s_plan,
                                                 int *s_tiles) {
@@ -219,6 +238,11 @@ __device__ __forceinline__ void wgrad_load_plan(const WgradParams &p, const int 
     int P, T, c_first, S, U;
     wgrad_plan_warp(cnt, G, P, T, c_first, S, U);
     s_plan[kWgradPlanUnits + f] = S;
+    {
+      const uint32_t heavy = __ballot_sync(0xffffffffu, S > kWgradDirectUnits);
+      const int h = __popc(heavy & ((1u << f) - 1u));
+      s_plan[kWgradPlanHeavy + f] = (S > kWgradDirectUnits && h < kWgradMaxHeavy) ? h : -1;
+    }
     const int b0 = (int)(((long long)c * T) / G), b1 = (int)(((long long)(c + 1) * T) / G);
     const bool has = cnt > 0 && c >= c_first && c < c_first + S;
     int k0 = 0, k1 = 0;
@@ -242,7 +266,7 @@ __device__ __forceinline__ void wgrad_load_plan(const WgradParams &p, const int 
       e[0] = f;
       e[1] = k0;
       e[2] = k1;
-      e[3] = U + (c - c_first);
+      e[3] = c - c_first;
       e[4] = len_incl - (k1 - k0);
     }
     if (f == 0) {
@@ -363,6 +387,10 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
     // sums layout: float4 (col/4, row) at index (col/4) * 128 + row, so that the 32 rows of a
     // warp touch 512 contiguous bytes
     auto sums_of = [&](int f) { return reinterpret_cast<float4 *>(p.acc) + ((long long)f * gy + blockIdx.y) * tile_f4; };
+    auto replica_sums = [&](int h, int rep) {
+      return reinterpret_cast<float4 *>(p.acc) +
+             ((long long)p.kv * gy + ((long long)h * gy + blockIdx.y) * kWgradMaxReplicas + rep) * tile_f4;
+    };
     // dW[m0 + row, f, n0 + 4 * q .. + 3] from four sums
     auto write_out = [&](int f, int row, int q, float4 v) {
       const int m = m0 + row, n = n0 + 4 * q;
@@ -400,7 +428,13 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
         p.lists, p.list_stride, s_plan, s_tiles, [&](int, int) -> bool { return true; },
         [&](int, int, bool) -> bool { return true; },
         [&](int u, int f, int active) -> bool {
-          float4 *sums = sums_of(f) + et;
+          // where this unit adds its result: the offset's sums, or one of its replicas
+          const int S = s_units[f];
+          const int h = s_plan[kWgradPlanHeavy + f];
+          const int R = h >= 0 ? wgrad_replicas(S) : 1;
+          const int rep = h >= 0 ? u % R : 0;
+          float4 *final_sums = sums_of(f) + et;
+          float4 *sums = h >= 0 ? replica_sums(h, rep) + et : final_sums;
           if (active > 0) {
             const int buf = acc_use & 1;
             if (et == 0) {
@@ -432,24 +466,46 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
             ++acc_use;
             __threadfence();  // this thread's additions are performed before the unit is counted in
           }
-          // a unit without tiles (fewer steps than CTAs) is still counted: the offset is complete
-          // when all of its units have arrived
-          named_bar_sync(1, 128);
-          if (et == 0) {
-            int *counter = p.arrivals + (long long)f * gy + blockIdx.y;
-            const int before = atomicAdd(counter, 1);
-            misc[6] = (before == s_units[f] - 1) ? 1 : 0;
-            if (before == s_units[f] - 1) {
-              *counter = 0;       // ready for the next call on this workspace
-              __threadfence();    // order the reads below after everybody's additions
+          // A unit without tiles (fewer steps than CTAs) is still counted in.  `arrive` counts this
+          // CTA in at `counter` and tells all 128 threads whether it was the last of `expected`;
+          // the last one finds everybody's additions performed and leaves the counter at zero.
+          auto arrive = [&](int *counter, int expected) -> bool {
+            named_bar_sync(1, 128);
+            if (et == 0) {
+              const int before = atomicAdd(counter, 1);
+              misc[6] = (before == expected - 1) ? 1 : 0;
+              if (before == expected - 1) {
+                *counter = 0;
+                __threadfence();
+              }
             }
+            named_bar_sync(1, 128);
+            return misc[6] != 0;
+          };
+          bool complete;
+          if (h >= 0) {
+            // units rep, rep + R, rep + 2R ... of the offset share this replica
+            int *rep_counter = p.arrivals + (long long)p.kv * gy + ((long long)h * gy + blockIdx.y) * kWgradMaxReplicas + rep;
+            complete = false;
+            if (arrive(rep_counter, (S - rep + R - 1) / R)) {
+              // the replica is complete: move it into the offset's sums and leave it zero
+#pragma unroll 4
+              for (int q = 0; q < BLOCK_N / 4; ++q) {
+                const float4 v = __ldcg(sums + q * 128);
+                __stcg(sums + q * 128, make_float4(0.f, 0.f, 0.f, 0.f));
+                red_add_f32x4(final_sums + q * 128, v.x, v.y, v.z, v.w);
+              }
+              __threadfence();
+              complete = arrive(p.arrivals + (long long)f * gy + blockIdx.y, R);
+            }
+          } else {
+            complete = arrive(p.arrivals + (long long)f * gy + blockIdx.y, S);
           }
-          named_bar_sync(1, 128);
-          if (misc[6]) {
+          if (complete) {
 #pragma unroll 4
             for (int q = 0; q < BLOCK_N / 4; ++q) {
-              const float4 v = __ldcg(sums + q * 128);
-              __stcg(sums + q * 128, make_float4(0.f, 0.f, 0.f, 0.f));
+              const float4 v = __ldcg(final_sums + q * 128);
+              __stcg(final_sums + q * 128, make_float4(0.f, 0.f, 0.f, 0.f));
               write_out(f, et, q, v);
             }
           }

@@ -1,5 +1,6 @@
 """Sum of one fp32 tensor per GPU through NVLink peer memory (``cb2_peer_allreduce``): the one
-exchange step of the row-sharded convolution, the weight-gradient partial sums.
+exchange step of the row-sharded convolution, the weight-gradient partial sums (reduce-scatter
+then all-gather by plain peer stores, every element summed once in GPU order).
 
 One process per GPU.  The buffers come from ``torch.distributed._symmetric_memory`` (plumbing:
 it allocates memory every GPU of the node can map and exchanges the handles); the data
@@ -64,9 +65,11 @@ class PeerAllReduce:
 
     def last_call_ns(self):
         """Global-timer readings of the last call on this rank, relative to its start: when its
-        pushes were done, when every rank's flag had been seen, when it finished (synchronises)."""
+        shards had been sent, when every rank's shard had arrived, when its own shard was summed
+        and sent out, when every rank's sums had arrived, when it finished (synchronises)."""
         import torch
         buf = self._keep[0] if isinstance(self._keep, tuple) else self._keep
         torch.cuda.synchronize(buf.device)
-        st = buf[2560:2560 + 32].view(torch.int64).cpu().tolist()
-        return {"pushed": st[1] - st[0], "flags_seen": st[2] - st[0], "done": st[3] - st[0]}
+        st = buf[2560:2560 + 48].view(torch.int64).cpu().tolist()
+        return {"scattered": st[1] - st[0], "shards_seen": st[2] - st[0], "reduced": st[3] - st[0],
+                "results_seen": st[4] - st[0], "done": st[5] - st[0]}

@@ -270,9 +270,12 @@ int cb2_pairgen_run(const cb2_pairgen_args *args, void *stream);
  * `peer_buffers`: a HOST array of `world` device pointers, the buffer of every GPU as mapped
  * in the calling process (peer_buffers[rank] is the caller's own), each of
  * cb2_peer_allreduce_buffer_size() bytes, zero-filled once before the first call.  The kernel
- * writes its array into every buffer with plain stores and waits, for at most `timeout_ns`
- * (0 = one second), for the other GPUs' arrays to arrive; a wait that runs out sets status
- * word 1 (cb2_device_status) and leaves the outputs untouched.
+ * sends shard s of its array to GPU s (plain stores over NVLink), sums the shards it receives
+ * in GPU order and sends the sums to every GPU; each of the two waits lasts at most
+ * `timeout_ns` (0 = one second), and a wait that runs out sets status word 1
+ * (cb2_device_status) and leaves the outputs untouched.  The kernel's CTAs all have to be
+ * resident at the same time; they are small (128 threads) so that they fit beside other
+ * kernels, and at most one per SM is launched.
  */
 typedef struct cb2_peer_allreduce_args {
   void *const *peer_buffers;
