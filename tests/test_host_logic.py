@@ -229,8 +229,12 @@ def test_peer_allreduce_buffer_size_is_a_host_function():
     L.cb2_peer_allreduce_buffer_size.restype = ctypes.c_size_t
     L.cb2_peer_allreduce_buffer_size.argtypes = [ctypes.c_longlong, ctypes.c_int]
     numel = 128 * 27 * 128
+    # control block, then per call parity: one receive slot per GPU of one shard each, and one result array
     one = L.cb2_peer_allreduce_buffer_size(numel, 1)
-    assert one == 4096 + 2 * numel * 4
-    assert L.cb2_peer_allreduce_buffer_size(numel, 8) == 4096 + 2 * 8 * numel * 4
+    assert one == 8192 + 2 * numel * 4 + 2 * numel * 4
+    shard = numel * 4 // 8
+    assert shard % 256 == 0
+    assert L.cb2_peer_allreduce_buffer_size(numel, 8) == 8192 + 2 * 8 * shard + 2 * numel * 4
+    assert L.cb2_peer_allreduce_buffer_size(numel + 2, 8) == 0  # not a multiple of 4
     assert L.cb2_peer_allreduce_buffer_size(numel, 17) == 0
     assert L.cb2_peer_allreduce_buffer_size(0, 2) == 0
