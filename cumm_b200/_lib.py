@@ -34,6 +34,8 @@ EXPORTED_SYMBOLS = (
     "cb2_pairgen_run",
     "cb2_peer_allreduce_buffer_size",
     "cb2_peer_allreduce",
+    "cb2_enumerate_gemm_desps",
+    "cb2_enumerate_conv_desps",
 )
 
 
@@ -120,6 +122,22 @@ class PairgenArgs(ctypes.Structure):
     ]
 
 
+class KernelDesp(ctypes.Structure):
+    """``cb2_kernel_desp``."""
+    _fields_ = [
+        ("op_type", ctypes.c_int), ("shuffle_type", ctypes.c_int),
+        ("dtype_a", ctypes.c_int), ("dtype_b", ctypes.c_int), ("dtype_c", ctypes.c_int),
+        ("dacc", ctypes.c_int), ("dcomp", ctypes.c_int),
+        ("trans_a", ctypes.c_int), ("trans_b", ctypes.c_int), ("trans_c", ctypes.c_int),
+        ("tile_shape", ctypes.c_int * 3), ("warp_tile_shape", ctypes.c_int * 3), ("tensorop", ctypes.c_int * 3),
+        ("num_stage", ctypes.c_int),
+        ("element_per_access", ctypes.c_int),
+        ("split_k_serial", ctypes.c_int),
+        ("mask_sparse", ctypes.c_int), ("increment_k_first", ctypes.c_int), ("is_int8_inference", ctypes.c_int),
+        ("min_arch_major", ctypes.c_int), ("min_arch_minor", ctypes.c_int),
+    ]
+
+
 class PeerAllreduceArgs(ctypes.Structure):
     """``cb2_peer_allreduce_args``."""
     _fields_ = [
@@ -174,6 +192,9 @@ def load() -> ctypes.CDLL:
     L.cb2_peer_allreduce_buffer_size.argtypes = [ctypes.c_longlong, ctypes.c_int]
     L.cb2_peer_allreduce.restype = ctypes.c_int
     L.cb2_peer_allreduce.argtypes = [ctypes.POINTER(PeerAllreduceArgs), ctypes.c_void_p]
+    for fn in (L.cb2_enumerate_gemm_desps, L.cb2_enumerate_conv_desps):
+        fn.restype = ctypes.c_int
+        fn.argtypes = [ctypes.POINTER(KernelDesp), ctypes.c_int]
     _lib = L
     return L
 
@@ -198,6 +219,16 @@ def device_status() -> int:
     v = ctypes.c_int(0)
     raise_for(load().cb2_device_status(ctypes.byref(v)))
     return v.value
+
+
+def kernel_table(which: str):
+    """The library's kernel variants (``cb2_enumerate_gemm_desps`` / ``cb2_enumerate_conv_desps``)."""
+    L = load()
+    fn = L.cb2_enumerate_conv_desps if which == "conv" else L.cb2_enumerate_gemm_desps
+    n = fn(None, 0)
+    arr = (KernelDesp * n)()
+    fn(arr, n)
+    return list(arr)
 
 
 def launch_count() -> int:

@@ -4,40 +4,27 @@ from __future__ import annotations
 
 from typing import List, Sequence, Tuple
 
-from ..tensorview import float16, float32, int8, int32
 from ..tensorview.gemm import (ConvAlgoDesp, ConvOpType, ConvParams, implicit_gemm_mnk, run_conv)
 
 TILE_M = 128
 
-# (trans_a, trans_b, trans_c) per op, cumm/conv/params.py:61-69
-_TRANS = {ConvOpType.Forward: (False, True, False),
-          ConvOpType.BackwardInput: (False, False, False),
-          ConvOpType.BackwardWeight: (True, False, False)}
-
-
-def _desp(op: ConvOpType, tile_n: int, tile_k: int, int8_inference: bool = False) -> ConvAlgoDesp:
-    d = ConvAlgoDesp(3, op)
-    if int8_inference:
-        d.dtype_a = d.dtype_b = d.dtype_c = int8
-        d.dacc, d.dcomp = int32, float32
-        epa = 16
-    else:
-        d.dtype_a = d.dtype_b = d.dtype_c = float16
-        d.dacc = d.dcomp = float32
-        epa = 8
-    d.trans_a, d.trans_b, d.trans_c = _TRANS[op]
-    tm = TILE_M
-    d.tile_shape = [tm, tile_n, tile_k]
-    d.warp_tile_shape = [tm, tile_n, tile_k]
-    d.tensorop = [128, tile_n, 32 if int8_inference else 16]
-    d.num_stage = 3
+def _from_record(r) -> ConvAlgoDesp:
+    """A descriptor from one ``cb2_kernel_desp`` record of the library's kernel table."""
+    d = ConvAlgoDesp(3, ConvOpType(r.op_type))
+    d.dtype_a, d.dtype_b, d.dtype_c = r.dtype_a, r.dtype_b, r.dtype_c
+    d.dacc, d.dcomp = r.dacc, r.dcomp
+    d.trans_a, d.trans_b, d.trans_c = bool(r.trans_a), bool(r.trans_b), bool(r.trans_c)
+    d.tile_shape = list(r.tile_shape)
+    d.warp_tile_shape = list(r.warp_tile_shape)
+    d.tensorop = list(r.tensorop)
+    d.num_stage = r.num_stage
     d.algo = "Blackwell"
-    d.split_k_serial = op == ConvOpType.BackwardWeight
-    d.element_per_access_a = d.element_per_access_b = d.element_per_access_c = epa
-    d.mask_sparse = True
-    d.increment_k_first = True
-    d.is_int8_inference = int8_inference
-    d.min_arch = (10, 0)
+    d.split_k_serial = bool(r.split_k_serial)
+    d.element_per_access_a = d.element_per_access_b = d.element_per_access_c = r.element_per_access
+    d.mask_sparse = bool(r.mask_sparse)
+    d.increment_k_first = bool(r.increment_k_first)
+    d.is_int8_inference = bool(r.is_int8_inference)
+    d.min_arch = (r.min_arch_major, r.min_arch_minor)
     return d
 
 
@@ -46,16 +33,10 @@ class ConvMainUnitTest:
     def get_all_conv_algo_desp() -> List[ConvAlgoDesp]:
         """cumm/conv/main.py:985-1050.  The reference ships an empty conv kernel list and lets
         its caller supply tile shapes (cumm/conv/main.py:236-239); the sm_100a kernels have a
-        fixed 128-row tile and pick the channel tiling from C and K, so the table is short."""
-        out = []
-        for op in (ConvOpType.Forward, ConvOpType.BackwardInput):
-            for tn in (64, 128):
-                for tk in (64, 128):
-                    out.append(_desp(op, tn, tk))
-        for tn in (64, 128):
-            out.append(_desp(ConvOpType.BackwardWeight, tn, 128))
-            out.append(_desp(ConvOpType.Forward, tn, 128, int8_inference=True))
-        return out
+        fixed 128-row tile and pick the channel tiling from C and K, so the table is short.  It is
+        read from the library (``cb2_enumerate_conv_desps``)."""
+        from .. import _lib
+        return [_from_record(r) for r in _lib.kernel_table("conv")]
 
     @staticmethod
     def extract_mnk(op_type: int, N: int, C: int, K: int, kernel_volume: int, in_prod: int = -1,

@@ -790,6 +790,69 @@ int cb2_peer_allreduce(const cb2_peer_allreduce_args *a, void *stream_v) {
   return CB2_OK;
 }
 
+// ---------------------------------------------------------------- the kernel table
+static cb2_kernel_desp make_desp(int op_type, int shuffle, bool int8, bool ta, bool tb, int tn, int tk) {
+  cb2_kernel_desp d;
+  memset(&d, 0, sizeof(d));
+  d.op_type = op_type;
+  d.shuffle_type = shuffle;
+  d.dtype_a = d.dtype_b = d.dtype_c = int8 ? CB2_DTYPE_I8 : CB2_DTYPE_F16;
+  d.dacc = int8 ? CB2_DTYPE_I32 : CB2_DTYPE_F32;
+  d.dcomp = CB2_DTYPE_F32;
+  d.trans_a = ta;
+  d.trans_b = tb;
+  d.trans_c = 0;
+  const int shape[3] = {128, tn, tk};
+  for (int i = 0; i < 3; ++i)
+    d.tile_shape[i] = d.warp_tile_shape[i] = shape[i];
+  d.tensorop[0] = 128;
+  d.tensorop[1] = tn;
+  d.tensorop[2] = int8 ? 32 : 16;
+  d.num_stage = 3;
+  d.element_per_access = int8 ? 16 : 8;
+  d.split_k_serial = (op_type == CB2_CONV_BACKWARD_WEIGHT || shuffle == CB2_SHUFFLE_AB) ? 1 : 0;
+  d.mask_sparse = op_type >= 0 ? 1 : 0;
+  d.increment_k_first = op_type >= 0 ? 1 : 0;
+  d.is_int8_inference = int8 ? 1 : 0;
+  d.min_arch_major = 10;
+  d.min_arch_minor = 0;
+  return d;
+}
+
+static int emit(const cb2_kernel_desp &d, cb2_kernel_desp *out, int capacity, int n) {
+  if (out && n < capacity)
+    out[n] = d;
+  return n + 1;
+}
+
+// The variants launch_rowconv and run_wgrad can dispatch to (the CB2_INST list above).
+int cb2_enumerate_gemm_desps(cb2_kernel_desp *out, int capacity) {
+  int n = 0;
+  const int shuffles[2] = {CB2_SHUFFLE_NONE, CB2_SHUFFLE_AC};
+  for (int s = 0; s < 2; ++s)
+    for (int tb = 1; tb >= 0; --tb)
+      for (int tn = 64; tn <= 128; tn += 64)
+        for (int tk = 64; tk <= 128; tk += 64)
+          n = emit(make_desp(-1, shuffles[s], false, false, tb != 0, tn, tk), out, capacity, n);
+  for (int tn = 64; tn <= 128; tn += 64)
+    n = emit(make_desp(-1, CB2_SHUFFLE_AB, false, true, false, tn, 128), out, capacity, n);
+  return n;
+}
+
+int cb2_enumerate_conv_desps(cb2_kernel_desp *out, int capacity) {
+  int n = 0;
+  // (trans_a, trans_b) per op: cumm/conv/params.py:61-69
+  for (int op = CB2_CONV_FORWARD; op <= CB2_CONV_BACKWARD_INPUT; ++op)
+    for (int tn = 64; tn <= 128; tn += 64)
+      for (int tk = 64; tk <= 128; tk += 64)
+        n = emit(make_desp(op, CB2_SHUFFLE_NONE, false, false, op == CB2_CONV_FORWARD, tn, tk), out, capacity, n);
+  for (int tn = 64; tn <= 128; tn += 64) {
+    n = emit(make_desp(CB2_CONV_BACKWARD_WEIGHT, CB2_SHUFFLE_NONE, false, true, false, tn, 128), out, capacity, n);
+    n = emit(make_desp(CB2_CONV_FORWARD, CB2_SHUFFLE_NONE, true, false, true, tn, 128), out, capacity, n);
+  }
+  return n;
+}
+
 const char *cb2_last_error(void) { return g_err.c_str(); }
 
 int cb2_tile_m(void) { return 128; }

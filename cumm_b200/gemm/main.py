@@ -4,26 +4,26 @@ from __future__ import annotations
 
 from typing import Dict, List, Sequence, Tuple
 
-from ..tensorview import float16, float32
 from ..tensorview.gemm import GemmAlgoDesp, GemmParams, ShuffleStrideType, run_gemm
 
 TILE_M = 128
 
 
-def _desp(trans_b: bool, tile_n: int, tile_k: int, shuffle: ShuffleStrideType, trans_a=False) -> GemmAlgoDesp:
+def _from_record(r) -> GemmAlgoDesp:
+    """A descriptor from one ``cb2_kernel_desp`` record of the library's kernel table."""
     d = GemmAlgoDesp()
-    d.dtype_a = d.dtype_b = d.dtype_c = float16
-    d.dacc = d.dcomp = float32
-    d.trans_a, d.trans_b, d.trans_c = trans_a, trans_b, False
-    d.tile_shape = [TILE_M, tile_n, tile_k]
-    d.warp_tile_shape = [TILE_M, tile_n, tile_k]  # one tcgen05 instruction stream per CTA tile
-    d.tensorop = [128, tile_n, 16]
-    d.num_stage = 3
+    d.dtype_a, d.dtype_b, d.dtype_c = r.dtype_a, r.dtype_b, r.dtype_c
+    d.dacc, d.dcomp = r.dacc, r.dcomp
+    d.trans_a, d.trans_b, d.trans_c = bool(r.trans_a), bool(r.trans_b), bool(r.trans_c)
+    d.tile_shape = list(r.tile_shape)
+    d.warp_tile_shape = list(r.warp_tile_shape)  # one tcgen05 instruction stream per CTA tile
+    d.tensorop = list(r.tensorop)
+    d.num_stage = r.num_stage
     d.algo = "Blackwell"
-    d.shuffle_type = shuffle
-    d.split_k_serial = shuffle == ShuffleStrideType.ShuffleAB
-    d.element_per_access_a = d.element_per_access_b = d.element_per_access_c = 8
-    d.min_arch = (10, 0)
+    d.shuffle_type = ShuffleStrideType(r.shuffle_type)
+    d.split_k_serial = bool(r.split_k_serial)
+    d.element_per_access_a = d.element_per_access_b = d.element_per_access_c = r.element_per_access
+    d.min_arch = (r.min_arch_major, r.min_arch_minor)
     return d
 
 
@@ -32,17 +32,11 @@ class GemmMainUnitTest:
 
     @staticmethod
     def get_all_algo_desp() -> List[GemmAlgoDesp]:
-        """cumm/gemm/main.py:916-965.  The kernel table: row-gather GEMMs (ShuffleAC / dense)
-        with B given as [n,k] or [k,n], and the gather-gather weight-gradient GEMM (ShuffleAB)."""
-        out = []
-        for shuffle in (ShuffleStrideType.NoShuffle, ShuffleStrideType.ShuffleAC):
-            for trans_b in (True, False):
-                for tn in (64, 128):
-                    for tk in (64, 128):
-                        out.append(_desp(trans_b, tn, tk, shuffle))
-        for tn in (64, 128):
-            out.append(_desp(False, tn, 128, ShuffleStrideType.ShuffleAB, trans_a=True))
-        return out
+        """cumm/gemm/main.py:916-965.  The kernel table, read from the library
+        (``cb2_enumerate_gemm_desps``): row-gather GEMMs (ShuffleAC / dense) with B given as
+        [n,k] or [k,n], and the gather-gather weight-gradient GEMM (ShuffleAB)."""
+        from .. import _lib
+        return [_from_record(r) for r in _lib.kernel_table("gemm")]
 
     @staticmethod
     def extract_mnk(a_shape: Sequence[int], b_shape: Sequence[int], trans_a: bool, trans_b: bool,

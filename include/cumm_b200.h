@@ -290,6 +290,32 @@ typedef struct cb2_peer_allreduce_args {
 size_t cb2_peer_allreduce_buffer_size(long long numel, int world);
 int cb2_peer_allreduce(const cb2_peer_allreduce_args *args, void *stream);
 
+/*
+ * The kernel table: one record per kernel variant a descriptor can select.  Replaces
+ * GemmMainUnitTest::get_all_algo_desp (cumm/gemm/main.py:916-965) and
+ * ConvMainUnitTest::get_all_conv_algo_desp (cumm/conv/main.py:985-1050); the fields are the
+ * ones of tv::gemm::GemmAlgoDesp / ConvAlgoDesp (include/tensorview/gemm/core/params.h:24-45,
+ * 166-190) that differ between the variants.  Both calls return the number of variants and
+ * fill at most `capacity` records (out may be null to ask for the count); they need no GPU.
+ */
+typedef struct cb2_kernel_desp {
+  int op_type;      /* conv: CB2_CONV_*; gemm: -1 */
+  int shuffle_type; /* gemm: CB2_SHUFFLE_*; conv: CB2_SHUFFLE_NONE */
+  int dtype_a, dtype_b, dtype_c, dacc, dcomp;
+  int trans_a, trans_b, trans_c;
+  int tile_shape[3];      /* rows, columns, reduction of one CTA tile */
+  int warp_tile_shape[3]; /* = tile_shape: one tcgen05.mma covers the CTA tile */
+  int tensorop[3];        /* shape of one tcgen05.mma instruction */
+  int num_stage;
+  int element_per_access; /* a, b and c alike: 16 bytes */
+  int split_k_serial;
+  int mask_sparse, increment_k_first, is_int8_inference;
+  int min_arch_major, min_arch_minor;
+} cb2_kernel_desp;
+
+int cb2_enumerate_gemm_desps(cb2_kernel_desp *out, int capacity);
+int cb2_enumerate_conv_desps(cb2_kernel_desp *out, int capacity);
+
 /* Rows of one output tile, i.e. the granularity of mask_out_ptr and the mask_width to
  * hand to backward weight (the reference uses the forward kernel's tile_shape[0],
  * cumm/conv/main_real_spconv.py:176-177). */
