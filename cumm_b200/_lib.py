@@ -36,6 +36,7 @@ EXPORTED_SYMBOLS = (
     "cb2_peer_allreduce",
     "cb2_enumerate_gemm_desps",
     "cb2_enumerate_conv_desps",
+    "cb2_last_launch_info",
 )
 
 
@@ -195,6 +196,8 @@ def load() -> ctypes.CDLL:
     for fn in (L.cb2_enumerate_gemm_desps, L.cb2_enumerate_conv_desps):
         fn.restype = ctypes.c_int
         fn.argtypes = [ctypes.POINTER(KernelDesp), ctypes.c_int]
+    L.cb2_last_launch_info.restype = ctypes.c_int
+    L.cb2_last_launch_info.argtypes = [ctypes.POINTER(ctypes.c_int)] * 3
     _lib = L
     return L
 
@@ -229,6 +232,14 @@ def kernel_table(which: str):
     arr = (KernelDesp * n)()
     fn(arr, n)
     return list(arr)
+
+
+def last_launch_info() -> dict:
+    """Registers per thread, threads per CTA and dynamic shared memory of the last kernel this
+    host thread launched through the library (``cb2_last_launch_info``)."""
+    r, t, m = ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0)
+    load().cb2_last_launch_info(ctypes.byref(r), ctypes.byref(t), ctypes.byref(m))
+    return {"num_regs": r.value, "num_threads": t.value, "smem_bytes": m.value}
 
 
 def launch_count() -> int:

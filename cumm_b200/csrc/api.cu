@@ -26,6 +26,14 @@ using namespace cb2;
 
 thread_local std::string g_err;
 std::atomic<uint64_t> g_launches{0};
+struct LaunchInfo {
+  int num_regs = 0, num_threads = 0, smem_bytes = 0;
+};
+thread_local LaunchInfo g_last_launch;
+template <class Kern> int kernel_regs(Kern kern) {
+  cudaFuncAttributes attr;
+  return cudaFuncGetAttributes(&attr, kern) == cudaSuccess ? attr.numRegs : 0;
+}
 
 int set_err(int code, const char *fmt, ...) {
   char buf[512];
@@ -183,12 +191,17 @@ int launch_rowconv_inst(const CUtensorMap &map, const CUtensorMap &map_a, const 
   using Cfg = RowConvCfg<KIND, NATOM_K, BLOCK_N, B_MN, TMA_GATHER>;
   auto kern = rowconv_kernel<KIND, NATOM_K, BLOCK_N, B_MN, TMA_GATHER>;
   static std::atomic<uint64_t> configured{0};  // bit per device
+  static std::atomic<int> regs{0};
   int dev = 0;
   CB2_CUDA(cudaGetDevice(&dev));
   if (!(configured.load() & (1ull << dev))) {
     CB2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    regs.store(kernel_regs(kern));
     configured.fetch_or(1ull << dev);
   }
+  g_last_launch.num_regs = regs.load();
+  g_last_launch.num_threads = Cfg::THREADS;
+  g_last_launch.smem_bytes = Cfg::SMEM_BYTES;
   // A gather-GEMM-scatter call is one of a run of small kernels (one per filter offset), where
   // overlapping each kernel's set-up with its predecessor's tail nearly halves the run.  For the
   // convolutions it measured +4 % for the int8 kernels (long epilogue tail) and neutral to
@@ -313,16 +326,13 @@ int run_rowconv(DeviceState *dev, RowConvParams &p, int kind, bool b_mn, int til
 
 // ---------------------------------------------------------------- weight gradient
 struct WgradLayout {
-  int block_n, gy, G, list_stride;
-  size_t off_arrivals, off_acc, off_lists, total;
-  long long acc_float4;
-  int n_arrivals;
+  int block_n, gy, G, slots, list_stride, n_ctl;
+  size_t off_ctl, off_partials, off_lists, total;
 };
 
-// Workspace of the weight gradient: 512-byte header (tile counts per offset), the arrival
-// counters and the fp32 sums ([kv][gy] tiles of 128 x block_n, then the replica tiles of the
-// offsets with many units), and per offset the list of the row tiles that carry it.
-// G = CTAs per (m, n) tile of the launch.
+// Workspace of the weight gradient: 512-byte header (tile counts per offset), the control words,
+// fp32 partials (one per unit: at most G + kv - 1 <= G + 32), and per offset the list of the
+// row tiles that carry it.  G = CTAs per (m, n) tile of the launch.
 void wgrad_layout(int num_sms, int max_ctas, int m_total, int n_total, long long n_rows, int kv, int tile_n,
                   WgradLayout *L) {
   L->block_n = (tile_n == 64 || tile_n == 128) ? tile_n : (n_total <= 64 ? 64 : 128);
@@ -332,14 +342,12 @@ void wgrad_layout(int num_sms, int max_ctas, int m_total, int n_total, long long
   L->G = sms / L->gy;
   if (L->G < 1)
     L->G = 1;
+  L->slots = L->G + 32;
   const int kvs = kv > 0 ? kv : 1;
-  // per offset one counter and one [128 x block_n] sum, plus the replicas of the heavy offsets
-  const int tiles = kvs * L->gy + kWgradMaxHeavy * L->gy * kWgradMaxReplicas;
-  L->n_arrivals = tiles;
-  L->acc_float4 = (long long)tiles * 32 * L->block_n;
-  L->off_arrivals = 512;
-  L->off_acc = L->off_arrivals + ((size_t)L->n_arrivals * 4 + 255) / 256 * 256;
-  L->off_lists = L->off_acc + (size_t)L->acc_float4 * 16;
+  L->n_ctl = kWgradCtlBase + 4 * kvs * L->gy;
+  L->off_ctl = 512;
+  L->off_partials = L->off_ctl + ((size_t)L->n_ctl * 4 + 255) / 256 * 256;
+  L->off_lists = L->off_partials + (size_t)L->slots * L->gy * 128 * L->block_n * 4;
   const long long ntiles = (n_rows + 127) / 128;
   L->list_stride = (int)((ntiles + 63) / 64 * 64);
   L->total = L->off_lists + (size_t)kvs * L->list_stride * 4;
@@ -351,12 +359,17 @@ int launch_wgrad_inst(const CUtensorMap &ma, const CUtensorMap &mb, const WgradP
   using Cfg = WgradCfg<BLOCK_N, GATHER>;
   auto kern = wgrad_kernel<BLOCK_N, GATHER>;
   static std::atomic<uint64_t> configured{0};
+  static std::atomic<int> regs{0};
   int dev = 0;
   CB2_CUDA(cudaGetDevice(&dev));
   if (!(configured.load() & (1ull << dev))) {
     CB2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    regs.store(kernel_regs(kern));
     configured.fetch_or(1ull << dev);
   }
+  g_last_launch.num_regs = regs.load();
+  g_last_launch.num_threads = Cfg::THREADS;
+  g_last_launch.smem_bytes = Cfg::SMEM_BYTES;
   CB2_CUDA(launch_after(1, kern, dim3(gx, gy), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, stream, ma, mb, p));
   g_launches.fetch_add(1);
   return CB2_OK;
@@ -371,6 +384,8 @@ int run_wgrad(DeviceState *dev, WgradParams &p, int tile_n, int max_ctas, int re
   wgrad_layout(dev->num_sms, max_ctas, p.m_total, p.n_total, p.n_rows, p.kv, tile_n, &L);
   CB2_CHECK_RT(workspace != nullptr && workspace_bytes >= L.total, "workspace at least %zu bytes.", L.total);
   CB2_CHECK_ARG(reinterpret_cast<uintptr_t>(workspace) % 256 == 0, "workspace must be 256-byte aligned");
+  CB2_CHECK_RT(L.gy <= kWgradMaxOutTiles, "the weight gradient has %d output tiles of 128 x %d; at most %d are supported",
+               L.gy, L.block_n, kWgradMaxOutTiles);
   CB2_CHECK_ARG(p.m_total % 8 == 0 && p.n_total % 8 == 0, "channel counts must be multiples of 8");
   CB2_CHECK_ARG((p.ld_dout * 2) % 16 == 0 && (p.ld_x * 2) % 16 == 0, "row strides must be multiples of 16 bytes");
   CB2_CHECK_ARG(aligned16(p.dout) && aligned16(p.x), "operand pointers must be 16-byte aligned");
@@ -379,15 +394,14 @@ int run_wgrad(DeviceState *dev, WgradParams &p, int tile_n, int max_ctas, int re
                 "the weight gradient and its row / offset strides must be 8-byte aligned");
   uint8_t *ws = reinterpret_cast<uint8_t *>(workspace);
   p.sched = reinterpret_cast<int *>(ws);
-  p.arrivals = reinterpret_cast<int *>(ws + L.off_arrivals);
-  p.acc = reinterpret_cast<float *>(ws + L.off_acc);
+  p.ctl = reinterpret_cast<int *>(ws + L.off_ctl);
+  p.partials = reinterpret_cast<float *>(ws + L.off_partials);
   p.lists = reinterpret_cast<const int *>(ws + L.off_lists);
   p.list_stride = L.list_stride;
   p.status = dev->status;
   if (!reuse_plan) {
-    // counts and lists of the row tiles per offset; sums and arrival counters to zero
-    wgrad_plan_kernel<<<p.kv, 1024, 0, stream>>>(p, reinterpret_cast<int *>(ws + L.off_lists), L.list_stride,
-                                                 L.acc_float4, L.n_arrivals);
+    // counts and lists of the row tiles per offset; control words to zero
+    wgrad_plan_kernel<<<p.kv, 1024, 0, stream>>>(p, reinterpret_cast<int *>(ws + L.off_lists), L.list_stride, L.n_ctl);
     CB2_CUDA(cudaGetLastError());
     g_launches.fetch_add(1);
   }
@@ -859,6 +873,16 @@ int cb2_tile_m(void) { return 128; }
 
 uint64_t cb2_launch_count(void) { return g_launches.load(); }
 
+int cb2_last_launch_info(int *num_regs, int *num_threads, int *smem_bytes) {
+  if (num_regs)
+    *num_regs = g_last_launch.num_regs;
+  if (num_threads)
+    *num_threads = g_last_launch.num_threads;
+  if (smem_bytes)
+    *smem_bytes = g_last_launch.smem_bytes;
+  return CB2_OK;
+}
+
 int cb2_device_status(int *status) {
   DeviceState *dev;
   int rc = get_device(&dev);
@@ -949,8 +973,9 @@ int cb2_conv_backward_weight_static(const cb2_conv_args *a, void *stream_v) {
   p.alpha = a->alpha;
   p.beta = a->beta;
   p.out_f32 = a->dtype_c == CB2_DTYPE_F32 ? 1 : 0;
-  // the planning kernel of every call clears the sums and counters the main kernel uses, so
-  // whatever an earlier call (of any size) left in the scratch does not matter
+  // the planning kernel of every call clears the control words the main kernel uses and the main
+  // kernel rewrites every partial it later reads, so whatever an earlier call (of any size) left
+  // in the scratch does not matter
   return run_wgrad(&st->dev, p, a->tile_n, a->max_ctas, 0, st->scratch, kStaticScratchBytes, stream);
 }
 

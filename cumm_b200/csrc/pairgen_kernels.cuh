@@ -12,6 +12,10 @@
 // Everything is integer work on HBM-resident arrays: coalesced passes, no tensor cores.
 // All loops are bounded: a probe sequence visits at most `capacity` slots and reports a full
 // table through the status word instead of spinning.
+// None of these kernels triggers programmatic dependent launch (griddepcontrol.launch_dependents):
+// the convolution kernels read masks, sort orders and index rows BEFORE their own
+// griddepcontrol.wait, which is only sound while whatever wrote those tables has completed in
+// the ordinary stream order.  Keep it that way.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>

@@ -6,15 +6,14 @@
 // The reduction runs over (sorted) rows, so both tcgen05 operands are gathered rows held
 // "MN-major": a gathered row is 128-byte-swizzled along its channels and the 128 rows of a
 // tile are the K dimension of the MMA.  Work is cut into units (filter offset f, range of
-// row tiles); a unit accumulates in TMEM and adds its fp32 result [128 x BLOCK_N] into the
-// offset's accumulator in the workspace (vector reductions that complete in L2), then counts
-// itself in; the CTA whose unit completes an offset applies alpha/beta, converts, writes dW and
-// puts the accumulator and the counter back to zero.  Additions to one address are performed one
-// after the other in L2, so an offset that has many units (the centre of a submanifold
-// convolution has one per CTA) spreads them over several replica accumulators, and the unit that
-// completes a replica adds it into the offset's accumulator: two short queues per address instead
-// of one long one.  One launch, and nobody waits for anybody (the reference serialises split-K
-// slices through a spinning semaphore, cumm/conv/kernel.py:960-1083).
+// row tiles); a unit accumulates in TMEM, leaves one fp32 partial [128 x BLOCK_N] in the
+// workspace and counts itself in.  The unit that completes an offset marks it ready; from then
+// on its partials are summed -- in unit order, so the result does not depend on timing -- in
+// column slices that any CTA of the grid may take: a CTA that has finished its own units stays
+// for a bounded time and takes slices of ready offsets, and the CTA that made an offset ready
+// does not leave before all of that offset's slices have been taken.  One launch, no atomics on
+// data, and nobody's progress depends on anybody else's (the reference serialises split-K slices
+// through a spinning semaphore, cumm/conv/kernel.py:960-1083).
 //
 // Semantics follow cumm/gemm/blockmma/mma.py:608-648,722-740 (a row takes part for
 // offset f iff the reduced-mask word covering it has bit f), cumm/conv/sparse_iters.py
@@ -39,10 +38,10 @@ struct WgradParams {
   const int32_t *argsort;  // [n_rows]
   const int32_t *a_inds;   // pair-list mode
   const int32_t *b_inds;   //   "
-  float *acc;              // workspace: [f][m_tile][n_tile][128 x BLOCK_N] fp32 sums, then the replica sums
-                           // [heavy offset h][m_tile][n_tile][replica][128 x BLOCK_N]; all zero between calls
-  int *arrivals;           // workspace: [f][m_tile][n_tile] arrivals at an offset's sums, then
-                           // [h][m_tile][n_tile][replica] arrivals at a replica; all zero between calls
+  float *partials;         // workspace: [unit][m_tile][n_tile][128 x BLOCK_N] fp32
+  int *ctl;                // workspace, zero between calls: [0] CTAs that have left; [8 + 2 by] offsets summed and
+                           // [9 + 2 by] bit mask of the ready offsets of output tile by; from kWgradCtlBase
+                           // on, four ints per (f, by): units arrived, next slice to hand out, slices summed
   int *sched;              // workspace header: [0,32) number of row tiles carrying offset f
   const int *lists;        // workspace: per offset, the ordered list of those tiles
   int list_stride;         // ints between two offsets' lists
@@ -109,7 +108,7 @@ __device__ __forceinline__ uint32_t wgrad_tile_mask(const WgradParams &p, int ti
 // there are at most G + kv - 1 of them.
 //
 // A small planning kernel (one block per offset) writes, per offset, the count and the ordered
-// list of its tiles, and clears the accumulators and arrival counters; the main kernel derives
+// list of its tiles, and clears the control words; the main kernel derives
 // everything else from the kv counts.  The plan depends only on the reduced masks, the row
 // count and the mask filter, so a caller that runs the same layer again (the next training
 // step) may keep it: see `reuse_plan` in the C ABI.
@@ -153,20 +152,13 @@ __device__ __forceinline__ void wgrad_plan_warp(int cnt, int G, int &P, int &T, 
 // One block per filter offset: count and list the tiles that carry it.  Warp w owns a
 // contiguous span of tiles, so the list comes out in ascending order with one block-wide
 // synchronisation per batch of 1024 * K tiles.
-__global__ void __launch_bounds__(1024) wgrad_plan_kernel(const WgradParams p, int *lists, int list_stride,
-                                                           long long acc_float4, int n_arrivals) {
+__global__ void __launch_bounds__(1024) wgrad_plan_kernel(const WgradParams p, int *lists, int list_stride, int n_ctl) {
   constexpr int K = 4;  // 4096 tiles per batch
   __shared__ int s_w[32];
   const int f = blockIdx.x;
-  // sums and arrival counters start from zero (every later call leaves them at zero again)
-  {
-    float4 *a4 = reinterpret_cast<float4 *>(p.acc);
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < acc_float4;
-         i += (long long)gridDim.x * blockDim.x)
-      a4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_arrivals; i += gridDim.x * blockDim.x)
-      p.arrivals[i] = 0;
-  }
+  // the control words start from zero (every later call leaves them at zero again)
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_ctl; i += gridDim.x * blockDim.x)
+    p.ctl[i] = 0;
   const int ntiles = (p.n_rows + 127) / 128;
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   grid_dep_launch();  // the main kernel may set itself up meanwhile; it waits before reading the lists
@@ -211,23 +203,15 @@ __global__ void __launch_bounds__(1024) wgrad_plan_kernel(const WgradParams p, i
 // Per CTA, in shared memory: s_plan[0] = number of units of this CTA, then five ints per unit
 // {f, first list index, one past the last, unit number, offset of its tiles in s_tiles};
 // s_tiles = the CTA's tiles in step order (when they fit; otherwise the walk reads the lists).
-// The unit number counts from the offset's first unit.  After the unit records:
-// s_plan[kWgradPlanUnits + f] = units of offset f over all CTAs, s_plan[kWgradPlanHeavy + f] = the
-// offset's place among the "heavy" offsets (those with more than kWgradDirectUnits units, which
-// get replica accumulators; the first kWgradMaxHeavy of them), or -1.
+// The unit number is global: the units of an offset are consecutive.  After the unit records:
+// s_plan[kWgradPlanUnits + f] = units of offset f over all CTAs, s_plan[kWgradPlanFirst + f] = the
+// first of them.
 constexpr int kWgradPlanUnits = 8 + 5 * 32;
-constexpr int kWgradPlanHeavy = kWgradPlanUnits + 32;
-constexpr int kWgradPlanInts = kWgradPlanHeavy + 32;
-constexpr int kWgradDirectUnits = 8;   // up to this many units add straight into the offset's sums
-constexpr int kWgradMaxHeavy = 4;      // offsets that can have replica sums
-constexpr int kWgradMaxReplicas = 16;  // replica sums per heavy offset
-// Replicas an offset with S units uses: about the square root of S, so that both queues are short.
-__host__ __device__ __forceinline__ int wgrad_replicas(int S) {
-  int r = 1;
-  while (r * r < S && r < kWgradMaxReplicas)
-    ++r;
-  return r;
-}
+constexpr int kWgradPlanFirst = kWgradPlanUnits + 32;
+constexpr int kWgradPlanInts = kWgradPlanFirst + 32;
+constexpr int kWgradMaxOutTiles = 128; // (m, n) tiles of the weight gradient a launch can have
+constexpr int kWgradCtlBase = 8 + 2 * kWgradMaxOutTiles;  // first per-(offset, tile) control word
+constexpr int kWgradLingerPolls = 256; // a CTA with nothing to do looks for ready slices this often, then leaves
 template <int TILE_CAP>
 __device__ __forceinline__ void wgrad_load_plan(const WgradParams &p, const int *lists, int list_stride, int *s_plan,
                                                 int *s_tiles) {
@@ -238,11 +222,7 @@ __device__ __forceinline__ void wgrad_load_plan(const WgradParams &p, const int 
     int P, T, c_first, S, U;
     wgrad_plan_warp(cnt, G, P, T, c_first, S, U);
     s_plan[kWgradPlanUnits + f] = S;
-    {
-      const uint32_t heavy = __ballot_sync(0xffffffffu, S > kWgradDirectUnits);
-      const int h = __popc(heavy & ((1u << f) - 1u));
-      s_plan[kWgradPlanHeavy + f] = (S > kWgradDirectUnits && h < kWgradMaxHeavy) ? h : -1;
-    }
+    s_plan[kWgradPlanFirst + f] = U;
     const int b0 = (int)(((long long)c * T) / G), b1 = (int)(((long long)(c + 1) * T) / G);
     const bool has = cnt > 0 && c >= c_first && c < c_first + S;
     int k0 = 0, k1 = 0;
@@ -266,7 +246,7 @@ __device__ __forceinline__ void wgrad_load_plan(const WgradParams &p, const int 
       e[0] = f;
       e[1] = k0;
       e[2] = k1;
-      e[3] = c - c_first;
+      e[3] = U + (c - c_first);
       e[4] = len_incl - (k1 - k0);
     }
     if (f == 0) {
@@ -379,18 +359,19 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
   const int gy = gridDim.y;
 
   if (warp < 4) {
-    // ======================= epilogue: add each unit's result into its offset's sums; the unit
-    // that completes an offset turns the sums into dW
+    // ======================= epilogue: one fp32 partial per unit, then the shared summing of
+    // whatever offsets are ready
     const int et = threadIdx.x;
     const int *s_units = s_plan + kWgradPlanUnits;
+    const int *s_first = s_plan + kWgradPlanFirst;
     const long long tile_f4 = 32ll * BLOCK_N;  // float4 per [128 x BLOCK_N] tile
-    // sums layout: float4 (col/4, row) at index (col/4) * 128 + row, so that the 32 rows of a
-    // warp touch 512 contiguous bytes
-    auto sums_of = [&](int f) { return reinterpret_cast<float4 *>(p.acc) + ((long long)f * gy + blockIdx.y) * tile_f4; };
-    auto replica_sums = [&](int h, int rep) {
-      return reinterpret_cast<float4 *>(p.acc) +
-             ((long long)p.kv * gy + ((long long)h * gy + blockIdx.y) * kWgradMaxReplicas + rep) * tile_f4;
+    constexpr int kSlices = BLOCK_N / 4;       // a slice = four columns of all 128 rows: one float4 per thread
+    // partial layout: float4 (col/4, row) at index (col/4) * 128 + row, so that the 32 rows of a
+    // warp touch 512 contiguous bytes; slice q of a partial is its q-th run of 128 float4
+    auto partial_of = [&](int u) {
+      return reinterpret_cast<float4 *>(p.partials) + ((long long)u * gy + blockIdx.y) * tile_f4;
     };
+    auto ctl_of = [&](int f) { return p.ctl + kWgradCtlBase + 4 * ((long long)f * gy + blockIdx.y); };
     // dW[m0 + row, f, n0 + 4 * q .. + 3] from four sums
     auto write_out = [&](int f, int row, int q, float4 v) {
       const int m = m0 + row, n = n0 + 4 * q;
@@ -419,23 +400,25 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
     };
     // Offsets inside the filter that no row tile carries get alpha * 0 + beta * source; CTA c
     // takes those with f = c (mod G).
+    int n_active = 0;  // offsets that have units: the ones that will be summed
+    for (int f = 0; f < p.kv; ++f)
+      n_active += s_units[f] > 0 ? 1 : 0;
     for (int f = blockIdx.x; f < p.kv; f += gridDim.x)
       if (((p.mask_filter >> f) & 1u) && s_units[f] == 0)
-        for (int q = 0; q < BLOCK_N / 4; ++q)
+        for (int q = 0; q < kSlices; ++q)
           write_out(f, et, q, make_float4(0.f, 0.f, 0.f, 0.f));
     int acc_use = 0;
+    bool walk_ok = true;
     wgrad_walk(
         p.lists, p.list_stride, s_plan, s_tiles, [&](int, int) -> bool { return true; },
         [&](int, int, bool) -> bool { return true; },
         [&](int u, int f, int active) -> bool {
-          // where this unit adds its result: the offset's sums, or one of its replicas
-          const int S = s_units[f];
-          const int h = s_plan[kWgradPlanHeavy + f];
-          const int R = h >= 0 ? wgrad_replicas(S) : 1;
-          const int rep = h >= 0 ? u % R : 0;
-          float4 *final_sums = sums_of(f) + et;
-          float4 *sums = h >= 0 ? replica_sums(h, rep) + et : final_sums;
-          if (active > 0) {
+          float4 *dst = partial_of(u) + et;
+          if (active == 0) {
+            // a unit without tiles (fewer steps than CTAs) still owns a partial: all zeros
+            for (int q = 0; q < kSlices; ++q)
+              dst[q * 128] = make_float4(0.f, 0.f, 0.f, 0.f);
+          } else {
             const int buf = acc_use & 1;
             if (et == 0) {
               CB2_TRACE_EVENT(4, 7, u);
@@ -446,8 +429,10 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
                 fail(kStatusWaitTimeout);
             }
             named_bar_sync(1, 128);
-            if (misc[2] == 0)
+            if (misc[2] == 0) {
+              walk_ok = false;
               return false;
+            }
             tc_fence_after();
             const uint32_t trow = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
                                   static_cast<uint32_t>(buf * BLOCK_N);
@@ -458,61 +443,94 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
               tmem_ld_wait();
 #pragma unroll
               for (int q = 0; q < 8; ++q)
-                red_add_f32x4(sums + (round * 8 + q) * 128, __uint_as_float(v[q * 4]), __uint_as_float(v[q * 4 + 1]),
-                              __uint_as_float(v[q * 4 + 2]), __uint_as_float(v[q * 4 + 3]));
+                reinterpret_cast<uint4 *>(dst)[(round * 8 + q) * 128] = make_uint4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
             }
             tc_fence_before();
             mbar_arrive(acc_empty(buf));
             ++acc_use;
-            __threadfence();  // this thread's additions are performed before the unit is counted in
           }
-          // A unit without tiles (fewer steps than CTAs) is still counted in.  `arrive` counts this
-          // CTA in at `counter` and tells all 128 threads whether it was the last of `expected`;
-          // the last one finds everybody's additions performed and leaves the counter at zero.
-          auto arrive = [&](int *counter, int expected) -> bool {
-            named_bar_sync(1, 128);
-            if (et == 0) {
-              const int before = atomicAdd(counter, 1);
-              misc[6] = (before == expected - 1) ? 1 : 0;
-              if (before == expected - 1) {
-                *counter = 0;
-                __threadfence();
-              }
-            }
-            named_bar_sync(1, 128);
-            return misc[6] != 0;
-          };
-          bool complete;
-          if (h >= 0) {
-            // units rep, rep + R, rep + 2R ... of the offset share this replica
-            int *rep_counter = p.arrivals + (long long)p.kv * gy + ((long long)h * gy + blockIdx.y) * kWgradMaxReplicas + rep;
-            complete = false;
-            if (arrive(rep_counter, (S - rep + R - 1) / R)) {
-              // the replica is complete: move it into the offset's sums and leave it zero
-#pragma unroll 4
-              for (int q = 0; q < BLOCK_N / 4; ++q) {
-                const float4 v = __ldcg(sums + q * 128);
-                __stcg(sums + q * 128, make_float4(0.f, 0.f, 0.f, 0.f));
-                red_add_f32x4(final_sums + q * 128, v.x, v.y, v.z, v.w);
-              }
+          // count the unit in; the one that completes the offset marks it ready
+          __threadfence();  // this thread's part of the partial is visible before the unit counts
+          named_bar_sync(1, 128);
+          if (et == 0) {
+            if (atomicAdd(ctl_of(f), 1) == s_units[f] - 1) {
               __threadfence();
-              complete = arrive(p.arrivals + (long long)f * gy + blockIdx.y, R);
+              atomicOr(p.ctl + 9 + 2 * blockIdx.y, 1 << f);  // ready: every partial of f is in place
             }
-          } else {
-            complete = arrive(p.arrivals + (long long)f * gy + blockIdx.y, S);
+            CB2_TRACE_EVENT(4, 9, u);  // partial written
           }
-          if (complete) {
-#pragma unroll 4
-            for (int q = 0; q < BLOCK_N / 4; ++q) {
-              const float4 v = __ldcg(final_sums + q * 128);
-              __stcg(final_sums + q * 128, make_float4(0.f, 0.f, 0.f, 0.f));
-              write_out(f, et, q, v);
-            }
-          }
-          if (et == 0)
-            CB2_TRACE_EVENT(4, 9, u);  // unit added
           return true;
         });
+    // ---- summing: take column slices of ready offsets until this tile's offsets are all summed,
+    // or nothing has been on offer for a while (whoever makes an offset ready finds its slices on
+    // offer in this very loop, so every slice is taken by somebody)
+    int polls = 0;
+    uint32_t handed_out = 0;  // offsets whose slices are known to be all taken (thread 0)
+    while (walk_ok) {
+      if (et == 0) {
+        int job = -1;
+        uint32_t open = static_cast<uint32_t>(ld_acquire_gpu(p.ctl + 9 + 2 * blockIdx.y)) & ~handed_out;
+        // start at a different offset in every CTA so that the CTAs spread over the ready offsets
+        const int rot = blockIdx.x % p.kv;
+        open = rot ? ((open >> rot) | (open << (32 - rot))) : open;
+        while (open && job < 0) {
+          const int k = __ffs(open) - 1;
+          open &= open - 1;
+          const int f = (k + rot) & 31;
+          const int sl = atomicAdd(ctl_of(f) + 1, 1);
+          if (sl < kSlices)
+            job = f * kSlices + sl;
+          else
+            handed_out |= 1u << f;
+        }
+        if (job < 0) {
+          const bool all_summed = ld_acquire_gpu(p.ctl + 8 + 2 * blockIdx.y) >= n_active;
+          if (all_summed || ++polls > kWgradLingerPolls)
+            job = -2;
+          else
+            __nanosleep(100);
+        }
+        misc[6] = job;
+      }
+      named_bar_sync(1, 128);
+      const int job = misc[6];
+      named_bar_sync(1, 128);  // everybody has read the job before thread 0 writes the next one
+      if (job == -2)
+        break;
+      if (job < 0)
+        continue;
+      const int f = job / kSlices, sl = job % kSlices;
+      const int S = s_units[f];
+      const float4 *src = partial_of(s_first[f]) + sl * 128 + et;
+      const long long ustride = (long long)gy * tile_f4;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+      for (int j = 0; j < S; ++j) {
+        const float4 v = __ldcg(src + j * ustride);
+        acc.x += v.x;
+        acc.y += v.y;
+        acc.z += v.z;
+        acc.w += v.w;
+      }
+      write_out(f, et, sl, acc);
+      named_bar_sync(1, 128);
+      if (et == 0) {
+        if (atomicAdd(ctl_of(f) + 2, 1) == kSlices - 1)
+          atomicAdd(p.ctl + 8 + 2 * blockIdx.y, 1);
+      }
+    }
+    // the last CTA to leave puts every control word back to zero for the next call
+    if (et == 0) {
+      __threadfence();
+      misc[6] = atomicAdd(p.ctl, 1) == (int)(gridDim.x * gridDim.y) - 1 ? 1 : 0;
+    }
+    named_bar_sync(1, 128);
+    if (misc[6]) {
+      const int n_ctl = kWgradCtlBase + 4 * p.kv * gy;
+      for (int i = et; i < n_ctl; i += 128)
+        p.ctl[i] = 0;
+      __threadfence();
+    }
   } else if (warp == 4) {
     // ======================= MMA issuer
     constexpr uint32_t idesc = make_idesc(0, true, true, 128, BLOCK_N);

@@ -136,3 +136,99 @@ def as_view(t) -> Optional[Tensor]:
         raise RuntimeError("tensors must live on a CUDA device (there is no CPU path)")
     return Tensor(t.data_ptr(), list(t.shape), _torch_dtype_code(t.dtype), t.device.index or 0,
                   list(t.stride()), keepalive=t)
+
+
+class CUDAKernelTimer:
+    """Named CUDA-event pairs with a namespace stack: the per-call ``timer`` of ``GemmParams`` /
+    ``ConvParams`` (tv::CUDAKernelTimer, include/tensorview/profile/cuda_profiler.h:225-405).  When
+    a call's params carry an enabled timer, the launch is bracketed by one event pair on the
+    call's stream, filed under the kernel's algorithm name, as the reference's
+    ``CUDAKernelTimerGuard`` does (cuda_profiler.h:408-440; cumm/conv/main.py:708).  Durations
+    are in milliseconds.  A name can be recorded once: use a fresh timer (or ``push`` another
+    namespace) for a second call of the same kernel."""
+
+    def __init__(self, enable: bool = True):
+        self.enable = bool(enable)
+        self._ns: List[str] = []
+        self._events = {}
+        self._pairs = {}
+
+    def push(self, name: str) -> None:
+        if self.enable:
+            self._ns.append(name)
+
+    def pop(self) -> None:
+        if self.enable:
+            if not self._ns:
+                raise RuntimeError("you pop value from empty namespaces")
+            self._ns.pop()
+
+    def _unique(self, name: str) -> str:
+        cur = ".".join(self._ns)
+        if not name:
+            return cur
+        return f"{cur}.{name}" if cur else name
+
+    def record(self, name: str, stream: int = 0) -> None:
+        if not self.enable:
+            return
+        import torch
+        unique = self._unique(name)
+        if unique in self._events:
+            raise RuntimeError(f"your name {unique} already exists")
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(torch.cuda.ExternalStream(int(stream)) if stream else torch.cuda.current_stream())
+        self._events[unique] = ev
+
+    def insert_pair(self, name: str, start: str, stop: str) -> str:
+        if not self.enable:
+            return ""
+        name, start, stop = self._unique(name), self._unique(start), self._unique(stop)
+        if name in self._pairs:
+            raise RuntimeError(f"your name {name} already exists")
+        self._pairs[name] = (start, stop)
+        return name
+
+    def has_pair(self, name: str) -> bool:
+        return self._unique(name) in self._pairs
+
+    def sync_all_event(self) -> None:
+        for ev in self._events.values():
+            ev.synchronize()
+
+    def get_pair_duration(self, name: str) -> float:
+        if name not in self._pairs:
+            raise RuntimeError(f"can't find your pair {name}")
+        a, b = (self._events[k] for k in self._pairs[name])
+        a.synchronize()
+        b.synchronize()
+        return float(a.elapsed_time(b))
+
+    def get_all_pair_time(self):
+        self.sync_all_event()
+        return {k: float(self._events[a].elapsed_time(self._events[b])) for k, (a, b) in self._pairs.items()}
+
+    get_all_pair_duration = get_all_pair_time
+
+
+class _TimerGuard:
+    """``with _TimerGuard(name, timer, stream):`` -- tv::CUDAKernelTimerGuard."""
+
+    def __init__(self, name: str, timer: Optional[CUDAKernelTimer], stream: int = 0):
+        self.name, self.timer, self.stream = name, timer, stream
+        self.active = timer is not None and getattr(timer, "enable", False)
+
+    def __enter__(self):
+        if self.active:
+            if self.name:
+                self.timer.push(self.name)
+            self.pair = self.timer.insert_pair("", "start", "stop")
+            self.timer.record("start", self.stream)
+        return self
+
+    def __exit__(self, *exc):
+        if self.active:
+            self.timer.record("stop", self.stream)
+            if self.name:
+                self.timer.pop()
+        return False

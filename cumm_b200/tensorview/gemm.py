@@ -608,7 +608,8 @@ def run_gemm(params: GemmParams) -> None:
         ptr, nbytes = _workspace_for(args._device, int(params.stream), need, params.workspace)
         args.workspace, args.workspace_bytes = ptr, nbytes
     import torch
-    with torch.cuda.device(args._device):
+    from . import _TimerGuard
+    with torch.cuda.device(args._device), _TimerGuard(params.algo_desp.__repr__(), params.timer, int(params.stream)):
         _lib.raise_for(L.cb2_gemm_run(ctypes.byref(args), ctypes.c_void_p(int(params.stream))))
 
 
@@ -733,19 +734,50 @@ def run_conv(params: ConvParams) -> None:
         ptr, nbytes = _workspace_for(args._device, int(params.stream), need, params.workspace)
         args.workspace, args.workspace_bytes = ptr, nbytes
     import torch
-    with torch.cuda.device(args._device):
+    from . import CUDAKernelTimer, _TimerGuard
+    name = params.conv_algo_desp.__repr__()
+    # verbose: registers of the kernel and the time of this launch (cumm/conv/main.py:723-729)
+    timer = params.timer
+    own = None
+    if params.verbose and not (timer is not None and getattr(timer, "enable", False)):
+        timer = own = CUDAKernelTimer(True)
+    with torch.cuda.device(args._device), _TimerGuard(name, timer, int(params.stream)):
         _lib.raise_for(L.cb2_conv_run(ctypes.byref(args), ctypes.c_void_p(int(params.stream))))
+    if params.verbose:
+        info = _lib.last_launch_info()
+        t = (own or timer).get_pair_duration(name)
+        print(f"{name} kernel num regs: {info['num_regs']} time: {t}")
+
+
+# The reference's run_nvrtc_* entry points launch the run-time-compiled module the caller puts
+# in ``params.nvrtc_params`` and throw when there is none.  This library ships prebuilt sm_100a
+# kernels and loads no foreign modules; a caller that wants those entry points to use the
+# prebuilt kernels says so here (or with CUMM_B200_NVRTC_USES_PREBUILT=1 in the environment).
+NVRTC_ENTRY_POINTS_USE_PREBUILT = False
+
+
+def _nvrtc_gate(nvrtc_params, what: str) -> None:
+    import os
+    if getattr(nvrtc_params, "cumodule", None) is not None:
+        raise RuntimeError(f"run-time-compiled modules are not loaded by this library; clear nvrtc_params.cumodule and "
+                           f"call the static entry point (matmul2 / implicit_gemm2) to run {what} on the prebuilt kernels")
+    if not (NVRTC_ENTRY_POINTS_USE_PREBUILT or os.environ.get("CUMM_B200_NVRTC_USES_PREBUILT") == "1"):
+        raise RuntimeError(f"you must use nvrtc kernel to run {what} by this function")
 
 
 def run_nvrtc_gemm_kernel(params: GemmParams) -> None:
-    """cumm/tensorview_bind.py:134-150.  The reference requires a run-time-compiled module
-    in ``params.nvrtc_params``; the prebuilt sm_100a kernels take its place, so the call
-    dispatches like ``matmul2``."""
+    """cumm/tensorview_bind.py:152-167: validates like ``matmul2``, then requires a
+    run-time-compiled kernel in ``params.nvrtc_params`` and throws without one.  Here: the
+    same error, unless :data:`NVRTC_ENTRY_POINTS_USE_PREBUILT` opts into the prebuilt kernels."""
+    _gemm_args(params)
+    _nvrtc_gate(params.nvrtc_params, "gemm")
     run_gemm(params)
 
 
 def run_nvrtc_conv_kernel(params: ConvParams) -> None:
-    """cumm/tensorview_bind.py:152-167; see :func:`run_nvrtc_gemm_kernel`."""
+    """cumm/tensorview_bind.py:134-150; see :func:`run_nvrtc_gemm_kernel`."""
+    _conv_args(params)
+    _nvrtc_gate(params.nvrtc_params, "conv")
     run_conv(params)
 
 

@@ -330,6 +330,11 @@ const char *cb2_last_error(void);
  * range; 3 and 4: see cb2_pairgen_args) in *status and clears it. */
 int cb2_device_status(int *status);
 
+/* Registers per thread, threads per CTA and dynamic shared memory of the last convolution / GEMM
+ * kernel launched by the calling host thread (what the reference prints for ConvParams::verbose
+ * from cudaFuncGetAttributes, cumm/conv/main.py:723-729).  Any pointer may be null. */
+int cb2_last_launch_info(int *num_regs, int *num_threads, int *smem_bytes);
+
 /* Number of kernels this library has launched from the calling process (all threads). */
 uint64_t cb2_launch_count(void);
 

@@ -325,3 +325,38 @@ def test_every_listed_tile_shape_computes_the_same(torch, oracle):
         got = H.run_conv_wgrad(torch, dout, x, tb, mo, tile=t)
         H.check_status()
         H.assert_close_wgrad(got, want_w, tb.indices, f"wgrad tile {t}")
+
+
+def test_timer_verbose_and_nvrtc_entry_point(torch, oracle, capsys, monkeypatch):
+    """params.timer brackets the launch with one event pair filed under the algorithm name
+    (cumm/conv/main.py:708); verbose prints registers and time (:723-729); run_nvrtc_conv_kernel
+    throws without a run-time-compiled module (cumm/tensorview_bind.py:147-149) unless the caller
+    opts into the prebuilt kernels."""
+    import cumm_b200.tensorview.gemm as G
+    from cumm_b200.tensorview import CUDAKernelTimer
+    tb, x, w, _ = make(1500, 801, 64, 64)
+    timer = CUDAKernelTimer(True)
+    p = ConvParams(3, ConvOpType.Forward, timer)
+    p.conv_algo_desp = H.conv_desp(ConvOpType.Forward, 64, 64)
+    p.input, p.weight = H.dev(x, torch), H.dev(w, torch)
+    p.output = torch.zeros((tb.n_out, 64), dtype=torch.float16, device="cuda")
+    p.indices, p.mask, p.mask_argsort = H.dev(tb.indices, torch), H.mask_to_torch(tb.mask, torch), H.dev(tb.mask_argsort, torch)
+    p.verbose = True
+    ConvMainUnitTest.implicit_gemm2(p)
+    name = p.conv_algo_desp.__repr__()
+    times = timer.get_all_pair_time()
+    assert list(times) == [name] and 0.0 < times[name] < 100.0  # milliseconds
+    printed = capsys.readouterr().out
+    assert name in printed and "kernel num regs:" in printed and "time:" in printed
+    want = oracle.mask_igemm(x, w, np.zeros((tb.n_out, 64), np.float16), tb.indices, tb.mask, tb.mask_argsort)
+    H.assert_close_f16(p.output.cpu().numpy(), want, "forward with timer")
+    p.verbose, p.timer = False, None
+    monkeypatch.delenv("CUMM_B200_NVRTC_USES_PREBUILT", raising=False)
+    with pytest.raises(RuntimeError, match="you must use nvrtc kernel"):
+        G.run_nvrtc_conv_kernel(p)
+    monkeypatch.setattr(G, "NVRTC_ENTRY_POINTS_USE_PREBUILT", True)
+    p.output.zero_()
+    G.run_nvrtc_conv_kernel(p)
+    torch.cuda.synchronize()
+    H.assert_close_f16(p.output.cpu().numpy(), want, "forward through run_nvrtc_conv_kernel, opted in")
+    H.check_status()

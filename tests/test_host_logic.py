@@ -238,3 +238,65 @@ def test_peer_allreduce_buffer_size_is_a_host_function():
     assert L.cb2_peer_allreduce_buffer_size(numel + 2, 8) == 0  # not a multiple of 4
     assert L.cb2_peer_allreduce_buffer_size(numel, 17) == 0
     assert L.cb2_peer_allreduce_buffer_size(0, 2) == 0
+
+
+def test_kernel_table_comes_from_the_library():
+    """get_all_algo_desp / get_all_conv_algo_desp read cb2_enumerate_*_desps (no GPU needed)."""
+    from cumm_b200.conv.main import ConvMainUnitTest
+    from cumm_b200.gemm.main import GemmMainUnitTest
+    from cumm_b200.tensorview.gemm import ConvOpType, ShuffleStrideType
+    L = ctypes.CDLL(str(_lib.LIB_PATH))
+    for fn in (L.cb2_enumerate_gemm_desps, L.cb2_enumerate_conv_desps):
+        fn.restype = ctypes.c_int
+        fn.argtypes = [ctypes.POINTER(_lib.KernelDesp), ctypes.c_int]
+    assert L.cb2_enumerate_gemm_desps(None, 0) == 18 and L.cb2_enumerate_conv_desps(None, 0) == 12
+    two = (_lib.KernelDesp * 2)()
+    assert L.cb2_enumerate_conv_desps(two, 2) == 12  # the count, whatever the capacity
+    assert two[0].op_type == 0 and list(two[0].tile_shape) == [128, 64, 64] and two[1].tile_shape[2] == 128
+    gemm = GemmMainUnitTest.get_all_algo_desp()
+    conv = ConvMainUnitTest.get_all_conv_algo_desp()
+    assert len(gemm) == 18 and len(conv) == 12
+    assert sum(d.shuffle_type == ShuffleStrideType.ShuffleAB for d in gemm) == 2
+    assert all(d.trans_a and not d.trans_b and d.split_k_serial for d in gemm if d.shuffle_type == ShuffleStrideType.ShuffleAB)
+    assert sum(bool(d.is_int8_inference) for d in conv) == 2
+    assert {tuple(d.tile_shape) for d in conv if d.op_type == ConvOpType.BackwardWeight} == {(128, 64, 128), (128, 128, 128)}
+    names = {d.__repr__() for d in conv} | {d.__repr__() for d in gemm}
+    assert len(names) == 30, "every variant has its own algorithm name"
+    assert all(n.startswith("Blackwell_") for n in names)
+
+
+def test_nvrtc_entry_points_throw_without_a_module(monkeypatch):
+    """cumm/tensorview_bind.py:147-149,164-166: run_nvrtc_* need a run-time-compiled kernel."""
+    import cumm_b200.tensorview.gemm as G
+    monkeypatch.delenv("CUMM_B200_NVRTC_USES_PREBUILT", raising=False)
+    with pytest.raises(RuntimeError, match="you must use nvrtc kernel to run conv"):
+        G._nvrtc_gate(G.NVRTCParams(), "conv")
+    with pytest.raises(RuntimeError, match="you must use nvrtc kernel to run gemm"):
+        G._nvrtc_gate(G.NVRTCParams(), "gemm")
+    p = G.NVRTCParams()
+    p.cumodule = object()
+    with pytest.raises(RuntimeError, match="not loaded by this library"):
+        G._nvrtc_gate(p, "gemm")
+    monkeypatch.setattr(G, "NVRTC_ENTRY_POINTS_USE_PREBUILT", True)
+    G._nvrtc_gate(G.NVRTCParams(), "conv")  # opted in: no error
+
+
+def test_kernel_timer_names_follow_the_namespace_stack():
+    """tv::CUDAKernelTimer naming rules (cuda_profiler.h:225-300), without touching a GPU."""
+    from cumm_b200.tensorview import CUDAKernelTimer
+    t = CUDAKernelTimer(True)
+    t.push("layer1")
+    t.push("Blackwell_x")
+    assert t._unique("start") == "layer1.Blackwell_x.start" and t._unique("") == "layer1.Blackwell_x"
+    name = t.insert_pair("", "start", "stop")
+    assert name == "layer1.Blackwell_x" and t.has_pair("")
+    with pytest.raises(RuntimeError, match="already exists"):
+        t.insert_pair("", "start", "stop")
+    t.pop()
+    t.pop()
+    with pytest.raises(RuntimeError, match="empty namespaces"):
+        t.pop()
+    off = CUDAKernelTimer(False)
+    off.push("x")
+    off.record("start")
+    assert off.insert_pair("", "a", "b") == "" and off._events == {}
