@@ -136,6 +136,7 @@ class KernelDesp(ctypes.Structure):
         ("split_k_serial", ctypes.c_int),
         ("mask_sparse", ctypes.c_int), ("increment_k_first", ctypes.c_int), ("is_int8_inference", ctypes.c_int),
         ("min_arch_major", ctypes.c_int), ("min_arch_minor", ctypes.c_int),
+        ("dynamic_mask", ctypes.c_int),
     ]
 
 

@@ -24,6 +24,7 @@ def _from_record(r) -> ConvAlgoDesp:
     d.mask_sparse = bool(r.mask_sparse)
     d.increment_k_first = bool(r.increment_k_first)
     d.is_int8_inference = bool(r.is_int8_inference)
+    d.dynamic_mask = bool(r.dynamic_mask)
     d.min_arch = (r.min_arch_major, r.min_arch_minor)
     return d
 

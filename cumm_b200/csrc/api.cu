@@ -185,11 +185,11 @@ cudaError_t launch_after(int level, Kern kern, dim3 grid, dim3 block, size_t sme
   return cudaLaunchKernelEx(&cfg, kern, args...);
 }
 
-template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN, bool TMA_GATHER>
+template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN, bool TMA_GATHER, int MW = 1>
 int launch_rowconv_inst(const CUtensorMap &map, const CUtensorMap &map_a, const RowConvParams &p, int grid_x,
                         int grid_y, cudaStream_t stream) {
-  using Cfg = RowConvCfg<KIND, NATOM_K, BLOCK_N, B_MN, TMA_GATHER>;
-  auto kern = rowconv_kernel<KIND, NATOM_K, BLOCK_N, B_MN, TMA_GATHER>;
+  using Cfg = RowConvCfg<KIND, NATOM_K, BLOCK_N, B_MN, TMA_GATHER, MW>;
+  auto kern = rowconv_kernel<KIND, NATOM_K, BLOCK_N, B_MN, TMA_GATHER, MW>;
   static std::atomic<uint64_t> configured{0};  // bit per device
   static std::atomic<int> regs{0};
   int dev = 0;
@@ -242,10 +242,15 @@ int plan_rowconv(int kind, int red, int nn, bool b_mn, int tile_n, int tile_k, R
 
 int launch_rowconv(const RowConvPlan &pl, const CUtensorMap &map, const CUtensorMap &map_a, bool tma_gather,
                    const RowConvParams &p, int gx, int gy, cudaStream_t s) {
+  // Kernel volumes above 32 (several mask words per row): one variant per shape, with the gather
+  // path that is the default for its row width.
 #define CB2_INST(K, A, N, M)                                                                      \
-  if (pl.kind == K && pl.natom_k == A && pl.block_n == N && pl.b_mn == M)                          \
+  if (pl.kind == K && pl.natom_k == A && pl.block_n == N && pl.b_mn == M) {                        \
+    if (p.mask_words > 1)                                                                          \
+      return launch_rowconv_inst<K, A, N, M, (A == 1), 4>(map, map_a, p, gx, gy, s);               \
     return tma_gather ? launch_rowconv_inst<K, A, N, M, true>(map, map_a, p, gx, gy, s)            \
-                      : launch_rowconv_inst<K, A, N, M, false>(map, map_a, p, gx, gy, s);
+                      : launch_rowconv_inst<K, A, N, M, false>(map, map_a, p, gx, gy, s);          \
+  }
   CB2_INST(0, 1, 64, false)
   CB2_INST(0, 1, 128, false)
   CB2_INST(0, 2, 64, false)
@@ -290,7 +295,7 @@ int run_rowconv(DeviceState *dev, RowConvParams &p, int kind, bool b_mn, int til
   // four rows); wider rows need a request per 128-byte column block, at which point the copy
   // engine's request rate, not memory, bounds a step, and 16-byte cp.async is faster.
   // CUMM_B200_GATHER forces one path for every width.
-  const bool tma_gather = getenv("CUMM_B200_GATHER") ? gather_mode() != 0 : pl.natom_k == 1;
+  const bool tma_gather = (getenv("CUMM_B200_GATHER") && p.mask_words == 1) ? gather_mode() != 0 : pl.natom_k == 1;
   CUtensorMap map_a;
   memset(&map_a, 0, sizeof(map_a));
   if (tma_gather) {
@@ -331,7 +336,7 @@ struct WgradLayout {
 };
 
 // Workspace of the weight gradient: 512-byte header (tile counts per offset), the control words,
-// fp32 partials (one per unit: at most G + kv - 1 <= G + 32), and per offset the list of the
+// fp32 partials (one per unit: at most G + kv - 1), and per offset the list of the
 // row tiles that carry it.  G = CTAs per (m, n) tile of the launch.
 void wgrad_layout(int num_sms, int max_ctas, int m_total, int n_total, long long n_rows, int kv, int tile_n,
                   WgradLayout *L) {
@@ -342,7 +347,7 @@ void wgrad_layout(int num_sms, int max_ctas, int m_total, int n_total, long long
   L->G = sms / L->gy;
   if (L->G < 1)
     L->G = 1;
-  L->slots = L->G + 32;
+  L->slots = L->G + (kv > 32 ? kv : 32);
   const int kvs = kv > 0 ? kv : 1;
   L->n_ctl = kWgradCtlBase + 4 * kvs * L->gy;
   L->off_ctl = 512;
@@ -855,14 +860,21 @@ int cb2_enumerate_gemm_desps(cb2_kernel_desp *out, int capacity) {
 
 int cb2_enumerate_conv_desps(cb2_kernel_desp *out, int capacity) {
   int n = 0;
-  // (trans_a, trans_b) per op: cumm/conv/params.py:61-69
-  for (int op = CB2_CONV_FORWARD; op <= CB2_CONV_BACKWARD_INPUT; ++op)
-    for (int tn = 64; tn <= 128; tn += 64)
-      for (int tk = 64; tk <= 128; tk += 64)
-        n = emit(make_desp(op, CB2_SHUFFLE_NONE, false, false, op == CB2_CONV_FORWARD, tn, tk), out, capacity, n);
-  for (int tn = 64; tn <= 128; tn += 64) {
-    n = emit(make_desp(CB2_CONV_BACKWARD_WEIGHT, CB2_SHUFFLE_NONE, false, true, false, tn, 128), out, capacity, n);
-    n = emit(make_desp(CB2_CONV_FORWARD, CB2_SHUFFLE_NONE, true, false, true, tn, 128), out, capacity, n);
+  // every variant twice: for kernel volumes up to 32, and (dynamic_mask) up to 128
+  for (int dyn = 0; dyn <= 1; ++dyn) {
+    auto add = [&](cb2_kernel_desp d) {
+      d.dynamic_mask = dyn;
+      n = emit(d, out, capacity, n);
+    };
+    // (trans_a, trans_b) per op: cumm/conv/params.py:61-69
+    for (int op = CB2_CONV_FORWARD; op <= CB2_CONV_BACKWARD_INPUT; ++op)
+      for (int tn = 64; tn <= 128; tn += 64)
+        for (int tk = 64; tk <= 128; tk += 64)
+          add(make_desp(op, CB2_SHUFFLE_NONE, false, false, op == CB2_CONV_FORWARD, tn, tk));
+    for (int tn = 64; tn <= 128; tn += 64) {
+      add(make_desp(CB2_CONV_BACKWARD_WEIGHT, CB2_SHUFFLE_NONE, false, true, false, tn, 128));
+      add(make_desp(CB2_CONV_FORWARD, CB2_SHUFFLE_NONE, true, false, true, tn, 128));
+    }
   }
   return n;
 }
@@ -963,6 +975,7 @@ int cb2_conv_backward_weight_static(const cb2_conv_args *a, void *stream_v) {
   p.n_total = a->C;
   p.kv = a->kernel_volume;
   p.mask_width = a->mask_width;
+  p.words = 1;
   p.rmask_words = a->mask_words;
   p.mask_filter = a->mask_filter;
   p.mode = kWgradMaskConv;
@@ -1027,6 +1040,7 @@ int cb2_gemm_run(const cb2_gemm_args *a, void *stream_v) {
     p.n_total = a->n;
     p.kv = 1;
     p.mask_width = 128;
+    p.words = 1;
     p.mask_filter = 0xffffffffu;
     p.mode = kWgradPairList;
     p.out = a->ptr_C;
@@ -1057,6 +1071,7 @@ int cb2_gemm_run(const cb2_gemm_args *a, void *stream_v) {
   p.red = a->k;
   p.nn = a->n;
   p.kv = 1;
+  p.mask_words = 1;
   p.mode = kModeGatherGemm;
   p.mask_filter = 0xffffffffu;
   p.alpha = a->alpha;
@@ -1089,8 +1104,8 @@ int cb2_conv_run(const cb2_conv_args *a, void *stream_v) {
   CB2_CHECK_RT(a->indice_ptr != nullptr, "error: indices empty");
   CB2_CHECK_RT(a->mask_ptr != nullptr, "error: mask empty");
   CB2_CHECK_RT(a->mask_argsort_ptr != nullptr, "error: mask_argsort empty");
-  CB2_CHECK_RT(a->kernel_volume >= 1 && a->kernel_volume <= 32,
-               "kernel volume %d: only the static-mask kernels (at most 32 filter offsets) are built",
+  CB2_CHECK_RT(a->kernel_volume >= 1 && a->kernel_volume <= 128,
+               "kernel volume %d: the kernels handle up to 128 filter offsets (four mask words per row)",
                a->kernel_volume);
   CB2_CHECK_RT(a->groups == 1 || a->groups == 0, "groups must be 1");
   CB2_CHECK_ARG(a->N >= 0 && a->C > 0 && a->K > 0, "bad N,C,K (%d,%d,%d)", a->N, a->C, a->K);
@@ -1108,7 +1123,7 @@ int cb2_conv_run(const cb2_conv_args *a, void *stream_v) {
   if (wgrad) {
     CB2_CHECK_RT(a->mask_width > 0 && (a->mask_width % 128 == 0 || 128 % a->mask_width == 0),
                  "error: mask_width must be positive and divide or be a multiple of %d", 128);
-    const int need_words = (a->N + a->mask_width - 1) / a->mask_width;
+    const int need_words = (a->N + a->mask_width - 1) / a->mask_width * ((a->kernel_volume + 31) / 32);
     CB2_CHECK_RT(a->mask_words >= need_words, "reduced mask has %d words, %d needed", a->mask_words, need_words);
     WgradParams p;
     memset(&p, 0, sizeof(p));
@@ -1126,7 +1141,8 @@ int cb2_conv_run(const cb2_conv_args *a, void *stream_v) {
     p.n_total = a->C;
     p.kv = a->kernel_volume;
     p.mask_width = a->mask_width;
-    p.rmask_words = a->mask_words;
+    p.words = (a->kernel_volume + 31) / 32;
+    p.rmask_words = a->mask_words / p.words;
     p.mask_filter = a->mask_filter;
     p.mode = kWgradMaskConv;
     p.out = a->ptr_C;
@@ -1155,6 +1171,7 @@ int cb2_conv_run(const cb2_conv_args *a, void *stream_v) {
   p.lda = p.red;
   p.ldo = p.nn;
   p.kv = a->kernel_volume;
+  p.mask_words = (a->kernel_volume + 31) / 32;
   p.mode = kModeMaskConv;
   p.skip_empty_tiles = dgrad ? 1 : 0;
   p.reverse_mask = (dgrad && a->reverse_mask) ? 1 : 0;

@@ -33,9 +33,9 @@ struct RowConvParams {
   const float *scale; // int8 requantisation, per output channel
   const float *bias;  //   "
   const int32_t *indices;  // [kv, n_rows] (mask-conv mode)
-  const uint32_t *mask;    // [n_rows] sorted order
+  const uint32_t *mask;    // [n_rows, mask_words] sorted order
   const int32_t *argsort;  // [n_rows]
-  uint32_t *mask_out;      // [tiles] or null
+  uint32_t *mask_out;      // [tiles, mask_words] or null
   const int32_t *a_inds;   // gather-GEMM mode (null = identity)
   const int32_t *c_inds;   //   "
   int *status;             // device status word (0 = ok)
@@ -46,6 +46,7 @@ struct RowConvParams {
   int red;                 // reduction width per filter offset
   int nn;                  // output width
   int kv;
+  int mask_words;          // 32-bit words per row mask: ceil(kv / 32), word w covers offsets 32w .. 32w+31
   int mode;
   int src_mode;
   int skip_empty_tiles;    // input-gradient: a tile whose mask is 0 is left untouched
@@ -75,7 +76,9 @@ struct RowConvParams {
 // TMA_GATHER: operand rows are fetched by the TMA unit (tile::gather4, four rows per request,
 // one warp per group) instead of 16-byte cp.async issued by 128 threads per group.  The copy
 // engine path keeps the load/store queues of the SM free for the other roles.
-template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN, bool TMA_GATHER> struct RowConvCfg {
+// MASK_WORDS: mask words per row the ring slots have room for (1: kernel volumes up to 32; 4: up
+// to 128, the reference's "dynamic mask" kernels, cumm/gemm/blockmma/mma.py:78-270).
+template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN, bool TMA_GATHER, int MASK_WORDS = 1> struct RowConvCfg {
   static constexpr int ES = KIND == 0 ? 2 : 1;            // operand element bytes
   static constexpr int OES = KIND == 0 ? 2 : 1;           // output element bytes
   static constexpr int ATOM_ELEMS = 128 / ES;             // elements per 128-byte swizzle row
@@ -87,8 +90,9 @@ template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN, bool TMA_GATHER> struct
   static constexpr int B_SLOT_BYTES = BLOCK_N * 128 * NATOM_K;
   static constexpr int OUT_ROW_BYTES = BLOCK_N * OES;
   static constexpr int STAGING_BYTES = TILE_M * OUT_ROW_BYTES;
-  static constexpr int RING = CB2_ROWCONV_RING;           // tile ring slots
-  static constexpr int RING_SLOT_INTS = 264;              // tile, mask, pad; 128 gather rows; 128 output rows
+  static constexpr int MW = MASK_WORDS;
+  static constexpr int RING = MASK_WORDS == 1 ? CB2_ROWCONV_RING : CB2_ROWCONV_RING / 2;  // tile ring slots
+  static constexpr int RING_SLOT_INTS = 136 + 128 * MASK_WORDS;  // header; 128 gather rows; 128 output rows / row masks
   // Weight slots: as many as fit (2 to 6).  A tile whose mask carries many offsets needs a new
   // weight tile every step, and with two slots the L2 latency of that load bounds the step.
   static constexpr int FIXED_BYTES = SA * A_STAGE_BYTES + STAGING_BYTES + SA * 2 * 128 * 4 + 128 * 4 +
@@ -180,18 +184,35 @@ struct RingView {
   __device__ __forceinline__ int *slot(int i) const { return slots + i * slot_ints; }
 };
 
-// OR of the neighbour masks of a tile's rows, from the raw mask words of its ring slot
-// (warp-collective).
-__device__ __forceinline__ uint32_t ring_tile_mask(const RowConvParams &p, const int *sl, int tile) {
-  if (tile < 0 || p.mode != kModeMaskConv)
-    return 1u;
+// OR of the neighbour masks of a tile's rows, word by word, from the raw mask words of its ring
+// slot (warp-collective); returns the number of filter offsets present.
+template <int MW>
+__device__ __forceinline__ int ring_tile_masks(const RowConvParams &p, const int *sl, int tile, uint32_t (&km)[MW]) {
+#pragma unroll
+  for (int w = 0; w < MW; ++w)
+    km[w] = 0u;
+  if (tile < 0 || p.mode != kModeMaskConv) {
+    km[0] = 1u;
+    return 1;
+  }
   const int lane = (int)lane_id();
-  const uint32_t m = static_cast<uint32_t>(sl[136 + lane]) | static_cast<uint32_t>(sl[136 + 32 + lane]) |
-                     static_cast<uint32_t>(sl[136 + 64 + lane]) | static_cast<uint32_t>(sl[136 + 96 + lane]);
-  uint32_t kmask = __reduce_or_sync(0xffffffffu, m) & p.mask_filter;
-  if (p.kv < 32)
-    kmask &= (1u << p.kv) - 1u;
-  return kmask;
+  int count = 0;
+#pragma unroll
+  for (int w = 0; w < MW; ++w) {
+    if (w < p.mask_words) {
+      uint32_t m = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        m |= static_cast<uint32_t>(sl[136 + (i * 32 + lane) * MW + w]);
+      m = __reduce_or_sync(0xffffffffu, m) & p.mask_filter;
+      const int left = p.kv - 32 * w;  // offsets this word covers
+      if (left < 32)
+        m &= left > 0 ? (1u << left) - 1u : 0u;
+      km[w] = m;
+      count += __popc(m);
+    }
+  }
+  return count;
 }
 
 // Walks the tiles the scheduler publishes and, inside each, the (filter offset, reduction
@@ -201,7 +222,7 @@ __device__ __forceinline__ uint32_t ring_tile_mask(const RowConvParams &p, const
 // SINGLE: the walk is run by one thread on its own (no warp-collective operation inside), which
 // is what the roles that issue from a single thread anyway use: their time per step is pure
 // instruction latency, and the collectives would only add to it.
-template <bool SINGLE, class TileFn, class StepFn>
+template <bool SINGLE, int MW, class TileFn, class StepFn>
 __device__ __forceinline__ bool walk_steps_impl(const RowConvParams &p, const RingView &rv, int kpasses,
                                                 TileFn on_tile, StepFn on_step, long long *prof_c = nullptr,
                                                 long long *prof_prev_p = nullptr) {
@@ -226,22 +247,52 @@ __device__ __forceinline__ bool walk_steps_impl(const RowConvParams &p, const Ri
     CB2_WALK_MARK(9);  // slot published
     const int *sl = rv.slot(si);
     const int tile = sl[0];
-    uint32_t kmask = static_cast<uint32_t>(sl[1]);
+    uint32_t kmask = static_cast<uint32_t>(sl[1]);  // MW == 1: the tile's mask; else: OR of its words
     const uint32_t kmask_store = kmask;
     bool cont = true;
     if (tile >= 0 && !(p.skip_empty_tiles && kmask == 0)) {
-      if (p.reverse_mask)
-        kmask = __brev(kmask) >> (32 - p.kv);
-      cont = on_tile(tile, sl, kmask_store, kmask != 0);
-      uint32_t bits = kmask;
-      bool first = true;
-      while (cont && bits) {
-        int f = __ffs(bits) - 1;
-        bits &= bits - 1;
-        for (int kp = 0; cont && kp < kpasses; ++kp) {
-          bool last = (bits == 0) && (kp == kpasses - 1);
-          cont = on_step(tile, f, kp, first, last);
-          first = false;
+      if constexpr (MW == 1) {
+        if (p.reverse_mask)
+          kmask = __brev(kmask) >> (32 - p.kv);
+        cont = on_tile(tile, sl, kmask_store, kmask != 0);
+        uint32_t bits = kmask;
+        bool first = true;
+        while (cont && bits) {
+          int f = __ffs(bits) - 1;
+          bits &= bits - 1;
+          for (int kp = 0; cont && kp < kpasses; ++kp) {
+            bool last = (bits == 0) && (kp == kpasses - 1);
+            cont = on_step(tile, f, kp, first, last);
+            first = false;
+          }
+        }
+      } else {
+        // several mask words: offsets in ascending order word by word; with reverse_mask step
+        // `pos` (weight offset pos) is taken iff the bit of offset kv - 1 - pos is set, so the
+        // words are walked from the last bit down
+        uint32_t km[MW];
+        int remaining = 0;
+#pragma unroll
+        for (int w = 0; w < MW; ++w) {
+          km[w] = static_cast<uint32_t>(sl[4 + w]);
+          remaining += __popc(km[w]);
+        }
+        cont = on_tile(tile, sl, kmask_store, remaining != 0);
+        bool first = true;
+        for (int ww = 0; cont && ww < MW; ++ww) {
+          const int w = p.reverse_mask ? MW - 1 - ww : ww;
+          uint32_t bits = km[w];
+          while (cont && bits) {
+            const int b = p.reverse_mask ? 31 - __clz(bits) : __ffs(bits) - 1;
+            bits &= ~(1u << b);
+            const int f = p.reverse_mask ? p.kv - 1 - (32 * w + b) : 32 * w + b;
+            --remaining;
+            for (int kp = 0; cont && kp < kpasses; ++kp) {
+              bool last = (remaining == 0) && (kp == kpasses - 1);
+              cont = on_step(tile, f, kp, first, last);
+              first = false;
+            }
+          }
         }
       }
     }
@@ -257,25 +308,27 @@ __device__ __forceinline__ bool walk_steps_impl(const RowConvParams &p, const Ri
   }
 }
 
-template <class TileFn, class StepFn>
+template <int MW, class TileFn, class StepFn>
 __device__ __forceinline__ bool walk_steps(const RowConvParams &p, const RingView &rv, int kpasses, TileFn on_tile,
                                            StepFn on_step) {
-  return walk_steps_impl<false>(p, rv, kpasses, on_tile, on_step);
+  return walk_steps_impl<false, MW>(p, rv, kpasses, on_tile, on_step);
 }
-template <class TileFn, class StepFn>
+template <int MW, class TileFn, class StepFn>
 __device__ __forceinline__ bool walk_steps_single(const RowConvParams &p, const RingView &rv, int kpasses,
                                                   TileFn on_tile, StepFn on_step, long long *prof_c = nullptr,
                                                   long long *prof_prev_p = nullptr) {
-  return walk_steps_impl<true>(p, rv, kpasses, on_tile, on_step, prof_c, prof_prev_p);
+  return walk_steps_impl<true, MW>(p, rv, kpasses, on_tile, on_step, prof_c, prof_prev_p);
 }
 
 // The scheduler warp: draws tiles and fetches their mask words and row numbers straight into
 // a ring slot with 4-byte cp.async.  The slot's "landed" barrier is completed by the copies
 // themselves (one asynchronous arrival per lane), so any number of tiles can be in flight and
 // each is published -- its OR-ed mask computed once, here -- as soon as ITS words are there.
-// Slot layout (ints): [0] tile (-1 = no more tiles), [1] OR-ed mask, [2] steps charged for the
-// tile (scheduler only), [8,136) rows the gather starts from, [136,264) destination rows in gather-GEMM mode /
-// raw mask words in conv mode (in conv mode the destination rows are the gather rows).
+// Slot layout (ints): [0] tile (-1 = no more tiles), [1] OR-ed mask (with several mask words per
+// row: the OR of all of them, and the OR-ed words themselves at [4, 4 + MW)), [2] steps charged
+// for the tile (scheduler only), [8,136) rows the gather starts from, from 136 on the destination
+// rows in gather-GEMM mode / the rows' raw mask words (MW per row) in conv mode (in conv mode the
+// destination rows are the gather rows).
 __device__ __forceinline__ void cp_async_4(uint32_t dst, const void *src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
@@ -288,6 +341,7 @@ __device__ __forceinline__ int first_ticket_count(int ntiles) {
   return b < 1 ? 1 : (b > CB2_ROWCONV_TICKET_BATCH ? CB2_ROWCONV_TICKET_BATCH : b);
 }
 
+template <int MW>
 __device__ __forceinline__ void scheduler_run(const RowConvParams &p, const RingView &rv, int ntiles, int kpasses,
                                               int first_base, int first_cnt) {
   constexpr int STEP_BUDGET = CB2_ROWCONV_STEP_BUDGET;  // steps a CTA may hold (drawn, not finished)
@@ -341,12 +395,20 @@ __device__ __forceinline__ void scheduler_run(const RowConvParams &p, const Ring
     while (accounted < issued &&
            mbar_test_warp(rv.landed0 + 8u * (accounted % rv.ring), (accounted / rv.ring) & 1)) {
       int *sl = rv.slot(accounted % rv.ring);
-      const uint32_t kmask = ring_tile_mask(p, sl, sl[0]);
-      const int nsteps = (sl[0] >= 0) ? max(1, __popc(kmask) * kpasses) : 1;
+      uint32_t km[MW];
+      const int offsets = ring_tile_masks<MW>(p, sl, sl[0], km);
+      const int nsteps = (sl[0] >= 0) ? max(1, offsets * kpasses) : 1;
       held_steps += nsteps - sl[2];
       __syncwarp();
       if (lane == 0) {
-        sl[1] = static_cast<int>(kmask);
+        uint32_t any = 0;
+#pragma unroll
+        for (int w = 0; w < MW; ++w) {
+          any |= km[w];
+          if (MW > 1)
+            sl[4 + w] = static_cast<int>(km[w]);
+        }
+        sl[1] = static_cast<int>(any);
         sl[2] = nsteps;
         CB2_TRACE_EVENT(6, 14, sl[0]);  // tile published
         mbar_arrive(rv.full0 + 8u * (accounted % rv.ring));
@@ -394,7 +456,10 @@ __device__ __forceinline__ void scheduler_run(const RowConvParams &p, const Ring
       if (tile >= 0 && r < p.n_rows) {
         if (conv) {
           cp_async_4(sa + (8 + j) * 4, p.argsort + r);
-          cp_async_4(sa + (136 + j) * 4, p.mask + r);
+#pragma unroll
+          for (int w = 0; w < MW; ++w)
+            if (w < p.mask_words)
+              cp_async_4(sa + (136 + j * MW + w) * 4, p.mask + (long long)r * p.mask_words + w);
         } else {
           sl[8 + j] = r;
           if (p.c_inds)
@@ -404,7 +469,9 @@ __device__ __forceinline__ void scheduler_run(const RowConvParams &p, const Ring
         }
       } else {
         sl[8 + j] = -1;
-        sl[136 + j] = conv ? 0 : -1;
+#pragma unroll
+        for (int w = 0; w < MW; ++w)
+          sl[136 + j * MW + w] = conv ? 0 : -1;
       }
     }
     cp_async_mbar_arrive_noinc(rv.landed0 + 8u * si);  // arrives when this lane's copies have landed
@@ -436,11 +503,12 @@ __device__ __forceinline__ void scheduler_run(const RowConvParams &p, const Ring
   cp_async_wait_all();
 }
 
-template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN, bool TMA_GATHER>
-__global__ void __launch_bounds__(RowConvCfg<KIND, NATOM_K, BLOCK_N, B_MN, TMA_GATHER>::THREADS, 1)
+template <int KIND, int NATOM_K, int BLOCK_N, bool B_MN, bool TMA_GATHER, int MASK_WORDS = 1>
+__global__ void __launch_bounds__(RowConvCfg<KIND, NATOM_K, BLOCK_N, B_MN, TMA_GATHER, MASK_WORDS>::THREADS, 1)
 rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_a,
                const RowConvParams p) {
-  using Cfg = RowConvCfg<KIND, NATOM_K, BLOCK_N, B_MN, TMA_GATHER>;
+  using Cfg = RowConvCfg<KIND, NATOM_K, BLOCK_N, B_MN, TMA_GATHER, MASK_WORDS>;
+  constexpr int MW = MASK_WORDS;
   extern __shared__ uint8_t smem_raw[];
   if (threadIdx.x == 0)
     CB2_TRACE_CTA(0, 0);
@@ -537,7 +605,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
     if (tile >= 0 && lane < 8) {
       const int r = tile * 128 + (lane & 3) * 32;
       if (r < p.n_rows) {
-        const void *line = (lane < 4) ? static_cast<const void *>(p.argsort + r) : static_cast<const void *>(p.mask + r);
+        const void *line = (lane < 4) ? static_cast<const void *>(p.argsort + r) : static_cast<const void *>(p.mask + (long long)r * p.mask_words);
         asm volatile("prefetch.global.L2 [%0];" ::"l"(line));
       }
     }
@@ -568,7 +636,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
     int acc_use = 0;
     bool dep_waited = false;
     CB2_PROF_BEGIN();
-    walk_steps(
+    walk_steps<MW>(
         p, rv, kpasses,
         [&](int tile, const int *sl, uint32_t kmask_store, bool has_work) -> bool {
           if (et == 0)
@@ -578,8 +646,21 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
             dep_waited = true;
           }
           const int o = (p.mode == kModeMaskConv) ? sl[8 + erow] : sl[136 + erow];  // destination row of this thread's tile row
-          if (et == 0 && p.mask_out && blockIdx.y == 0)
-            p.mask_out[tile] = kmask_store;
+          int tile_offsets = __popc(kmask_store);  // filter offsets the tile carries
+          if constexpr (MW > 1) {
+            tile_offsets = 0;
+#pragma unroll
+            for (int w = 0; w < MW; ++w)
+              tile_offsets += __popc(static_cast<uint32_t>(sl[4 + w]));
+          }
+          if (et == 0 && p.mask_out && blockIdx.y == 0) {
+            if constexpr (MW == 1) {
+              p.mask_out[tile] = kmask_store;
+            } else {
+              for (int w = 0; w < p.mask_words; ++w)
+                p.mask_out[(long long)tile * p.mask_words + w] = static_cast<uint32_t>(sl[4 + w]);
+            }
+          }
           const int buf = acc_use % Cfg::NUM_ACC;
           if (has_work) {
             if (et == 0) {
@@ -603,7 +684,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
           const uint32_t trow = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
                                 static_cast<uint32_t>(buf * BLOCK_N);
           const bool use_src = (p.src_mode != kSrcNone) && (p.beta != 0.f);
-          const bool small_acc = KIND == 1 && __popc(kmask_store) * kpasses * Cfg::KRED <= 255;
+          const bool small_acc = KIND == 1 && tile_offsets * kpasses * Cfg::KRED <= 255;
           // fast path: out = cvt(acc); everything else goes through the general epilogue
           const bool plain = !use_src && p.act_type == 0 && p.alpha == 1.f;
           constexpr int ROUNDS = COLS_PER_HALF / 32;
@@ -803,7 +884,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
                                      : make_smem_desc(sbase + Cfg::OFF_B, 16, 1024);
     CB2_PROF_BEGIN();
     if (lane == 0) {
-    walk_steps_single(
+    walk_steps_single<MW>(
         p, rv, kpasses,
         [&](int, const int *, uint32_t, bool) -> bool {
           CB2_PROF_MARK(7);  // previous slot released, this tile's slot read
@@ -901,7 +982,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
     if (lane == 0) {
     tma_prefetch_desc(&tmap_b);
     grid_dep_wait();
-    walk_steps_single(
+    walk_steps_single<MW>(
         p, rv, kpasses, [&](int, const int *, uint32_t, bool) -> bool { return true; },
         [&](int tile, int f, int kp, bool, bool) -> bool {
           int ok = 1;
@@ -941,7 +1022,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
     __syncwarp();
   } else if (warp == Cfg::SCHED_WARP) {
     // ======================= scheduler: draws tiles, publishes their masks and row numbers
-    scheduler_run(p, rv, ntiles, kpasses, early_base, early_cnt);
+    scheduler_run<MW>(p, rv, ntiles, kpasses, early_base, early_cnt);
   } else {
     // ======================= operand-row gather: group g owns stage g
     if constexpr (TMA_GATHER) {
@@ -969,7 +1050,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
       bool dep_waited = false;
       int step = 0;
       int o[4] = {-1, -1, -1, -1};
-      walk_steps(
+      walk_steps<MW>(
           p, rv, kpasses,
           [&](int tile, const int *sl, uint32_t, bool) -> bool {
             const int4 v = *reinterpret_cast<const int4 *>(sl + 8 + lane * 4);
@@ -1051,7 +1132,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
       for (int r = 0; r < RPT; ++r)
         o[r] = -1;
       const uint8_t *a_bytes = reinterpret_cast<const uint8_t *>(p.a);
-      walk_steps(
+      walk_steps<MW>(
           p, rv, kpasses,
           [&](int tile, const int *sl, uint32_t, bool) -> bool {
             // the rows this thread's gathers start from (sort index, or the row itself)

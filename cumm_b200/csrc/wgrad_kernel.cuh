@@ -34,15 +34,16 @@ struct WgradParams {
   const void *dout;        // A rows [*, m_total]  (fp16)
   const void *x;           // B rows [*, n_total]  (fp16)
   const int32_t *indices;  // [kv, n_rows]
-  const uint32_t *rmask;   // reduced masks, one word per mask_width sorted rows
+  const uint32_t *rmask;   // reduced masks: `words` words (32 filter offsets each) per mask_width sorted rows
   const int32_t *argsort;  // [n_rows]
   const int32_t *a_inds;   // pair-list mode
   const int32_t *b_inds;   //   "
   float *partials;         // workspace: [unit][m_tile][n_tile][128 x BLOCK_N] fp32
-  int *ctl;                // workspace, zero between calls: [0] CTAs that have left; [8 + 2 by] offsets summed and
-                           // [9 + 2 by] bit mask of the ready offsets of output tile by; from kWgradCtlBase
-                           // on, four ints per (f, by): units arrived, next slice to hand out, slices summed
-  int *sched;              // workspace header: [0,32) number of row tiles carrying offset f
+  int *ctl;                // workspace, zero between calls: [0] CTAs that have left; [8 + 8 by] offsets summed and
+                           // [9 + 8 by, 13 + 8 by) bit masks of the ready offsets of output tile by; from
+                           // kWgradCtlBase on, four ints per (f, by): units arrived, next slice to hand
+                           // out, slices summed
+  int *sched;              // workspace header: [0,128) number of row tiles carrying offset f
   const int *lists;        // workspace: per offset, the ordered list of those tiles
   int list_stride;         // ints between two offsets' lists
   int *status;
@@ -58,7 +59,8 @@ struct WgradParams {
   int m_total, n_total;
   int kv;
   int mask_width;
-  int rmask_words;
+  int words;               // mask words per chunk of mask_width rows: ceil(kv / 32)
+  int rmask_words;         // chunks the reduced-mask array holds
   uint32_t mask_filter;
   int mode;
 };
@@ -75,18 +77,22 @@ template <int BLOCK_N, int GATHER> struct WgradCfg {
   static constexpr int OFF_ROWIDX = SA * STAGE_BYTES;       // SA x 2 buffers x 2 operands x 128 ints
   static constexpr int OFF_SCHED = OFF_ROWIDX + SA * 2 * 2 * 128 * 4;  // this CTA's units, then units per offset
   static constexpr int TILE_CAP = 2048;                      // tiles of one CTA staged in shared memory
-  static constexpr int OFF_TILES = OFF_SCHED + 256 * 4;
+  static constexpr int OFF_TILES = OFF_SCHED + 1024 * 4;
   static constexpr int OFF_BARS = OFF_TILES + TILE_CAP * 4;
   static constexpr int OFF_MISC = OFF_BARS + 16 * 8;
   static constexpr int SMEM_BYTES = OFF_MISC + 64 + 1024;
 };
 
-// OR of the reduced-mask words that cover sorted rows [128*tile, 128*tile + 128).
-__device__ __forceinline__ uint32_t wgrad_tile_mask(const WgradParams &p, int tile) {
+// Does row tile `tile` (sorted rows [128*tile, 128*tile + 128)) carry filter offset f?  OR of the
+// reduced-mask words of offset f's group of 32 over the chunks that cover the tile.
+__device__ __forceinline__ bool wgrad_tile_has(const WgradParams &p, int tile, int f) {
   if (p.mode != kWgradMaskConv)
-    return 1u;
-  if (p.mask_width == 128)  // the usual case: one word per tile
-    return tile < p.rmask_words ? (__ldg(p.rmask + tile) & p.mask_filter) : 0u;
+    return true;
+  if (!((p.mask_filter >> (f & 31)) & 1u))
+    return false;
+  const uint32_t *col = p.rmask + (f >> 5);
+  if (p.mask_width == 128)  // the usual case: one chunk per tile
+    return tile < p.rmask_words && ((__ldg(col + (long long)tile * p.words) >> (f & 31)) & 1u);
   const int r0 = tile * 128;
   int r1 = r0 + 127;
   if (r1 >= p.n_rows)
@@ -95,8 +101,8 @@ __device__ __forceinline__ uint32_t wgrad_tile_mask(const WgradParams &p, int ti
   uint32_t v = 0;
   for (int w = w0; w <= w1; ++w)
     if (w < p.rmask_words)
-      v |= __ldg(p.rmask + w);
-  return v & p.mask_filter;
+      v |= __ldg(col + (long long)w * p.words);
+  return (v >> (f & 31)) & 1u;
 }
 
 // ---------------------------------------------------------------- schedule
@@ -115,38 +121,48 @@ __device__ __forceinline__ uint32_t wgrad_tile_mask(const WgradParams &p, int ti
 //   sched[f]                      tiles carrying offset f
 //   lists[f * list_stride + k]    the k-th of them
 
-// For lane f of one warp, given cnt_f: P = steps before offset f, T = all steps, c_first =
-// CTA holding step P, S = units of f, U = units before f.
-__device__ __forceinline__ void wgrad_plan_warp(int cnt, int G, int &P, int &T, int &c_first, int &S, int &U) {
+// One warp plans for up to 128 offsets: lane l owns offsets 4l .. 4l+3.
+constexpr int kWgradMaxOffsets = 128;
+// Exclusive prefix sum, in offset order, of four values per lane; `total` = the sum of all.
+__device__ __forceinline__ void wgrad_scan4(const int (&v)[4], int (&excl)[4], int &total) {
   const int lane = (int)lane_id();
-  int incl = cnt;
+  const int mine = v[0] + v[1] + v[2] + v[3];
+  int incl = mine;
 #pragma unroll
   for (int d = 1; d < 32; d <<= 1) {
-    const int v = __shfl_up_sync(0xffffffffu, incl, d);
+    const int t = __shfl_up_sync(0xffffffffu, incl, d);
     if (lane >= d)
-      incl += v;
+      incl += t;
   }
-  T = __shfl_sync(0xffffffffu, incl, 31);
-  P = incl - cnt;
+  total = __shfl_sync(0xffffffffu, incl, 31);
+  int run = incl - mine;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    excl[j] = run;
+    run += v[j];
+  }
+}
+// Given the tile counts of this lane's offsets: P = steps before each offset, T = all steps,
+// c_first = CTA holding step P, S = units of the offset, U = units before it.
+__device__ __forceinline__ void wgrad_plan_warp(const int (&cnt)[4], int G, int (&P)[4], int &T, int (&c_first)[4],
+                                                int (&S)[4], int (&U)[4]) {
+  wgrad_scan4(cnt, P, T);
   // the CTA holding step x is the largest c with c*T/G <= x, i.e. ceil((x+1)*G/T) - 1
   auto chunk_of = [&](int x) -> int {
     const int c = (int)((((long long)x + 1) * G + T - 1) / T) - 1;
     return c < G - 1 ? c : G - 1;
   };
-  c_first = 0;
-  S = 0;
-  if (cnt > 0) {
-    c_first = chunk_of(P);
-    S = chunk_of(P + cnt - 1) - c_first + 1;
-  }
-  int incl_s = S;
 #pragma unroll
-  for (int d = 1; d < 32; d <<= 1) {
-    const int v = __shfl_up_sync(0xffffffffu, incl_s, d);
-    if (lane >= d)
-      incl_s += v;
+  for (int j = 0; j < 4; ++j) {
+    c_first[j] = 0;
+    S[j] = 0;
+    if (cnt[j] > 0) {
+      c_first[j] = chunk_of(P[j]);
+      S[j] = chunk_of(P[j] + cnt[j] - 1) - c_first[j] + 1;
+    }
   }
-  U = incl_s - S;
+  int total_units;
+  wgrad_scan4(S, U, total_units);
 }
 
 // One block per filter offset: count and list the tiles that carry it.  Warp w owns a
@@ -169,7 +185,7 @@ __global__ void __launch_bounds__(1024) wgrad_plan_kernel(const WgradParams p, i
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       const int t = base + (wid * K + k) * 32 + lane;
-      on[k] = t < ntiles && ((wgrad_tile_mask(p, t) >> f) & 1u);
+      on[k] = t < ntiles && wgrad_tile_has(p, t, f);
     }
     int mine = 0;
 #pragma unroll
@@ -206,51 +222,57 @@ __global__ void __launch_bounds__(1024) wgrad_plan_kernel(const WgradParams p, i
 // The unit number is global: the units of an offset are consecutive.  After the unit records:
 // s_plan[kWgradPlanUnits + f] = units of offset f over all CTAs, s_plan[kWgradPlanFirst + f] = the
 // first of them.
-constexpr int kWgradPlanUnits = 8 + 5 * 32;
-constexpr int kWgradPlanFirst = kWgradPlanUnits + 32;
-constexpr int kWgradPlanInts = kWgradPlanFirst + 32;
+constexpr int kWgradPlanUnits = 8 + 5 * kWgradMaxOffsets;
+constexpr int kWgradPlanFirst = kWgradPlanUnits + kWgradMaxOffsets;
+constexpr int kWgradPlanInts = kWgradPlanFirst + kWgradMaxOffsets;  // 904 <= the 1024 reserved
 constexpr int kWgradMaxOutTiles = 128; // (m, n) tiles of the weight gradient a launch can have
-constexpr int kWgradCtlBase = 8 + 2 * kWgradMaxOutTiles;  // first per-(offset, tile) control word
+constexpr int kWgradCtlBase = 8 + 8 * kWgradMaxOutTiles;  // first per-(offset, tile) control word
 constexpr int kWgradLingerPolls = 256; // a CTA with nothing to do looks for ready slices this often, then leaves
 template <int TILE_CAP>
 __device__ __forceinline__ void wgrad_load_plan(const WgradParams &p, const int *lists, int list_stride, int *s_plan,
                                                 int *s_tiles) {
   const int G = gridDim.x, c = blockIdx.x;
   if (threadIdx.x < 32) {
-    const int f = threadIdx.x;
-    const int cnt = (f < p.kv) ? __ldg(p.sched + f) : 0;
-    int P, T, c_first, S, U;
-    wgrad_plan_warp(cnt, G, P, T, c_first, S, U);
-    s_plan[kWgradPlanUnits + f] = S;
-    s_plan[kWgradPlanFirst + f] = U;
-    const int b0 = (int)(((long long)c * T) / G), b1 = (int)(((long long)(c + 1) * T) / G);
-    const bool has = cnt > 0 && c >= c_first && c < c_first + S;
-    int k0 = 0, k1 = 0;
-    if (has) {
-      k0 = max(b0, P) - P;
-      k1 = min(b1, P + cnt) - P;
-      if (k1 < k0)
-        k1 = k0;
-    }
-    const uint32_t bal = __ballot_sync(0xffffffffu, has);
-    int len_incl = k1 - k0;
+    const int lane = threadIdx.x;
+    int cnt[4], P[4], c_first[4], S[4], U[4], T;
 #pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      const int v = __shfl_up_sync(0xffffffffu, len_incl, d);
-      if (f >= d)
-        len_incl += v;
+    for (int j = 0; j < 4; ++j) {
+      const int f = 4 * lane + j;
+      cnt[j] = (f < p.kv) ? __ldg(p.sched + f) : 0;
     }
-    const int total_len = __shfl_sync(0xffffffffu, len_incl, 31);
-    if (has) {
-      int *e = s_plan + 8 + 5 * __popc(bal & ((1u << f) - 1u));
-      e[0] = f;
-      e[1] = k0;
-      e[2] = k1;
-      e[3] = U + (c - c_first);
-      e[4] = len_incl - (k1 - k0);
+    wgrad_plan_warp(cnt, G, P, T, c_first, S, U);
+    const int b0 = (int)(((long long)c * T) / G), b1 = (int)(((long long)(c + 1) * T) / G);
+    int has[4], k0[4], k1[4], len[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int f = 4 * lane + j;
+      s_plan[kWgradPlanUnits + f] = S[j];
+      s_plan[kWgradPlanFirst + f] = U[j];
+      has[j] = (cnt[j] > 0 && c >= c_first[j] && c < c_first[j] + S[j]) ? 1 : 0;
+      k0[j] = k1[j] = 0;
+      if (has[j]) {
+        k0[j] = max(b0, P[j]) - P[j];
+        k1[j] = min(b1, P[j] + cnt[j]) - P[j];
+        if (k1[j] < k0[j])
+          k1[j] = k0[j];
+      }
+      len[j] = k1[j] - k0[j];
     }
-    if (f == 0) {
-      s_plan[0] = __popc(bal);
+    int slot[4], toff[4], n_units, total_len;
+    wgrad_scan4(has, slot, n_units);
+    wgrad_scan4(len, toff, total_len);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (has[j]) {
+        int *e = s_plan + 8 + 5 * slot[j];
+        e[0] = 4 * lane + j;
+        e[1] = k0[j];
+        e[2] = k1[j];
+        e[3] = U[j] + (c - c_first[j]);
+        e[4] = toff[j];
+      }
+    if (lane == 0) {
+      s_plan[0] = n_units;
       s_plan[1] = total_len <= TILE_CAP ? 1 : 0;  // tiles are staged in shared memory
     }
   }
@@ -404,7 +426,7 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
     for (int f = 0; f < p.kv; ++f)
       n_active += s_units[f] > 0 ? 1 : 0;
     for (int f = blockIdx.x; f < p.kv; f += gridDim.x)
-      if (((p.mask_filter >> f) & 1u) && s_units[f] == 0)
+      if ((p.mode != kWgradMaskConv || ((p.mask_filter >> (f & 31)) & 1u)) && s_units[f] == 0)
         for (int q = 0; q < kSlices; ++q)
           write_out(f, et, q, make_float4(0.f, 0.f, 0.f, 0.f));
     int acc_use = 0;
@@ -455,7 +477,7 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
           if (et == 0) {
             if (atomicAdd(ctl_of(f), 1) == s_units[f] - 1) {
               __threadfence();
-              atomicOr(p.ctl + 9 + 2 * blockIdx.y, 1 << f);  // ready: every partial of f is in place
+              atomicOr(p.ctl + 9 + 8 * blockIdx.y + (f >> 5), 1 << (f & 31));  // ready: every partial of f is in place
             }
             CB2_TRACE_EVENT(4, 9, u);  // partial written
           }
@@ -465,26 +487,30 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
     // or nothing has been on offer for a while (whoever makes an offset ready finds its slices on
     // offer in this very loop, so every slice is taken by somebody)
     int polls = 0;
-    uint32_t handed_out = 0;  // offsets whose slices are known to be all taken (thread 0)
+    uint32_t handed_out[4] = {0u, 0u, 0u, 0u};  // offsets whose slices are known to be all taken (thread 0)
     while (walk_ok) {
       if (et == 0) {
         int job = -1;
-        uint32_t open = static_cast<uint32_t>(ld_acquire_gpu(p.ctl + 9 + 2 * blockIdx.y)) & ~handed_out;
         // start at a different offset in every CTA so that the CTAs spread over the ready offsets
-        const int rot = blockIdx.x % p.kv;
-        open = rot ? ((open >> rot) | (open << (32 - rot))) : open;
-        while (open && job < 0) {
-          const int k = __ffs(open) - 1;
-          open &= open - 1;
-          const int f = (k + rot) & 31;
-          const int sl = atomicAdd(ctl_of(f) + 1, 1);
-          if (sl < kSlices)
-            job = f * kSlices + sl;
-          else
-            handed_out |= 1u << f;
+        const int rot = blockIdx.x & 31;
+        for (int ww = 0; ww < p.words && job < 0; ++ww) {
+          const int w = (ww + (blockIdx.x >> 5)) % p.words;
+          uint32_t open = static_cast<uint32_t>(ld_acquire_gpu(p.ctl + 9 + 8 * blockIdx.y + w)) & ~handed_out[w];
+          open = rot ? ((open >> rot) | (open << (32 - rot))) : open;
+          while (open && job < 0) {
+            const int k = __ffs(open) - 1;
+            open &= open - 1;
+            const int b = (k + rot) & 31;
+            const int f = 32 * w + b;
+            const int sl = atomicAdd(ctl_of(f) + 1, 1);
+            if (sl < kSlices)
+              job = f * kSlices + sl;
+            else
+              handed_out[w] |= 1u << b;
+          }
         }
         if (job < 0) {
-          const bool all_summed = ld_acquire_gpu(p.ctl + 8 + 2 * blockIdx.y) >= n_active;
+          const bool all_summed = ld_acquire_gpu(p.ctl + 8 + 8 * blockIdx.y) >= n_active;
           if (all_summed || ++polls > kWgradLingerPolls)
             job = -2;
           else
@@ -516,7 +542,7 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
       named_bar_sync(1, 128);
       if (et == 0) {
         if (atomicAdd(ctl_of(f) + 2, 1) == kSlices - 1)
-          atomicAdd(p.ctl + 8 + 2 * blockIdx.y, 1);
+          atomicAdd(p.ctl + 8 + 8 * blockIdx.y, 1);
       }
     }
     // the last CTA to leave puts every control word back to zero for the next call
@@ -618,9 +644,9 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
           int ia = -1, ib = -1;
           if (r < p.n_rows) {
             if (p.mode == kWgradMaskConv) {
-              const uint32_t word = __ldg(p.rmask + r / p.mask_width);
+              const uint32_t word = __ldg(p.rmask + (long long)(r / p.mask_width) * p.words + (f >> 5));
               const int o = __ldg(p.argsort + r);  // independent of `word`: both loads are in flight together
-              if ((word >> f) & 1u) {
+              if ((word >> (f & 31)) & 1u) {
                 ib = __ldg(p.indices + (long long)f * p.n_rows + o);
                 ia = (ib >= 0) ? o : -1;  // a zero B row makes the A row irrelevant
               }

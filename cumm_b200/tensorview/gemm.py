@@ -658,6 +658,14 @@ def _conv_args(params: ConvParams) -> _lib.ConvArgs:
     if indices.ndim != 2 or indices.dim(0) != kv:
         raise RuntimeError(f"indices shape {indices.shape} does not match [{kv}, -1]")
     N = indices.dim(1)
+    # Kernel volumes above 32: ceil(kv / 32) mask words per row / per reduced-mask chunk (the
+    # reference's dynamic-mask kernels, cumm/gemm/blockmma/mma.py:78-270, which compute the same
+    # count from the kernel volume, cumm/conv/kernel.py:829,935).
+    mask_words = _div_up(kv, 32)
+    if kv > 128:
+        raise RuntimeError(f"kernel volume {kv}: the kernels handle up to 128 filter offsets")
+    if kv > 32 and not desp.dynamic_mask:
+        raise RuntimeError(f"kernel volume {kv} needs a dynamic-mask descriptor (ConvAlgoDesp.dynamic_mask)")
     if op in (ConvOpType.BackwardWeight, ConvOpType.Forward):
         if N != output.dim(0):
             raise RuntimeError("error: indices.dim(1) must equal output.dim(0)")
@@ -710,8 +718,10 @@ def _conv_args(params: ConvParams) -> _lib.ConvArgs:
     args.rows_A = a_t.dim(0)
     args.rows_B = b_t.dim(0)
     args.mask_words = mask.size()
+    if op != ConvOpType.BackwardWeight and mask.size() < N * mask_words:
+        raise RuntimeError(f"mask has {mask.size()} words, {N * mask_words} needed ({mask_words} per row)")
     if op == ConvOpType.Forward and mask_output is not None:
-        if mask_output.size() < _div_up(N, 128):
+        if mask_output.size() < _div_up(N, 128) * mask_words:
             raise RuntimeError("mask_output is too small")
     # The descriptor selects the kernel: tile_shape = [rows, columns, reduction] of one CTA tile
     # (for backward weight the reduction runs over rows and is tied to mask_width).

@@ -29,7 +29,7 @@ class ConvTables:
     n_out: int
     kv: int
     indices: np.ndarray        # [kv, n_out] int32, -1 = no pair   (forward direction)
-    mask: np.ndarray           # [n_out] uint32, sorted ascending
+    mask: np.ndarray           # [n_out] uint32, sorted ascending ([n_out, words] when kv > 32)
     mask_argsort: np.ndarray   # [n_out] int32
     indices_bwd: np.ndarray    # [kv, n_in] int32                  (input-gradient direction)
     mask_bwd: np.ndarray       # [n_in] uint32, sorted
@@ -87,15 +87,24 @@ def neighbour_table(in_coords, out_coords, grid, ksize, stride, pad, dil) -> np.
 
 
 def masks_from_indices(indices: np.ndarray) -> np.ndarray:
+    """Per-row neighbour masks: [n] for kernel volumes up to 32, else [n, ceil(kv / 32)] with
+    word w covering offsets 32w .. 32w+31 (the layout of the reference's dynamic-mask kernels,
+    cumm/gemm/blockmma/mma.py:78-270)."""
     kv = indices.shape[0]
-    mask = np.zeros(indices.shape[1], np.uint32)
-    for f in range(min(kv, 32)):
-        mask |= (indices[f] >= 0).astype(np.uint32) << np.uint32(f)
-    return mask
+    words = (kv + 31) // 32
+    mask = np.zeros((indices.shape[1], words), np.uint32)
+    for f in range(kv):
+        mask[:, f >> 5] |= (indices[f] >= 0).astype(np.uint32) << np.uint32(f & 31)
+    return mask[:, 0].copy() if words == 1 else mask
 
 
 def sort_masks(mask: np.ndarray):
-    order = np.argsort(mask, kind="stable").astype(np.int32)
+    """Stable ascending sort; masks of several words compare as one integer whose most
+    significant word is the last one."""
+    if mask.ndim == 2:
+        order = np.lexsort(tuple(mask[:, w] for w in range(mask.shape[1]))).astype(np.int32)
+    else:
+        order = np.argsort(mask, kind="stable").astype(np.int32)
     return np.ascontiguousarray(mask[order]), order
 
 

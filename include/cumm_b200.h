@@ -117,6 +117,10 @@ typedef struct cb2_gemm_args {
  * indice_ptr [kv, N] int32 in original row order, -1 = no neighbour; mask_ptr: forward /
  * backward input: per-row masks in sorted order [N]; backward weight: reduced masks, one
  * word per mask_width sorted rows (the forward pass's mask_out_ptr).
+ * Kernel volumes from 33 to 128 (the reference's dynamic-mask kernels, cumm/gemm/blockmma/mma.py:78-270):
+ * W = ceil(kv / 32) words per row, [N, W], word w covering offsets 32w .. 32w+31; mask_out_ptr
+ * [ceil(N / 128), W]; reduced masks [chunks, W]; mask_filter applies to every word; with
+ * reverse_mask, weight offset p is visited iff the mask bit of offset kv - 1 - p is set.
  * ptr_D: source rows for beta (default C); with d_is_bias a length-(output width) vector.
  * int8 inference (dtype_a == i8, forward only): scale_pointer / bias_pointer fp32 per
  * output channel; ptr_D (if beta != 0) are int8 rows added after scaling
@@ -311,6 +315,8 @@ typedef struct cb2_kernel_desp {
   int split_k_serial;
   int mask_sparse, increment_k_first, is_int8_inference;
   int min_arch_major, min_arch_minor;
+  int dynamic_mask; /* conv: the variant for kernel volumes above 32 (several mask words per row, up to 128
+                       offsets; name suffix D, params.h:191-224); it also runs smaller volumes */
 } cb2_kernel_desp;
 
 int cb2_enumerate_gemm_desps(cb2_kernel_desp *out, int capacity);

@@ -114,7 +114,8 @@ def build_pairs(in_coords, out_coords, grid, ksize, stride, pad, dil):
     kv = int(np.prod(ksize))
     n_in, n_out = len(in_coords), len(out_coords)
     indices = np.empty((kv, n_out), np.int32)
-    mask = np.empty((n_out,), np.uint32)
+    words = (kv + 31) // 32  # kernel volumes above 32: several mask words per row
+    mask = np.empty((n_out,) if words == 1 else (n_out, words), np.uint32)
     arr = lambda v: np.ascontiguousarray(v, np.int32)
     g, k, s, p, d = arr(grid), arr(ksize), arr(stride), arr(pad), arr(dil)
     rc = lib().orc_build_pairs(n_in, _p(in_coords, c_i32p), n_out, _p(out_coords, c_i32p),
@@ -154,8 +155,12 @@ def regular_out_coords(in_coords, grid, ksize, stride, pad, dil):
 
 
 def sort_masks(mask):
-    """Stable ascending sort of the per-row masks; returns (sorted mask, argsort)."""
-    order = np.argsort(mask, kind="stable").astype(np.int32)
+    """Stable ascending sort of the per-row masks; returns (sorted mask, argsort).  Masks of
+    several words compare as one integer whose most significant word is the last one."""
+    if mask.ndim == 2:
+        order = np.lexsort(tuple(mask[:, w] for w in range(mask.shape[1]))).astype(np.int32)
+    else:
+        order = np.argsort(mask, kind="stable").astype(np.int32)
     return np.ascontiguousarray(mask[order]), order
 
 

@@ -248,13 +248,30 @@ void orc_gemm_shuffle_ab_f16(int m, int n, int kk, const uint16_t *a, int64_t ld
  * `nn` are the reduction and output widths.  tile_m is the number of sorted rows that
  * share one OR-ed mask.  mask is in sorted order, indices in original order.
  * d (may be NULL): source rows (same layout as out) or, when d_is_bias, a length-nn vector.
+ *
+ * Kernel volumes above 32 (cumm/gemm/blockmma/mma.py:78-270, the dynamic mask loader): a row's
+ * mask is `words` = ceil(kv / 32) consecutive 32-bit words, word w covering offsets 32w..32w+31;
+ * each OR-ed word is ANDed with mask_filter; mask_out[tile * words + w]; the input gradient
+ * leaves a tile untouched when all words are zero, and reverse_mask makes step `pos` (weight
+ * offset pos) depend on the mask bit of offset kv - 1 - pos.
  * ---------------------------------------------------------------------------------- */
-static uint32_t orc_brev(uint32_t v) {
-  uint32_t r = 0;
-  for (int i = 0; i < 32; ++i)
-    if (v & (1u << i))
-      r |= 1u << (31 - i);
-  return r;
+/* OR of the mask words of the rows of a tile, filtered; returns whether any bit is left. */
+static int orc_tile_masks(const uint32_t *mask, int r0, int rows, int words, uint32_t mask_filter,
+                          uint32_t *kmask) {
+  int any = 0;
+  for (int w = 0; w < words; ++w) {
+    uint32_t m = 0;
+    for (int r = 0; r < rows; ++r)
+      m |= mask[(size_t)(r0 + r) * words + w];
+    kmask[w] = m & mask_filter;
+    any |= kmask[w] != 0;
+  }
+  return any;
+}
+/* Is step `pos` (weight offset pos) of a tile taken?  With reverse, the bit of offset kv-1-pos. */
+static int orc_step_on(const uint32_t *kmask, int kv, int pos, int reverse) {
+  int f = reverse ? kv - 1 - pos : pos;
+  return (kmask[f >> 5] >> (f & 31)) & 1u;
 }
 
 void orc_mask_igemm_f16(int is_dgrad, int N, int a_rows, int C_in, int K_out, int kv,
@@ -265,6 +282,8 @@ void orc_mask_igemm_f16(int is_dgrad, int N, int a_rows, int C_in, int K_out, in
                         int tile_m, float alpha, float beta, int act_type,
                         float act_alpha) {
   (void)a_rows;
+  const int words = (kv + 31) / 32;
+  uint32_t kmask[8];
   int red = is_dgrad ? K_out : C_in;
   int nn = is_dgrad ? C_in : K_out;
   /* weights as float, laid out [f][n][red] for contiguous dot products */
@@ -281,22 +300,17 @@ void orc_mask_igemm_f16(int is_dgrad, int N, int a_rows, int C_in, int K_out, in
   for (int t = 0; t < tiles; ++t) {
     int r0 = t * tile_m;
     int rows = N - r0 < tile_m ? N - r0 : tile_m;
-    uint32_t kmask = 0;
-    for (int r = 0; r < rows; ++r)
-      kmask |= mask[r0 + r];
-    kmask &= mask_filter;
+    int any = orc_tile_masks(mask, r0, rows, words, mask_filter, kmask);
     if (!is_dgrad) {
       if (mask_out)
-        mask_out[t] = kmask;
-    } else {
-      if (kmask == 0)
-        continue; /* tile left untouched */
-      if (reverse_mask)
-        kmask = orc_brev(kmask) >> (32 - kv);
+        for (int w = 0; w < words; ++w)
+          mask_out[(size_t)t * words + w] = kmask[w];
+    } else if (!any) {
+      continue; /* tile left untouched */
     }
     memset(acc, 0, sizeof(float) * (size_t)tile_m * nn);
     for (int f = 0; f < kv; ++f) {
-      if (!((kmask >> f) & 1u))
+      if (!orc_step_on(kmask, kv, f, is_dgrad && reverse_mask))
         continue;
       const float *wff = wf + (size_t)f * nn * red;
       for (int r = 0; r < rows; ++r) {
@@ -359,12 +373,13 @@ void orc_mask_igemm_wgrad_f16(int N, int C_in, int K_out, int kv, const uint16_t
   float *acc = (float *)malloc(sizeof(float) * (size_t)K_out * C_in);
   float *dor = (float *)malloc(sizeof(float) * K_out);
   float *xr = (float *)malloc(sizeof(float) * C_in);
+  const int words = (kv + 31) / 32; /* reduced_mask[chunk * words + f / 32], filter bit f % 32 */
   for (int f = 0; f < kv; ++f) {
-    if (!((mask_filter >> f) & 1u))
+    if (!((mask_filter >> (f & 31)) & 1u))
       continue;
     memset(acc, 0, sizeof(float) * (size_t)K_out * C_in);
     for (int r = 0; r < N; ++r) {
-      if (!((reduced_mask[r / mask_width] >> f) & 1u))
+      if (!((reduced_mask[(size_t)(r / mask_width) * words + (f >> 5)] >> (f & 31)) & 1u))
         continue;
       int o = mask_argsort[r];
       int i = indices[(size_t)f * N + o];
@@ -418,18 +433,18 @@ void orc_mask_igemm_s8(int N, int C_in, int K_out, int kv, const int8_t *x, cons
                        int tile_m, float beta, int act_type, float act_alpha) {
   int32_t *acc = (int32_t *)malloc(sizeof(int32_t) * (size_t)tile_m * K_out);
   int tiles = (N + tile_m - 1) / tile_m;
+  const int words = (kv + 31) / 32;
+  uint32_t kmask[8];
   for (int t = 0; t < tiles; ++t) {
     int r0 = t * tile_m;
     int rows = N - r0 < tile_m ? N - r0 : tile_m;
-    uint32_t kmask = 0;
-    for (int r = 0; r < rows; ++r)
-      kmask |= mask[r0 + r];
-    kmask &= mask_filter;
+    orc_tile_masks(mask, r0, rows, words, mask_filter, kmask);
     if (mask_out)
-      mask_out[t] = kmask;
+      for (int w = 0; w < words; ++w)
+        mask_out[(size_t)t * words + w] = kmask[w];
     memset(acc, 0, sizeof(int32_t) * (size_t)tile_m * K_out);
     for (int f = 0; f < kv; ++f) {
-      if (!((kmask >> f) & 1u))
+      if (!orc_step_on(kmask, kv, f, 0))
         continue;
       for (int r = 0; r < rows; ++r) {
         int o = mask_argsort[r0 + r];
@@ -574,7 +589,9 @@ int orc_build_pairs(int n_in, const int32_t *in_coords, int n_out, const int32_t
     orc_hash_put(&h, key, i);
   }
   int kv = ksize[0] * ksize[1] * ksize[2];
-  (void)kv;
+  const int words = (kv + 31) / 32; /* mask words per output row */
+  if (words > 1)
+    memset(mask, 0, sizeof(uint32_t) * (size_t)n_out * words);
   for (int o = 0; o < n_out; ++o) {
     const int32_t *c = out_coords + 4 * (size_t)o;
     uint32_t mk = 0;
@@ -591,10 +608,17 @@ int orc_build_pairs(int n_in, const int32_t *in_coords, int n_out, const int32_t
             v = orc_hash_get(&h, key);
           }
           indices[(size_t)f * n_out + o] = v;
-          if (v >= 0 && f < 32)
-            mk |= 1u << f;
+          if (v >= 0) {
+            if (words == 1) {
+              if (f < 32)
+                mk |= 1u << f;
+            } else {
+              mask[(size_t)o * words + (f >> 5)] |= 1u << (f & 31);
+            }
+          }
         }
-    mask[o] = mk;
+    if (words == 1)
+      mask[o] = mk;
   }
   orc_hash_free(&h);
   return 0;

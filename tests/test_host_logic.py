@@ -249,19 +249,19 @@ def test_kernel_table_comes_from_the_library():
     for fn in (L.cb2_enumerate_gemm_desps, L.cb2_enumerate_conv_desps):
         fn.restype = ctypes.c_int
         fn.argtypes = [ctypes.POINTER(_lib.KernelDesp), ctypes.c_int]
-    assert L.cb2_enumerate_gemm_desps(None, 0) == 18 and L.cb2_enumerate_conv_desps(None, 0) == 12
+    assert L.cb2_enumerate_gemm_desps(None, 0) == 18 and L.cb2_enumerate_conv_desps(None, 0) == 24
     two = (_lib.KernelDesp * 2)()
-    assert L.cb2_enumerate_conv_desps(two, 2) == 12  # the count, whatever the capacity
+    assert L.cb2_enumerate_conv_desps(two, 2) == 24  # the count, whatever the capacity
     assert two[0].op_type == 0 and list(two[0].tile_shape) == [128, 64, 64] and two[1].tile_shape[2] == 128
     gemm = GemmMainUnitTest.get_all_algo_desp()
     conv = ConvMainUnitTest.get_all_conv_algo_desp()
-    assert len(gemm) == 18 and len(conv) == 12
+    assert len(gemm) == 18 and len(conv) == 24
     assert sum(d.shuffle_type == ShuffleStrideType.ShuffleAB for d in gemm) == 2
     assert all(d.trans_a and not d.trans_b and d.split_k_serial for d in gemm if d.shuffle_type == ShuffleStrideType.ShuffleAB)
-    assert sum(bool(d.is_int8_inference) for d in conv) == 2
+    assert sum(bool(d.is_int8_inference) for d in conv) == 4 and sum(bool(d.dynamic_mask) for d in conv) == 12
     assert {tuple(d.tile_shape) for d in conv if d.op_type == ConvOpType.BackwardWeight} == {(128, 64, 128), (128, 128, 128)}
     names = {d.__repr__() for d in conv} | {d.__repr__() for d in gemm}
-    assert len(names) == 30, "every variant has its own algorithm name"
+    assert len(names) == 42, "every variant has its own algorithm name"
     assert all(n.startswith("Blackwell_") for n in names)
 
 
