@@ -380,57 +380,57 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
   };
   const int gy = gridDim.y;
 
-  if (warp < 4) {
-    // ======================= epilogue: one fp32 partial per unit, then the shared summing of
-    // whatever offsets are ready
-    const int et = threadIdx.x;
-    const int *s_units = s_plan + kWgradPlanUnits;
-    const int *s_first = s_plan + kWgradPlanFirst;
-    const long long tile_f4 = 32ll * BLOCK_N;  // float4 per [128 x BLOCK_N] tile
-    constexpr int kSlices = BLOCK_N / 4;       // a slice = four columns of all 128 rows: one float4 per thread
-    // partial layout: float4 (col/4, row) at index (col/4) * 128 + row, so that the 32 rows of a
-    // warp touch 512 contiguous bytes; slice q of a partial is its q-th run of 128 float4
-    auto partial_of = [&](int u) {
-      return reinterpret_cast<float4 *>(p.partials) + ((long long)u * gy + blockIdx.y) * tile_f4;
-    };
-    auto ctl_of = [&](int f) { return p.ctl + kWgradCtlBase + 4 * ((long long)f * gy + blockIdx.y); };
-    // dW[m0 + row, f, n0 + 4 * q .. + 3] from four sums
-    auto write_out = [&](int f, int row, int q, float4 v) {
-      const int m = m0 + row, n = n0 + 4 * q;
-      if (m >= p.m_total || n >= p.n_total)
-        return;
-      const long long off = (long long)m * p.ldo + (long long)f * p.f_stride + n;
-      float r[4] = {v.x, v.y, v.z, v.w};
-      if (p.out_f32) {
-        float *o = reinterpret_cast<float *>(p.out);
-        const float *sp = reinterpret_cast<const float *>(p.src);
+  // ---- shared by the epilogue warps and the summing phase at the end
+  const int *s_units = s_plan + kWgradPlanUnits;
+  const int *s_first = s_plan + kWgradPlanFirst;
+  constexpr int kTileF4 = 32 * BLOCK_N;  // float4 per [128 x BLOCK_N] tile
+  // partial layout: float4 (col/4, row) at index (col/4) * 128 + row, so that the 32 rows of a
+  // warp touch 512 contiguous bytes
+  auto partial_of = [&](int u) {
+    return reinterpret_cast<float4 *>(p.partials) + ((long long)u * gy + blockIdx.y) * kTileF4;
+  };
+  auto ctl_of = [&](int f) { return p.ctl + kWgradCtlBase + 4 * ((long long)f * gy + blockIdx.y); };
+  // dW[m0 + row, f, n0 + 4 * q .. + 3] from four sums
+  auto write_out = [&](int f, int row, int q, float4 v) {
+    const int m = m0 + row, n = n0 + 4 * q;
+    if (m >= p.m_total || n >= p.n_total)
+      return;
+    const long long off = (long long)m * p.ldo + (long long)f * p.f_stride + n;
+    float r[4] = {v.x, v.y, v.z, v.w};
+    if (p.out_f32) {
+      float *o = reinterpret_cast<float *>(p.out);
+      const float *sp = reinterpret_cast<const float *>(p.src);
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          o[off + j] = (p.beta != 0.f) ? __fmaf_rn(p.alpha, r[j], __fmul_rn(p.beta, sp[off + j])) : __fmul_rn(p.alpha, r[j]);
-      } else {
-        __half *o = reinterpret_cast<__half *>(p.out);
-        const __half *sp = reinterpret_cast<const __half *>(p.src);
-        __half h[4];
+      for (int j = 0; j < 4; ++j)
+        o[off + j] = (p.beta != 0.f) ? __fmaf_rn(p.alpha, r[j], __fmul_rn(p.beta, sp[off + j])) : __fmul_rn(p.alpha, r[j]);
+    } else {
+      __half *o = reinterpret_cast<__half *>(p.out);
+      const __half *sp = reinterpret_cast<const __half *>(p.src);
+      __half h[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float t = (p.beta != 0.f) ? __fmaf_rn(p.alpha, r[j], __fmul_rn(p.beta, __half2float(sp[off + j])))
-                                          : __fmul_rn(p.alpha, r[j]);
-          h[j] = __float2half_rn(t);
-        }
-        *reinterpret_cast<uint2 *>(o + off) = *reinterpret_cast<const uint2 *>(h);
+      for (int j = 0; j < 4; ++j) {
+        const float t = (p.beta != 0.f) ? __fmaf_rn(p.alpha, r[j], __fmul_rn(p.beta, __half2float(sp[off + j])))
+                                        : __fmul_rn(p.alpha, r[j]);
+        h[j] = __float2half_rn(t);
       }
-    };
+      *reinterpret_cast<uint2 *>(o + off) = *reinterpret_cast<const uint2 *>(h);
+    }
+  };
+  int n_active = 0;  // offsets that have units: the ones that will be summed
+  for (int f = 0; f < p.kv; ++f)
+    n_active += s_units[f] > 0 ? 1 : 0;
+
+  if (warp < 4) {
+    // ======================= epilogue: one fp32 partial per unit; the unit that completes an
+    // offset marks it ready for the summing phase
+    const int et = threadIdx.x;
     // Offsets inside the filter that no row tile carries get alpha * 0 + beta * source; CTA c
     // takes those with f = c (mod G).
-    int n_active = 0;  // offsets that have units: the ones that will be summed
-    for (int f = 0; f < p.kv; ++f)
-      n_active += s_units[f] > 0 ? 1 : 0;
     for (int f = blockIdx.x; f < p.kv; f += gridDim.x)
       if ((p.mode != kWgradMaskConv || ((p.mask_filter >> (f & 31)) & 1u)) && s_units[f] == 0)
-        for (int q = 0; q < kSlices; ++q)
+        for (int q = 0; q < BLOCK_N / 4; ++q)
           write_out(f, et, q, make_float4(0.f, 0.f, 0.f, 0.f));
     int acc_use = 0;
-    bool walk_ok = true;
     wgrad_walk(
         p.lists, p.list_stride, s_plan, s_tiles, [&](int, int) -> bool { return true; },
         [&](int, int, bool) -> bool { return true; },
@@ -438,7 +438,7 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
           float4 *dst = partial_of(u) + et;
           if (active == 0) {
             // a unit without tiles (fewer steps than CTAs) still owns a partial: all zeros
-            for (int q = 0; q < kSlices; ++q)
+            for (int q = 0; q < BLOCK_N / 4; ++q)
               dst[q * 128] = make_float4(0.f, 0.f, 0.f, 0.f);
           } else {
             const int buf = acc_use & 1;
@@ -451,10 +451,8 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
                 fail(kStatusWaitTimeout);
             }
             named_bar_sync(1, 128);
-            if (misc[2] == 0) {
-              walk_ok = false;
+            if (misc[2] == 0)
               return false;
-            }
             tc_fence_after();
             const uint32_t trow = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
                                   static_cast<uint32_t>(buf * BLOCK_N);
@@ -483,80 +481,6 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
           }
           return true;
         });
-    // ---- summing: take column slices of ready offsets until this tile's offsets are all summed,
-    // or nothing has been on offer for a while (whoever makes an offset ready finds its slices on
-    // offer in this very loop, so every slice is taken by somebody)
-    int polls = 0;
-    uint32_t handed_out[4] = {0u, 0u, 0u, 0u};  // offsets whose slices are known to be all taken (thread 0)
-    while (walk_ok) {
-      if (et == 0) {
-        int job = -1;
-        // start at a different offset in every CTA so that the CTAs spread over the ready offsets
-        const int rot = blockIdx.x & 31;
-        for (int ww = 0; ww < p.words && job < 0; ++ww) {
-          const int w = (ww + (blockIdx.x >> 5)) % p.words;
-          uint32_t open = static_cast<uint32_t>(ld_acquire_gpu(p.ctl + 9 + 8 * blockIdx.y + w)) & ~handed_out[w];
-          open = rot ? ((open >> rot) | (open << (32 - rot))) : open;
-          while (open && job < 0) {
-            const int k = __ffs(open) - 1;
-            open &= open - 1;
-            const int b = (k + rot) & 31;
-            const int f = 32 * w + b;
-            const int sl = atomicAdd(ctl_of(f) + 1, 1);
-            if (sl < kSlices)
-              job = f * kSlices + sl;
-            else
-              handed_out[w] |= 1u << b;
-          }
-        }
-        if (job < 0) {
-          const bool all_summed = ld_acquire_gpu(p.ctl + 8 + 8 * blockIdx.y) >= n_active;
-          if (all_summed || ++polls > kWgradLingerPolls)
-            job = -2;
-          else
-            __nanosleep(100);
-        }
-        misc[6] = job;
-      }
-      named_bar_sync(1, 128);
-      const int job = misc[6];
-      named_bar_sync(1, 128);  // everybody has read the job before thread 0 writes the next one
-      if (job == -2)
-        break;
-      if (job < 0)
-        continue;
-      const int f = job / kSlices, sl = job % kSlices;
-      const int S = s_units[f];
-      const float4 *src = partial_of(s_first[f]) + sl * 128 + et;
-      const long long ustride = (long long)gy * tile_f4;
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-      for (int j = 0; j < S; ++j) {
-        const float4 v = __ldcg(src + j * ustride);
-        acc.x += v.x;
-        acc.y += v.y;
-        acc.z += v.z;
-        acc.w += v.w;
-      }
-      write_out(f, et, sl, acc);
-      named_bar_sync(1, 128);
-      if (et == 0) {
-        if (atomicAdd(ctl_of(f) + 2, 1) == kSlices - 1)
-          atomicAdd(p.ctl + 8 + 8 * blockIdx.y, 1);
-      }
-    }
-    // the last CTA to leave puts every control word back to zero for the next call
-    if (et == 0) {
-      __threadfence();
-      misc[6] = atomicAdd(p.ctl, 1) == (int)(gridDim.x * gridDim.y) - 1 ? 1 : 0;
-    }
-    named_bar_sync(1, 128);
-    if (misc[6]) {
-      const int n_ctl = kWgradCtlBase + 4 * p.kv * gy;
-      for (int i = et; i < n_ctl; i += 128)
-        p.ctl[i] = 0;
-      __threadfence();
-    }
   } else if (warp == 4) {
     // ======================= MMA issuer
     constexpr uint32_t idesc = make_idesc(0, true, true, 128, BLOCK_N);
@@ -746,8 +670,132 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
       cp_async_wait_all();
   }
 
+  // ---------------------------------------------------------------- summing
+  // Every role has finished its walk; the whole CTA now helps to sum the partials of whatever
+  // offsets are ready, claiming ranges of the tile's float4 positions, until this output tile's
+  // offsets are all summed or nothing has been on offer for a while.  Whoever makes an offset
+  // ready finds its ranges on offer in this very loop, so every range is taken by somebody.
+  // Each output element is summed by one thread -- for offsets with many units: by sixteen warps
+  // whose sums are combined in warp order -- so the result does not depend on timing.
   tc_fence_before();
   __syncthreads();
+  {
+    const int tid = threadIdx.x;
+    float4 *s_part = reinterpret_cast<float4 *>(smem + Cfg::OFF_STAGES);  // the operand stages are idle now
+    const long long ustride = (long long)gy * kTileF4;
+    int polls = 0;
+    uint32_t handed_out[4] = {0u, 0u, 0u, 0u};  // offsets whose ranges are known to be all taken (thread 0)
+    const bool usable = *abort_flag == 0;
+    while (usable) {
+      if (tid == 0) {
+        int job_f = -1, q0 = 0, q1 = 0;
+        // start at a different offset in every CTA so that the CTAs spread over the ready offsets
+        const int rot = blockIdx.x & 31;
+        for (int ww = 0; ww < p.words && job_f < 0; ++ww) {
+          const int w = (ww + (blockIdx.x >> 5)) % p.words;
+          uint32_t open = static_cast<uint32_t>(ld_acquire_gpu(p.ctl + 9 + 8 * blockIdx.y + w)) & ~handed_out[w];
+          open = rot ? ((open >> rot) | (open << (32 - rot))) : open;
+          while (open && job_f < 0) {
+            const int k = __ffs(open) - 1;
+            open &= open - 1;
+            const int b = (k + rot) & 31;
+            const int f = 32 * w + b;
+            // few units: a quarter of the tile or all of it at once; many: 32 positions, the
+            // units split over sixteen warps
+            const int S = s_units[f];
+            const int claim = S > 16 ? 32 : (S > 4 ? kTileF4 / 4 : kTileF4);
+            const int q = atomicAdd(ctl_of(f) + 1, claim);
+            if (q < kTileF4) {
+              job_f = f;
+              q0 = q;
+              q1 = q + claim;
+            } else {
+              handed_out[w] |= 1u << b;
+            }
+          }
+        }
+        if (job_f < 0) {
+          const bool all_summed = ld_acquire_gpu(p.ctl + 8 + 8 * blockIdx.y) >= n_active;
+          if (all_summed || ++polls > kWgradLingerPolls)
+            job_f = -2;
+          else
+            __nanosleep(100);
+        }
+        misc[6] = job_f;
+        misc[7] = q0;
+        misc[8] = q1;
+      }
+      __syncthreads();
+      const int f = misc[6], q0 = misc[7], q1 = misc[8];
+      __syncthreads();  // everybody has read the job before thread 0 writes the next one
+      if (f == -2)
+        break;
+      if (f < 0)
+        continue;
+      const int S = s_units[f];
+      const float4 *src = partial_of(s_first[f]);
+      if (S > 16) {
+        // positions q0 .. q0+31; warp w < 16 adds units w, w + 16, ... in order
+        if (warp < 16) {
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          const float4 *sp = src + q0 + lane;
+#pragma unroll 4
+          for (int j = warp; j < S; j += 16) {
+            const float4 v = __ldcg(sp + j * ustride);
+            acc.x += v.x;
+            acc.y += v.y;
+            acc.z += v.z;
+            acc.w += v.w;
+          }
+          s_part[warp * 32 + lane] = acc;
+        }
+        __syncthreads();
+        if (warp == 0) {
+          float4 acc = s_part[lane];
+#pragma unroll
+          for (int w = 1; w < 16; ++w) {
+            const float4 v = s_part[w * 32 + lane];
+            acc.x += v.x;
+            acc.y += v.y;
+            acc.z += v.z;
+            acc.w += v.w;
+          }
+          const int q = q0 + lane;
+          write_out(f, q & 127, q >> 7, acc);
+        }
+      } else {
+        for (int q = q0 + tid; q < q1; q += Cfg::THREADS) {
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 16
+          for (int j = 0; j < S; ++j) {
+            const float4 v = __ldcg(src + j * ustride + q);
+            acc.x += v.x;
+            acc.y += v.y;
+            acc.z += v.z;
+            acc.w += v.w;
+          }
+          write_out(f, q & 127, q >> 7, acc);
+        }
+      }
+      __syncthreads();
+      if (tid == 0) {
+        if (atomicAdd(ctl_of(f) + 2, q1 - q0) + (q1 - q0) == kTileF4)
+          atomicAdd(p.ctl + 8 + 8 * blockIdx.y, 1);
+      }
+    }
+    // the last CTA to leave puts every control word back to zero for the next call
+    if (tid == 0) {
+      __threadfence();
+      misc[6] = atomicAdd(p.ctl, 1) == (int)(gridDim.x * gridDim.y) - 1 ? 1 : 0;
+    }
+    __syncthreads();
+    if (misc[6]) {
+      const int n_ctl = kWgradCtlBase + 4 * p.kv * gy;
+      for (int i = tid; i < n_ctl; i += Cfg::THREADS)
+        p.ctl[i] = 0;
+      __threadfence();
+    }
+  }
   if (threadIdx.x == 0)
     CB2_TRACE_CTA(1, 0);
   if (warp == 4) {
