@@ -43,7 +43,7 @@ WORKLOAD = "scale-out: 8 scenes x 120k voxels, grid [41,1600,1408], seed 4, fwd+
 L2_BYTES = 126 * 1024 * 1024
 # SM shares of the three kernels when they run side by side (forward, backward input, backward
 # weight); the weight gradient moves the same bytes with more steps per row tile.
-SHARES = (48, 48, 52)
+SHARES = tuple(int(v) for v in os.environ.get("CUMM_B200_BENCH_SHARES", "48,48,52").split(","))
 
 
 def host_features(n_in, n_out, seed):

@@ -6,10 +6,12 @@ There is no fallback: if the library is missing or a call fails, an exception is
 from __future__ import annotations
 
 import ctypes
+import os
 from pathlib import Path
 
 _HERE = Path(__file__).resolve().parent
-LIB_PATH = _HERE / "libcumm_b200.so"
+# CUMM_B200_LIBRARY: another build of the same library (e.g. one compiled with -DCB2_TRACE)
+LIB_PATH = Path(os.environ.get("CUMM_B200_LIBRARY") or _HERE / "libcumm_b200.so")
 
 CB2_OK = 0
 CB2_ERR_INVALID_ARG = -1

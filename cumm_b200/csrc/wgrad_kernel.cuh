@@ -7,13 +7,16 @@
 // "MN-major": a gathered row is 128-byte-swizzled along its channels and the 128 rows of a
 // tile are the K dimension of the MMA.  Work is cut into units (filter offset f, range of
 // row tiles); a unit accumulates in TMEM, leaves one fp32 partial [128 x BLOCK_N] in the
-// workspace and counts itself in.  The unit that completes an offset marks it ready; from then
-// on its partials are summed -- in unit order, so the result does not depend on timing -- in
-// column slices that any CTA of the grid may take: a CTA that has finished its own units stays
-// for a bounded time and takes slices of ready offsets, and the CTA that made an offset ready
-// does not leave before all of that offset's slices have been taken.  One launch, no atomics on
-// data, and nobody's progress depends on anybody else's (the reference serialises split-K slices
-// through a spinning semaphore, cumm/conv/kernel.py:960-1083).
+// workspace and counts itself in; the unit that completes an offset sets the offset's ready flag.
+// The partials of an offset are summed in unit order (the result does not depend on timing)
+// by CTAs that have finished their own units and wait, bounded, for that flag: an offset with few
+// units by one CTA (the offsets are dealt out over the grid); an offset with many units (the
+// centre of a submanifold convolution has one per CTA) by all CTAs, each taking a fixed share
+// of the tile's positions.  One launch, no atomics on data.  The wait
+// is the only place where a CTA depends on others: like every wait in this library it gives up
+// after a second and reports through the status word, and the launcher keeps the grid within
+// the number of SMs so that all CTAs run at once (the reference serialises split-K slices through
+// an unbounded spinning semaphore, cumm/conv/kernel.py:960-1083).
 //
 // Semantics follow cumm/gemm/blockmma/mma.py:608-648,722-740 (a row takes part for
 // offset f iff the reduced-mask word covering it has bit f), cumm/conv/sparse_iters.py
@@ -39,10 +42,9 @@ struct WgradParams {
   const int32_t *a_inds;   // pair-list mode
   const int32_t *b_inds;   //   "
   float *partials;         // workspace: [unit][m_tile][n_tile][128 x BLOCK_N] fp32
-  int *ctl;                // workspace, zero between calls: [0] CTAs that have left; [8 + 8 by] offsets summed and
-                           // [9 + 8 by, 13 + 8 by) bit masks of the ready offsets of output tile by; from
-                           // kWgradCtlBase on, four ints per (f, by): units arrived, next slice to hand
-                           // out, slices summed
+  int *ctl;                // workspace, zero between calls: [0] CTAs that have left; [9 + 8 by, 13 + 8 by) bit
+                           // masks of the ready offsets of output tile by; from kWgradCtlBase on, per
+                           // (f, by) at a pitch of four ints: units arrived
   int *sched;              // workspace header: [0,128) number of row tiles carrying offset f
   const int *lists;        // workspace: per offset, the ordered list of those tiles
   int list_stride;         // ints between two offsets' lists
@@ -227,7 +229,7 @@ constexpr int kWgradPlanFirst = kWgradPlanUnits + kWgradMaxOffsets;
 constexpr int kWgradPlanInts = kWgradPlanFirst + kWgradMaxOffsets;  // 904 <= the 1024 reserved
 constexpr int kWgradMaxOutTiles = 128; // (m, n) tiles of the weight gradient a launch can have
 constexpr int kWgradCtlBase = 8 + 8 * kWgradMaxOutTiles;  // first per-(offset, tile) control word
-constexpr int kWgradLingerPolls = 256; // a CTA with nothing to do looks for ready slices this often, then leaves
+constexpr int kWgradSharedSumUnits = 16;  // offsets with more units than this are summed by all CTAs together
 template <int TILE_CAP>
 __device__ __forceinline__ void wgrad_load_plan(const WgradParams &p, const int *lists, int list_stride, int *s_plan,
                                                 int *s_tiles) {
@@ -416,10 +418,6 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
       *reinterpret_cast<uint2 *>(o + off) = *reinterpret_cast<const uint2 *>(h);
     }
   };
-  int n_active = 0;  // offsets that have units: the ones that will be summed
-  for (int f = 0; f < p.kv; ++f)
-    n_active += s_units[f] > 0 ? 1 : 0;
-
   if (warp < 4) {
     // ======================= epilogue: one fp32 partial per unit; the unit that completes an
     // offset marks it ready for the summing phase
@@ -538,8 +536,6 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
           }
           return true;
         });
-    if (lane == 0)
-      CB2_TRACE_CTA(2, (unsigned long long)step);
     if (lane == 0 && ok_all) {
       tc_commit(final_bar);
       if (!mbar_wait(final_bar, 0, abort_flag))
@@ -671,130 +667,131 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
   }
 
   // ---------------------------------------------------------------- summing
-  // Every role has finished its walk; the whole CTA now helps to sum the partials of whatever
-  // offsets are ready, claiming ranges of the tile's float4 positions, until this output tile's
-  // offsets are all summed or nothing has been on offer for a while.  Whoever makes an offset
-  // ready finds its ranges on offer in this very loop, so every range is taken by somebody.
-  // Each output element is summed by one thread -- for offsets with many units: by sixteen warps
-  // whose sums are combined in warp order -- so the result does not depend on timing.
+  // Every role has finished its walk; the whole CTA now sums partials.  Each output element is
+  // summed by one thread in unit order -- for the offsets with many units: by sixteen warps, each
+  // over every sixteenth unit, whose sums are combined in warp order.
   tc_fence_before();
   __syncthreads();
-  {
+  if (threadIdx.x == 0)
+    CB2_TRACE_CTA(2, global_timer_ns());  // roles done
+  if (*abort_flag == 0) {
     const int tid = threadIdx.x;
     float4 *s_part = reinterpret_cast<float4 *>(smem + Cfg::OFF_STAGES);  // the operand stages are idle now
     const long long ustride = (long long)gy * kTileF4;
-    int polls = 0;
-    uint32_t handed_out[4] = {0u, 0u, 0u, 0u};  // offsets whose ranges are known to be all taken (thread 0)
-    const bool usable = *abort_flag == 0;
-    while (usable) {
+    // this CTA's share of the offsets with many units: positions [c, c + 1) * kTileF4 / G in runs of 32
+    const int q_begin = (int)(((long long)blockIdx.x * kTileF4) / gridDim.x) & ~31;
+    const int q_end = blockIdx.x + 1 == gridDim.x ? kTileF4 : ((int)(((long long)(blockIdx.x + 1) * kTileF4) / gridDim.x) & ~31);
+    for (int f = 0; f < p.kv; ++f) {
+      const int S = s_units[f];
+      if (S == 0)
+        continue;
+      const bool shared_sum = S > kWgradSharedSumUnits;
+      // an offset with few units belongs to a small group of neighbouring CTAs (the groups are dealt
+      // out evenly over the grid), each summing an equal run of positions
+      const int group = max(1, (int)gridDim.x / p.kv);
+      const int member = (int)blockIdx.x - (int)(((long long)f * gridDim.x) / p.kv);
+      const int lo = shared_sum ? q_begin : ((member * kTileF4) / group) & ~1;
+      const int hi = shared_sum ? q_end : (member + 1 == group ? kTileF4 : (((member + 1) * kTileF4) / group) & ~1);
+      if (shared_sum ? (q_begin >= q_end) : (member < 0 || member >= group))
+        continue;
       if (tid == 0) {
-        int job_f = -1, q0 = 0, q1 = 0;
-        // start at a different offset in every CTA so that the CTAs spread over the ready offsets
-        const int rot = blockIdx.x & 31;
-        for (int ww = 0; ww < p.words && job_f < 0; ++ww) {
-          const int w = (ww + (blockIdx.x >> 5)) % p.words;
-          uint32_t open = static_cast<uint32_t>(ld_acquire_gpu(p.ctl + 9 + 8 * blockIdx.y + w)) & ~handed_out[w];
-          open = rot ? ((open >> rot) | (open << (32 - rot))) : open;
-          while (open && job_f < 0) {
-            const int k = __ffs(open) - 1;
-            open &= open - 1;
-            const int b = (k + rot) & 31;
-            const int f = 32 * w + b;
-            // few units: a quarter of the tile or all of it at once; many: 32 positions, the
-            // units split over sixteen warps
-            const int S = s_units[f];
-            const int claim = S > 16 ? 32 : (S > 4 ? kTileF4 / 4 : kTileF4);
-            const int q = atomicAdd(ctl_of(f) + 1, claim);
-            if (q < kTileF4) {
-              job_f = f;
-              q0 = q;
-              q1 = q + claim;
-            } else {
-              handed_out[w] |= 1u << b;
+        // bounded wait for the last unit of f
+        const int *flag = p.ctl + 9 + 8 * blockIdx.y + (f >> 5);
+        int ok = 1;
+        unsigned long long t0 = 0;
+        for (unsigned spin = 0; !((static_cast<uint32_t>(ld_acquire_gpu(flag)) >> (f & 31)) & 1u); ++spin) {
+          __nanosleep(100);
+          if ((spin & 63u) == 63u) {
+            const unsigned long long now = global_timer_ns();
+            if (t0 == 0)
+              t0 = now;
+            else if (now - t0 > kWaitLimitNs) {
+              ok = 0;
+              break;
             }
           }
         }
-        if (job_f < 0) {
-          const bool all_summed = ld_acquire_gpu(p.ctl + 8 + 8 * blockIdx.y) >= n_active;
-          if (all_summed || ++polls > kWgradLingerPolls)
-            job_f = -2;
-          else
-            __nanosleep(100);
-        }
-        misc[6] = job_f;
-        misc[7] = q0;
-        misc[8] = q1;
+        if (!ok)
+          fail(kStatusWaitTimeout);
+        misc[6] = ok;
+        CB2_TRACE_EVENT(6, 20, f);  // offset ready
       }
       __syncthreads();
-      const int f = misc[6], q0 = misc[7], q1 = misc[8];
-      __syncthreads();  // everybody has read the job before thread 0 writes the next one
-      if (f == -2)
+      const bool ok = misc[6] != 0;
+      __syncthreads();  // everybody has read the result before thread 0 writes the next one
+      if (!ok)
         break;
-      if (f < 0)
-        continue;
-      const int S = s_units[f];
       const float4 *src = partial_of(s_first[f]);
-      if (S > 16) {
-        // positions q0 .. q0+31; warp w < 16 adds units w, w + 16, ... in order
-        if (warp < 16) {
-          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-          const float4 *sp = src + q0 + lane;
-#pragma unroll 4
-          for (int j = warp; j < S; j += 16) {
-            const float4 v = __ldcg(sp + j * ustride);
-            acc.x += v.x;
-            acc.y += v.y;
-            acc.z += v.z;
-            acc.w += v.w;
-          }
-          s_part[warp * 32 + lane] = acc;
-        }
-        __syncthreads();
-        if (warp == 0) {
-          float4 acc = s_part[lane];
+      if (!shared_sum) {
+        // two positions per thread at a time, all units' loads of both in flight together
+        for (int q0 = lo + 2 * tid; q0 < hi; q0 += 2 * Cfg::THREADS) {
+          float4 acc[2];
 #pragma unroll
-          for (int w = 1; w < 16; ++w) {
-            const float4 v = s_part[w * 32 + lane];
-            acc.x += v.x;
-            acc.y += v.y;
-            acc.z += v.z;
-            acc.w += v.w;
+          for (int g = 0; g < 2; ++g)
+            acc[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+          for (int j = 0; j < S; ++j) {
+            const float4 *sp = src + j * ustride + q0;
+#pragma unroll
+            for (int g = 0; g < 2; ++g) {
+              const float4 v = __ldcg(sp + g);
+              acc[g].x += v.x;
+              acc[g].y += v.y;
+              acc[g].z += v.z;
+              acc[g].w += v.w;
+            }
           }
-          const int q = q0 + lane;
-          write_out(f, q & 127, q >> 7, acc);
+#pragma unroll
+          for (int g = 0; g < 2; ++g)
+            write_out(f, (q0 + g) & 127, (q0 + g) >> 7, acc[g]);
         }
       } else {
-        for (int q = q0 + tid; q < q1; q += Cfg::THREADS) {
-          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 16
-          for (int j = 0; j < S; ++j) {
-            const float4 v = __ldcg(src + j * ustride + q);
-            acc.x += v.x;
-            acc.y += v.y;
-            acc.z += v.z;
-            acc.w += v.w;
+        for (int q0 = lo; q0 < hi; q0 += 32) {
+          if (warp < 16) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            const float4 *sp = src + q0 + lane;
+#pragma unroll 8
+            for (int j = warp; j < S; j += 16) {
+              const float4 v = __ldcg(sp + j * ustride);
+              acc.x += v.x;
+              acc.y += v.y;
+              acc.z += v.z;
+              acc.w += v.w;
+            }
+            s_part[warp * 32 + lane] = acc;
           }
-          write_out(f, q & 127, q >> 7, acc);
+          __syncthreads();
+          if (warp == 0) {
+            float4 acc = s_part[lane];
+#pragma unroll
+            for (int w = 1; w < 16; ++w) {
+              const float4 v = s_part[w * 32 + lane];
+              acc.x += v.x;
+              acc.y += v.y;
+              acc.z += v.z;
+              acc.w += v.w;
+            }
+            const int q = q0 + lane;
+            write_out(f, q & 127, q >> 7, acc);
+          }
+          __syncthreads();
         }
       }
-      __syncthreads();
-      if (tid == 0) {
-        if (atomicAdd(ctl_of(f) + 2, q1 - q0) + (q1 - q0) == kTileF4)
-          atomicAdd(p.ctl + 8 + 8 * blockIdx.y, 1);
-      }
+      if (tid == 0)
+        CB2_TRACE_EVENT(6, 21, f);  // summed
     }
-    // the last CTA to leave puts every control word back to zero for the next call
-    if (tid == 0) {
-      __threadfence();
-      misc[6] = atomicAdd(p.ctl, 1) == (int)(gridDim.x * gridDim.y) - 1 ? 1 : 0;
-    }
-    __syncthreads();
-    if (misc[6]) {
-      const int n_ctl = kWgradCtlBase + 4 * p.kv * gy;
-      for (int i = tid; i < n_ctl; i += Cfg::THREADS)
-        p.ctl[i] = 0;
-      __threadfence();
-    }
+  }
+  // the last CTA to leave puts every control word back to zero for the next call
+  if (threadIdx.x == 0) {
+    __threadfence();
+    misc[6] = atomicAdd(p.ctl, 1) == (int)(gridDim.x * gridDim.y) - 1 ? 1 : 0;
+  }
+  __syncthreads();
+  if (misc[6]) {
+    const int n_ctl = kWgradCtlBase + 4 * p.kv * gy;
+    for (int i = threadIdx.x; i < n_ctl; i += Cfg::THREADS)
+      p.ctl[i] = 0;
+    __threadfence();
   }
   if (threadIdx.x == 0)
     CB2_TRACE_CTA(1, 0);
