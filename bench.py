@@ -478,6 +478,8 @@ def main():
         barrier()
         rep_ms.append(e0.elapsed_time(e1) / args.steps)
     clocks = sampler.finish()
+    # the exchange kernel's own clock readings in the last timed step (graph replay, ranks in step)
+    exchange_in_step_ns = peer_ar.last_call_ns() if peer_ar is not None else None
     rep_t = torch.tensor(rep_ms, dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(rep_t, op=dist.ReduceOp.MAX)
@@ -496,10 +498,10 @@ def main():
             op_ms += [evs[j].elapsed_time(evs[j + 1]) for j in range(4)]
     op_ms /= reps
     if peer_ar is not None:
-        # Between events the exchange also holds the wait for the slowest rank's eager launches;
-        # the kernel's own clock readings (start to finish of the last call on this rank) are the
-        # figure that belongs beside the other kernels.
-        op_ms[3] = peer_ar.last_call_ns()["done"] * 1e-6
+        # Between events of eager launches the exchange also holds the wait for the slowest rank's
+        # host; the kernel's own clock readings in the last timed step (start to finish on this
+        # rank) are the figure that belongs beside the other kernels.
+        op_ms[3] = exchange_in_step_ns["done"] * 1e-6
     status = _lib.device_status()
 
     t = torch.tensor([float(num_pairs), float(n_out), float(status)], dtype=torch.float64, device=dev)
@@ -572,7 +574,7 @@ def main():
                          "graph(fwd+wgrad), then NCCL all-reduce + cast eagerly on a side stream overlapped with graph(dgrad)"),
             "exchange": exchange_kind if world > 1 else "none (one GPU)",
             "exchange_verified": exchange_verified,
-            "exchange_last_call_ns_rank0": peer_ar.last_call_ns() if peer_ar is not None else None,
+            "exchange_last_call_ns_rank0": exchange_in_step_ns,
             "timed_region": f"{len(rep_ms)} repeats of {args.steps} steps; ms_per_step is the median repeat",
         })
         line = {

@@ -39,6 +39,7 @@ EXPORTED_SYMBOLS = (
     "cb2_enumerate_gemm_desps",
     "cb2_enumerate_conv_desps",
     "cb2_last_launch_info",
+    "cb2_dense_tables_run",
 )
 
 
@@ -142,6 +143,18 @@ class KernelDesp(ctypes.Structure):
     ]
 
 
+class DenseTablesArgs(ctypes.Structure):
+    """``cb2_dense_tables_args``."""
+    _fields_ = [
+        ("batch", ctypes.c_int),
+        ("in_dims", ctypes.c_int * 3), ("out_dims", ctypes.c_int * 3),
+        ("ksize", ctypes.c_int * 3), ("stride", ctypes.c_int * 3), ("pad", ctypes.c_int * 3), ("dil", ctypes.c_int * 3),
+        ("indices_fwd", ctypes.c_void_p), ("indices_bwd", ctypes.c_void_p),
+        ("mask_fwd", ctypes.c_void_p), ("argsort_fwd", ctypes.c_void_p),
+        ("mask_bwd", ctypes.c_void_p), ("argsort_bwd", ctypes.c_void_p),
+    ]
+
+
 class PeerAllreduceArgs(ctypes.Structure):
     """``cb2_peer_allreduce_args``."""
     _fields_ = [
@@ -199,6 +212,8 @@ def load() -> ctypes.CDLL:
     for fn in (L.cb2_enumerate_gemm_desps, L.cb2_enumerate_conv_desps):
         fn.restype = ctypes.c_int
         fn.argtypes = [ctypes.POINTER(KernelDesp), ctypes.c_int]
+    L.cb2_dense_tables_run.restype = ctypes.c_int
+    L.cb2_dense_tables_run.argtypes = [ctypes.POINTER(DenseTablesArgs), ctypes.c_void_p]
     L.cb2_last_launch_info.restype = ctypes.c_int
     L.cb2_last_launch_info.argtypes = [ctypes.POINTER(ctypes.c_int)] * 3
     _lib = L

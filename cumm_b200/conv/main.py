@@ -44,7 +44,12 @@ class ConvMainUnitTest:
                     out_prod: int = -1, mask_sparse: bool = True) -> Tuple[int, int, int]:
         """cumm/conv/main.py:469-482 -> include/tensorview/gemm/core/utils.h:62-92."""
         if not mask_sparse:
-            raise RuntimeError("only mask-sparse implicit GEMM is built")
+            # dense convolution (include/tensorview/gemm/core/utils.h:62-92): batch times the output
+            # positions (forward, backward weight) or the input positions (backward input)
+            prod = in_prod if int(op_type) == int(ConvOpType.BackwardInput) else out_prod
+            if prod < 0:
+                raise RuntimeError("a dense convolution needs in_prod / out_prod")
+            N = N * prod
         return implicit_gemm_mnk(op_type, N, C, K, kernel_volume)
 
     @staticmethod

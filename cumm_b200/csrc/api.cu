@@ -740,6 +740,60 @@ int cb2_pairgen_run(const cb2_pairgen_args *a, void *stream_v) {
   return CB2_OK;
 }
 
+// ---------------------------------------------------------------- tables of a dense convolution
+int cb2_dense_tables_run(const cb2_dense_tables_args *a, void *stream_v) {
+  CB2_CHECK_ARG(a != nullptr, "null arguments");
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  DeviceState *dev;
+  int rc = get_device(&dev);
+  if (rc)
+    return rc;
+  cb2pg::DenseGeometry g;
+  g.batch = a->batch;
+  long long n_in = a->batch, n_out = a->batch, kv = 1;
+  CB2_CHECK_ARG(a->batch >= 1, "bad batch %d", a->batch);
+  for (int i = 0; i < 3; ++i) {
+    CB2_CHECK_ARG(a->in_dims[i] >= 1 && a->out_dims[i] >= 1 && a->ksize[i] >= 1 && a->stride[i] >= 1 &&
+                      a->dil[i] >= 1 && a->pad[i] >= 0,
+                  "bad geometry on axis %d", i);
+    const int span = a->in_dims[i] + 2 * a->pad[i] - a->dil[i] * (a->ksize[i] - 1) - 1;
+    CB2_CHECK_ARG(span >= 0 && a->out_dims[i] == span / a->stride[i] + 1,
+                  "output extent %d on axis %d does not match input %d, kernel %d, stride %d, padding %d, dilation %d",
+                  a->out_dims[i], i, a->in_dims[i], a->ksize[i], a->stride[i], a->pad[i], a->dil[i]);
+    g.in_dims[i] = a->in_dims[i];
+    g.out_dims[i] = a->out_dims[i];
+    g.ksize[i] = a->ksize[i];
+    g.stride[i] = a->stride[i];
+    g.pad[i] = a->pad[i];
+    g.dil[i] = a->dil[i];
+    n_in *= a->in_dims[i];
+    n_out *= a->out_dims[i];
+    kv *= a->ksize[i];
+  }
+  CB2_CHECK_RT(kv <= 128, "kernel volume %lld: the kernels handle up to 128 filter offsets", kv);
+  CB2_CHECK_RT(n_in < (1ll << 31) && n_out < (1ll << 31), "too many rows for 32-bit row indices");
+  CB2_CHECK_RT(a->indices_fwd != nullptr, "error: indices empty");
+  g.kv = (int)kv;
+  const int words = ((int)kv + 31) / 32;
+  auto blocks = [](long long n) { return (unsigned)((n + 255) / 256); };
+  cb2pg::dense_table_fwd_kernel<<<blocks(n_out * kv), 256, 0, stream>>>(g, n_out, a->indices_fwd);
+  g_launches.fetch_add(1);
+  if (a->indices_bwd) {
+    cb2pg::dense_table_bwd_kernel<<<blocks(n_in * kv), 256, 0, stream>>>(g, n_in, a->indices_bwd);
+    g_launches.fetch_add(1);
+  }
+  if (a->mask_fwd && a->argsort_fwd) {
+    cb2pg::dense_masks_kernel<<<blocks(n_out), 256, 0, stream>>>(n_out, (int)kv, words, a->mask_fwd, a->argsort_fwd);
+    g_launches.fetch_add(1);
+  }
+  if (a->mask_bwd && a->argsort_bwd) {
+    cb2pg::dense_masks_kernel<<<blocks(n_in), 256, 0, stream>>>(n_in, (int)kv, words, a->mask_bwd, a->argsort_bwd);
+    g_launches.fetch_add(1);
+  }
+  CB2_CUDA(cudaGetLastError());
+  return CB2_OK;
+}
+
 // ---------------------------------------------------------------- sum over GPUs through peer memory
 struct PeerLayout {
   long long shard_f4, shard_bytes, result_bytes;

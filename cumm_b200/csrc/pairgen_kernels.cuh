@@ -228,6 +228,87 @@ constexpr int kSortThreads = 256;
 constexpr int kSortItems = 8;
 constexpr int kSortTile = kSortThreads * kSortItems;
 
+// Neighbour tables of a DENSE convolution (every grid position is a row, channels last): the
+// coordinate rule of the reference's dense iterators, in = out * stride - pad + r * dilation per
+// axis (cumm/conv/input_iters.py:2666,2684), written in the layout the row-gather kernels read.
+// With them a dense convolution runs through the same kernels as a sparse one whose voxels fill
+// the grid.  One thread per (row, filter offset); rows are (batch, z, y, x) row-major.
+struct DenseGeometry {
+  int batch;
+  int in_dims[3], out_dims[3];
+  int ksize[3], stride[3], pad[3], dil[3];
+  int kv;
+};
+// forward: indices[f, o] = input row feeding output row o through offset f, or -1
+__global__ void __launch_bounds__(256) dense_table_fwd_kernel(DenseGeometry g, long long n_out, int32_t *__restrict__ indices) {
+  const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n_out * g.kv)
+    return;
+  const int f = (int)(t / n_out);
+  const long long o = t % n_out;
+  long long rem = o;
+  int oc[3];
+  for (int a = 2; a >= 0; --a) {
+    oc[a] = (int)(rem % g.out_dims[a]);
+    rem /= g.out_dims[a];
+  }
+  const long long b = rem;
+  int r[3], fr = f;
+  for (int a = 2; a >= 0; --a) {
+    r[a] = fr % g.ksize[a];
+    fr /= g.ksize[a];
+  }
+  long long row = b;
+  bool ok = true;
+  for (int a = 0; a < 3; ++a) {
+    const int ic = oc[a] * g.stride[a] - g.pad[a] + r[a] * g.dil[a];
+    ok = ok && ic >= 0 && ic < g.in_dims[a];
+    row = row * g.in_dims[a] + ic;
+  }
+  indices[t] = ok ? (int32_t)row : -1;
+}
+// backward: indices[f, i] = output row that input row i feeds through offset f, or -1
+__global__ void __launch_bounds__(256) dense_table_bwd_kernel(DenseGeometry g, long long n_in, int32_t *__restrict__ indices) {
+  const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n_in * g.kv)
+    return;
+  const int f = (int)(t / n_in);
+  const long long i = t % n_in;
+  long long rem = i;
+  int ic[3];
+  for (int a = 2; a >= 0; --a) {
+    ic[a] = (int)(rem % g.in_dims[a]);
+    rem /= g.in_dims[a];
+  }
+  const long long b = rem;
+  int r[3], fr = f;
+  for (int a = 2; a >= 0; --a) {
+    r[a] = fr % g.ksize[a];
+    fr /= g.ksize[a];
+  }
+  long long row = b;
+  bool ok = true;
+  for (int a = 0; a < 3; ++a) {
+    const int num = ic[a] + g.pad[a] - r[a] * g.dil[a];
+    const int oc = num / g.stride[a];
+    ok = ok && num >= 0 && num % g.stride[a] == 0 && oc < g.out_dims[a];
+    row = row * g.out_dims[a] + oc;
+  }
+  indices[t] = ok ? (int32_t)row : -1;
+}
+// every row carries every offset (the table says which neighbours exist); rows keep their order
+__global__ void __launch_bounds__(256) dense_masks_kernel(long long n, int kv, int words, uint32_t *__restrict__ mask,
+                                                          int32_t *__restrict__ argsort) {
+  const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n)
+    return;
+  argsort[t] = (int32_t)t;
+  for (int w = 0; w < words; ++w) {
+    const int left = kv - 32 * w;
+    mask[t * words + w] = left >= 32 ? 0xffffffffu : (1u << left) - 1u;
+  }
+}
+
 // OR of the neighbour masks of each run of 128 sorted rows: what the forward kernel reports per
 // row tile and the weight gradient reads as its reduced masks.  One warp per tile.
 __global__ void __launch_bounds__(256) tile_masks_kernel(const uint32_t *__restrict__ sorted_mask, int n,

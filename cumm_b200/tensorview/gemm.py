@@ -618,7 +618,8 @@ def _conv_args(params: ConvParams) -> _lib.ConvArgs:
     desp = params.conv_algo_desp
     desp.check_valid()
     if not desp.mask_sparse:
-        raise RuntimeError("can't find any suitable algo: only mask-sparse implicit GEMM is built")
+        raise RuntimeError("a dense convolution has no flat argument record of its own: run_conv routes it "
+                           "through cumm_b200.dense")
     inp, weight, output = as_view(params.input), as_view(params.weight), as_view(params.output)
     if inp is None or weight is None or output is None:
         raise RuntimeError("input, weight, output must not empty")
@@ -737,6 +738,10 @@ def _conv_args(params: ConvParams) -> _lib.ConvArgs:
 
 def run_conv(params: ConvParams) -> None:
     """What ``ConvMainUnitTest.implicit_gemm2`` does (cumm/conv/main.py:485-745)."""
+    if not params.conv_algo_desp.mask_sparse:
+        # dense convolution: the same kernels over the neighbour table of the full grid
+        from ..dense import run_dense_conv
+        return run_dense_conv(params)
     L = _lib.load()
     args = _conv_args(params)
     need = L.cb2_conv_workspace_size(ctypes.byref(args))

@@ -200,15 +200,16 @@ size_t cb2_conv_workspace_size(const cb2_conv_args *args);
  * part of the library image (cb2_static_scratch_bytes()).  Every GPU that loads the library
  * holds that array until the process exits.
  *
- *  - Problems whose scratch does not fit (roughly K * C > 128 * 128 on a 148-SM part, or more
- *    than about five million rows at K = C = 128: the scratch also holds the per-offset lists of
- *    row tiles) are refused with CB2_ERR_RUNTIME and a message naming both sizes; nothing is
- *    launched.
+ *  - Problems whose scratch does not fit (K * C of 256 * 256 and beyond on a 148-SM part, or
+ *    more than about five million rows at K = C = 128: the scratch holds one partial sum per
+ *    unit of work and the per-offset lists of row tiles) are refused with CB2_ERR_RUNTIME and a
+ *    message naming both sizes; nothing is launched.
  *  - The first call on each device resolves the array's device address.  That one call
  *    should be made before any stream capture begins on that device.
- *  - All calls share the one array and it keeps the previous call's contents; the kernels
- *    rewrite every word they later read, so no clearing is needed between calls, but two
- *    calls that overlap on the same GPU (different streams, no ordering) race on it.
+ *  - All calls share the one array and it keeps the previous call's contents; every call
+ *    clears the control words it uses and rewrites every partial sum it later reads, so nothing
+ *    has to be cleared between calls, but two calls that overlap on the same GPU (different
+ *    streams, no ordering) race on it.
  *  - Neither this call nor anything it calls uses cudaMalloc, cudaFree or an allocating
  *    library routine.  Its kernels report through their own status word:
  *    cb2_static_status() is to this entry point what cb2_device_status() is to the others.
@@ -263,6 +264,29 @@ typedef struct cb2_pairgen_args {
 size_t cb2_pairgen_workspace_size(const cb2_pairgen_args *args);
 int cb2_pairgen_count_outputs(const cb2_pairgen_args *args, int *n_out, void *stream);
 int cb2_pairgen_run(const cb2_pairgen_args *args, void *stream);
+
+/*
+ * Neighbour tables of a DENSE (non-mask) convolution, channels last: with them the dense
+ * convolutions of the reference (ConvAlgoDesp::mask_sparse == false; cumm/conv/input_iters.py:2353,
+ * harness cumm/conv/main_real.py:41-231) run through cb2_conv_run like a sparse convolution whose
+ * voxels fill the grid.  Rows are (batch, z, y, x) row-major; unused leading axes have extent 1.
+ * Coordinate rule: in = out * stride - pad + r * dilation per axis (cumm/conv/input_iters.py:2666,2684).
+ * indices_fwd [kv, n_out] (forward, backward weight), indices_bwd [kv, n_in] (backward input; may be
+ * null), mask_* [rows, ceil(kv / 32)] all-ones masks and identity orders for each direction (may be null).
+ */
+typedef struct cb2_dense_tables_args {
+  int batch;
+  int in_dims[3], out_dims[3]; /* (z, y, x) */
+  int ksize[3], stride[3], pad[3], dil[3];
+  int32_t *indices_fwd;
+  int32_t *indices_bwd;
+  uint32_t *mask_fwd;
+  int32_t *argsort_fwd;
+  uint32_t *mask_bwd;
+  int32_t *argsort_bwd;
+} cb2_dense_tables_args;
+
+int cb2_dense_tables_run(const cb2_dense_tables_args *args, void *stream);
 
 /*
  * Sum of one fp32 array per GPU over NVLink peer memory, for the weight gradient of a
