@@ -44,6 +44,9 @@ L2_BYTES = 126 * 1024 * 1024
 # SM shares of the three kernels when they run side by side (forward, backward input, backward
 # weight); the weight gradient moves the same bytes with more steps per row tile.
 SHARES = tuple(int(v) for v in os.environ.get("CUMM_B200_BENCH_SHARES", "48,48,52").split(","))
+# Several GPUs: the weight gradient runs first on the whole GPU, then forward and backward input side
+# by side on these shares while the exchange runs on the SMs they leave free.
+PAIR_SHARES = tuple(int(v) for v in os.environ.get("CUMM_B200_BENCH_PAIR_SHARES", "68,68").split(","))
 
 
 def host_features(n_in, n_out, seed):
@@ -316,7 +319,10 @@ def main():
             dw = dw32 if world > 1 else dw16
             alone = SparseConvLayer(t, w_d, x, out, dout, din, dw, stream=stream.cuda_stream)
             shared = SparseConvLayer(t, w_d, x, out, dout, din, dw, stream=stream.cuda_stream, cta_shares=shares)
-            sets.append(dict(t=t, x=x, dout=dout, out=out, din=din, dw32=dw32, dw16=dw16, alone=alone, shared=shared))
+            pair = SparseConvLayer(t, w_d, x, out, dout, din, None, stream=stream.cuda_stream,
+                                   cta_shares={ConvOpType.Forward: PAIR_SHARES[0], ConvOpType.BackwardInput: PAIR_SHARES[1]})
+            sets.append(dict(t=t, x=x, dout=dout, out=out, din=din, dw32=dw32, dw16=dw16, alone=alone, shared=shared,
+                             pair=pair))
     stream.synchronize()
 
     ev = lambda: torch.cuda.Event(enable_timing=True)
@@ -331,6 +337,8 @@ def main():
             try:
                 from cumm_b200.peer_allreduce import PeerAllReduce
                 peer_ar = PeerAllReduce.over_process_group(C_OUT * KV * C_IN, dev)
+                # its CTAs go to the SMs the convolution kernels leave free, not beside them
+                peer_ar.own_sm_smem_bytes = 16 * 1024
                 ok = 1
             except Exception as e:  # noqa: BLE001 - any set-up failure means: use NCCL, and say so
                 print(f"[rank {rank}] peer-memory sum unavailable ({e!r}); using NCCL", file=sys.stderr, flush=True)
@@ -365,17 +373,28 @@ def main():
             events[4].record(stream)
 
     def step_branches(s):
-        """The step as three branches: forward on the main stream, input gradient and weight
-        gradient (followed by the exchange) on two others, joined at the end."""
-        L = s["shared"]
+        """One GPU: the step as three branches: forward on the main stream, input gradient and
+        weight gradient on two others, joined at the end.  Several GPUs: the weight gradient first,
+        on the whole GPU, then three branches: the exchange of its partial sums, forward and
+        input gradient (the two convolutions leave the exchange a few SMs of its own)."""
         s_dgrad.wait_stream(stream)
         s_wgrad.wait_stream(stream)
-        L.fwd.launch()
-        with torch.cuda.stream(s_wgrad):
-            L.wgrad.launch(s_wgrad.cuda_stream)
-            exchange(s, s_wgrad.cuda_stream)
-        with torch.cuda.stream(s_dgrad):
-            L.dgrad.launch(s_dgrad.cuda_stream)
+        if world == 1:
+            L = s["shared"]
+            L.fwd.launch()
+            with torch.cuda.stream(s_wgrad):
+                L.wgrad.launch(s_wgrad.cuda_stream)
+            with torch.cuda.stream(s_dgrad):
+                L.dgrad.launch(s_dgrad.cuda_stream)
+        else:
+            s["alone"].wgrad.launch()
+            s_dgrad.wait_stream(stream)
+            s_wgrad.wait_stream(stream)
+            with torch.cuda.stream(s_wgrad):
+                exchange(s, s_wgrad.cuda_stream)
+            s["pair"].fwd.launch()
+            with torch.cuda.stream(s_dgrad):
+                s["pair"].dgrad.launch(s_dgrad.cuda_stream)
         stream.wait_stream(s_dgrad)
         stream.wait_stream(s_wgrad)
 
@@ -569,7 +588,10 @@ def main():
         run.update({
             "l2": f"rotating {nsets} buffer sets ({nsets * step_bytes / 1e6:.0f} MB touched) > 126 MB L2",
             "schedule": (f"one CUDA graph per step, three branches side by side (max_ctas {SHARES[0]}/{SHARES[1]}/{SHARES[2]}: "
-                         "forward / backward input / backward weight)" if concurrent and one_graph else
+                         "forward / backward input / backward weight)" if concurrent and one_graph and world == 1 else
+                         f"one CUDA graph per step: backward weight on the whole GPU, then forward / backward input side by "
+                         f"side (max_ctas {PAIR_SHARES[0]}/{PAIR_SHARES[1]}) with the exchange on the SMs they leave free"
+                         if concurrent and one_graph else
                          "one CUDA graph per step, operators one after the other" if one_graph else
                          "graph(fwd+wgrad), then NCCL all-reduce + cast eagerly on a side stream overlapped with graph(dgrad)"),
             "exchange": exchange_kind if world > 1 else "none (one GPU)",
@@ -922,14 +944,14 @@ def config1_gather_gemm(torch, dev, stream, coords, time_calls, peak, nsets):
         if len(o_idx):
             pairs.append((f, tb.indices[f][o_idx].astype(np.int32), o_idx))
     n_pairs = sum(len(o) for _, _, o in pairs)
-    sequences = []
+    sequences, param_sets = [], []
     with torch.cuda.stream(stream):
         w = torch.from_numpy(wh).to(dev)
         idx_dev = [(f, torch.from_numpy(i).to(dev), torch.from_numpy(o).to(dev)) for f, i, o in pairs]
         for _ in range(nsets):
             x = torch.from_numpy(xh).to(dev)
             out = torch.zeros((tb.n_out, K), dtype=torch.float16, device=dev)
-            calls = []
+            calls, plist = [], []
             for f, i_idx, o_idx in idx_dev:
                 p = GemmParams()
                 p.algo_desp = d
@@ -938,7 +960,9 @@ def config1_gather_gemm(torch, dev, stream, coords, time_calls, peak, nsets):
                 p.beta = 1.0
                 p.stream = stream.cuda_stream
                 calls.append(prepare_gemm(p))
+                plist.append(p)
             sequences.append(calls)
+            param_sets.append(plist)
     stream.synchronize()
 
     class Sequence:
@@ -951,8 +975,19 @@ def config1_gather_gemm(torch, dev, stream, coords, time_calls, peak, nsets):
 
     us = time_calls([Sequence(c) for c in sequences])
     nbytes = tb.n_in * C * 2 + tb.n_out * K * 2 + 27 * C * K * 2 + 8 * n_pairs
-    return {"us": us, "calls": len(pairs), "pairs": int(n_pairs), "eff_tflops": 2 * n_pairs * C * K / us / 1e6,
-            "gbs": nbytes / us / 1e3, "frac_hbm_measured": nbytes / us / 1e3 / peak}
+    res = {"us": us, "calls": len(pairs), "pairs": int(n_pairs), "eff_tflops": 2 * n_pairs * C * K / us / 1e6,
+           "gbs": nbytes / us / 1e3, "frac_hbm_measured": nbytes / us / 1e3 / peak}
+    # the same calls handed over as one layer (cb2_gemm_sequence_run): one launch over a neighbour
+    # table scattered from the pair lists (built on the first launch, outside the timed replays)
+    from cumm_b200.sequence import prepare_gemm_sequence
+    with torch.cuda.stream(stream):
+        one = [prepare_gemm_sequence(params, stream=stream.cuda_stream) for params in param_sets]
+    stream.synchronize()
+    us1 = time_calls(one)
+    res["one_launch"] = {"us": us1, "eff_tflops": 2 * n_pairs * C * K / us1 / 1e6, "gbs": nbytes / us1 / 1e3,
+                         "frac_hbm_measured": nbytes / us1 / 1e3 / peak,
+                         "what": "the 27 GemmParams of the layer through cb2_gemm_sequence_run (tables reused)"}
+    return res
 
 
 if __name__ == "__main__":

@@ -40,6 +40,8 @@ EXPORTED_SYMBOLS = (
     "cb2_enumerate_conv_desps",
     "cb2_last_launch_info",
     "cb2_dense_tables_run",
+    "cb2_gemm_sequence_workspace_size",
+    "cb2_gemm_sequence_run",
 )
 
 
@@ -126,6 +128,18 @@ class PairgenArgs(ctypes.Structure):
     ]
 
 
+class GemmSequenceArgs(ctypes.Structure):
+    """``cb2_gemm_sequence_args``."""
+    _fields_ = [
+        ("calls", ctypes.POINTER(GemmArgs)),
+        ("count", ctypes.c_int),
+        ("n_out_rows", ctypes.c_int),
+        ("workspace", ctypes.c_void_p),
+        ("workspace_bytes", ctypes.c_size_t),
+        ("reuse_tables", ctypes.c_int),
+    ]
+
+
 class KernelDesp(ctypes.Structure):
     """``cb2_kernel_desp``."""
     _fields_ = [
@@ -165,6 +179,7 @@ class PeerAllreduceArgs(ctypes.Structure):
         ("out_f16", ctypes.c_void_p),
         ("numel", ctypes.c_longlong),
         ("timeout_ns", ctypes.c_ulonglong),
+        ("own_sm_smem_bytes", ctypes.c_int),
     ]
 
 
@@ -212,6 +227,10 @@ def load() -> ctypes.CDLL:
     for fn in (L.cb2_enumerate_gemm_desps, L.cb2_enumerate_conv_desps):
         fn.restype = ctypes.c_int
         fn.argtypes = [ctypes.POINTER(KernelDesp), ctypes.c_int]
+    L.cb2_gemm_sequence_workspace_size.restype = ctypes.c_size_t
+    L.cb2_gemm_sequence_workspace_size.argtypes = [ctypes.POINTER(GemmSequenceArgs)]
+    L.cb2_gemm_sequence_run.restype = ctypes.c_int
+    L.cb2_gemm_sequence_run.argtypes = [ctypes.POINTER(GemmSequenceArgs), ctypes.c_void_p]
     L.cb2_dense_tables_run.restype = ctypes.c_int
     L.cb2_dense_tables_run.argtypes = [ctypes.POINTER(DenseTablesArgs), ctypes.c_void_p]
     L.cb2_last_launch_info.restype = ctypes.c_int

@@ -740,6 +740,134 @@ int cb2_pairgen_run(const cb2_pairgen_args *a, void *stream_v) {
   return CB2_OK;
 }
 
+// ---------------------------------------------------------------- a layer's ShuffleAC calls in one launch
+struct SeqLayout {
+  size_t off_table, off_mask, off_argsort, off_m, off_v, off_hist, off_tickets, total;
+};
+static void seq_layout(int count, long long n, SeqLayout *L) {
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    const size_t at = off;
+    off = align256(off + bytes);
+    return at;
+  };
+  L->off_tickets = take(256);
+  L->off_table = take(static_cast<size_t>(count) * n * 4);
+  L->off_mask = take(static_cast<size_t>(n) * 4);
+  L->off_argsort = take(static_cast<size_t>(n) * 4);
+  L->off_m = take(static_cast<size_t>(n) * 4);
+  L->off_v = take(static_cast<size_t>(n) * 4);
+  L->off_hist = take(static_cast<size_t>(256) * ((n + cb2pg::kSortTile - 1) / cb2pg::kSortTile + 1) * 4);
+  L->total = off;
+}
+
+size_t cb2_gemm_sequence_workspace_size(const cb2_gemm_sequence_args *a) {
+  if (!a || a->count < 1 || a->count > cb2pg::kSeqMaxCalls || a->n_out_rows < 0)
+    return 0;
+  SeqLayout L;
+  seq_layout(a->count, a->n_out_rows, &L);
+  return L.total;
+}
+
+int cb2_gemm_sequence_run(const cb2_gemm_sequence_args *a, void *stream_v) {
+  CB2_CHECK_ARG(a != nullptr && a->calls != nullptr, "null arguments");
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  DeviceState *dev;
+  int rc = get_device(&dev);
+  if (rc)
+    return rc;
+  CB2_CHECK_ARG(a->count >= 1 && a->count <= cb2pg::kSeqMaxCalls, "a sequence holds 1 to %d calls", cb2pg::kSeqMaxCalls);
+  CB2_CHECK_ARG(a->n_out_rows >= 0, "negative row count");
+  const cb2_gemm_args &c0 = a->calls[0];
+  CB2_CHECK_RT(c0.ptr_A && c0.ptr_B && c0.ptr_C, "a,b,c must not empty");
+  CB2_CHECK_RT(kind_of(c0.dtype_a, c0.dtype_b, c0.dtype_c, 0, false) == 0,
+               "can't find any suitable algo for dtypes (%d,%d,%d): only f16,f16,f16 is built", c0.dtype_a, c0.dtype_b,
+               c0.dtype_c);
+  CB2_CHECK_ARG(c0.k % 8 == 0 && c0.n % 8 == 0, "this m, n, k isn't supported due to misaligned contiguous dim.");
+  // what makes the calls one layer
+  const long long b_step = a->count > 1 ? (reinterpret_cast<const char *>(a->calls[1].ptr_B) -
+                                           reinterpret_cast<const char *>(c0.ptr_B))
+                                        : 0;
+  cb2pg::SeqPairLists lists;
+  memset(&lists, 0, sizeof(lists));
+  lists.count = a->count;
+  for (int f = 0; f < a->count; ++f) {
+    const cb2_gemm_args &c = a->calls[f];
+    const bool same = c.shuffle_type == CB2_SHUFFLE_AC && !c.trans_a && !c.trans_c && c.trans_b == c0.trans_b &&
+                      c.ptr_A == c0.ptr_A && c.stride_A == c0.stride_A && c.rows_A == c0.rows_A && c.ptr_C == c0.ptr_C &&
+                      c.stride_C == c0.stride_C && (c.ptr_D == nullptr || c.ptr_D == c.ptr_C) && !c.d_is_vector &&
+                      c.n == c0.n && c.k == c0.k && c.stride_B == c0.stride_B && c.alpha == 1.f && c.beta == 1.f &&
+                      c.act_type == CB2_ACT_NONE && c.dtype_a == c0.dtype_a && c.dtype_b == c0.dtype_b &&
+                      c.dtype_c == c0.dtype_c && c.m >= 0 && c.indiceBorC != nullptr &&
+                      reinterpret_cast<const char *>(c.ptr_B) - reinterpret_cast<const char *>(c0.ptr_B) == f * b_step;
+    if (!same)
+      return set_err(CB2_ERR_UNSUPPORTED,
+                     "call %d of the sequence does not fit the layer form (ShuffleAC, shared A and C, alpha = beta = 1, "
+                     "no activation, equally spaced B): run the calls one by one",
+                     f);
+    lists.a_inds[f] = c.indiceA;
+    lists.c_inds[f] = c.indiceBorC;
+    lists.first[f + 1] = lists.first[f] + c.m;
+  }
+  CB2_CHECK_RT(b_step % 2 == 0 && b_step >= 0, "B matrices must be ascending slices of one tensor");
+  const int n = a->n_out_rows;
+  if (n == 0)
+    return CB2_OK;
+  SeqLayout L;
+  seq_layout(a->count, n, &L);
+  CB2_CHECK_RT(a->workspace != nullptr && a->workspace_bytes >= L.total, "workspace at least %zu bytes.", L.total);
+  CB2_CHECK_ARG(reinterpret_cast<uintptr_t>(a->workspace) % 256 == 0, "workspace must be 256-byte aligned");
+  uint8_t *ws = reinterpret_cast<uint8_t *>(a->workspace);
+  int32_t *table = reinterpret_cast<int32_t *>(ws + L.off_table);
+  uint32_t *mask = reinterpret_cast<uint32_t *>(ws + L.off_mask);
+  int32_t *argsort = reinterpret_cast<int32_t *>(ws + L.off_argsort);
+  if (!a->reuse_tables) {
+    uint32_t *m_tmp = reinterpret_cast<uint32_t *>(ws + L.off_m);
+    int *v_tmp = reinterpret_cast<int *>(ws + L.off_v);
+    CB2_CUDA(cudaMemsetAsync(ws + L.off_tickets, 0, 256, stream));
+    CB2_CUDA(cudaMemsetAsync(table, 0xFF, static_cast<size_t>(a->count) * n * 4, stream));
+    const long long pairs = lists.first[a->count];
+    if (pairs > 0)
+      cb2pg::seq_scatter_kernel<<<static_cast<unsigned>((pairs + 255) / 256), 256, 0, stream>>>(lists, n, c0.rows_A, table,
+                                                                                              dev->status);
+    cb2pg::mask_from_table_kernel<<<(n + 255) / 256, 256, 0, stream>>>(table, n, a->count, sort_source(mask, m_tmp, a->count),
+                                                                        sort_source(argsort, v_tmp, a->count));
+    CB2_CUDA(cudaGetLastError());
+    g_launches.fetch_add(2);
+    rc = radix_sort<uint32_t, true>(mask, argsort, m_tmp, v_tmp, n, a->count, reinterpret_cast<int *>(ws + L.off_hist), stream);
+    if (rc)
+      return rc;
+  }
+  RowConvParams p;
+  memset(&p, 0, sizeof(p));
+  p.a = c0.ptr_A;
+  p.out = c0.ptr_C;
+  p.indices = table;
+  p.mask = mask;
+  p.argsort = argsort;
+  p.n_rows = n;
+  p.a_rows = c0.rows_A;
+  p.red = c0.k;
+  p.nn = c0.n;
+  p.lda = c0.stride_A;
+  p.ldo = c0.stride_C;
+  p.kv = a->count;
+  p.mask_words = 1;
+  p.mode = kModeMaskConv;
+  p.mask_filter = 0xffffffffu;
+  p.alpha = 1.f;
+  p.beta = 1.f;
+  p.src = c0.ptr_C;
+  p.src_mode = kSrcRows;
+  p.lds = c0.stride_C;
+  // the weight tensor as [outer, f, inner]: B_f is [n, k] (trans_b) or [k, n]
+  const bool b_mn = !c0.trans_b;
+  const uint64_t inner = b_mn ? c0.n : c0.k, outer = b_mn ? c0.k : c0.n;
+  const uint64_t f_stride = a->count > 1 ? static_cast<uint64_t>(b_step / 2) : inner;
+  return run_rowconv(dev, p, 0, b_mn, c0.tile_n, c0.tile_k, ws + L.off_tickets, c0.max_ctas, c0.ptr_B, inner, a->count, outer,
+                     f_stride, c0.stride_B, stream);
+}
+
 // ---------------------------------------------------------------- tables of a dense convolution
 int cb2_dense_tables_run(const cb2_dense_tables_args *a, void *stream_v) {
   CB2_CHECK_ARG(a != nullptr, "null arguments");
@@ -857,7 +985,8 @@ int cb2_peer_allreduce(const cb2_peer_allreduce_args *a, void *stream_v) {
   }();
   int grid = static_cast<int>(std::min<long long>((a->numel / 4 + cb2::kPeerThreads - 1) / cb2::kPeerThreads, max_grid));
   grid = std::max(1, std::min(grid, dev->num_sms));
-  cb2::peer_reduce_kernel<<<grid, cb2::kPeerThreads, 0, stream>>>(p);
+  CB2_CHECK_ARG(a->own_sm_smem_bytes >= 0 && a->own_sm_smem_bytes <= 48 * 1024, "own_sm_smem_bytes must be 0 .. 48 KiB");
+  cb2::peer_reduce_kernel<<<grid, cb2::kPeerThreads, static_cast<size_t>(a->own_sm_smem_bytes), stream>>>(p);
   CB2_CUDA(cudaGetLastError());
   g_launches.fetch_add(1);
   return CB2_OK;

@@ -220,6 +220,34 @@ __global__ void __launch_bounds__(256) mask_from_table_kernel(const int32_t *__r
   iota[j] = j;
 }
 
+// A sequence of gather-GEMM-scatter calls (one per filter offset, each with its own pair lists)
+// turned into the neighbour table of ONE convolution: table[f, c_inds_f[i]] = a_inds_f[i].
+// One thread per pair; `first[f]` = pairs before call f.
+constexpr int kSeqMaxCalls = 32;
+struct SeqPairLists {
+  const int32_t *a_inds[kSeqMaxCalls];  // null = the pair's own position
+  const int32_t *c_inds[kSeqMaxCalls];
+  long long first[kSeqMaxCalls + 1];
+  int count;
+};
+__global__ void __launch_bounds__(256) seq_scatter_kernel(SeqPairLists L, int n_out, int a_rows, int32_t *__restrict__ table,
+                                                          int *status) {
+  const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= L.first[L.count])
+    return;
+  int f = 0;
+  while (f + 1 < L.count && t >= L.first[f + 1])
+    ++f;
+  const long long i = t - L.first[f];
+  const int o = L.c_inds[f][i];
+  const int a = L.a_inds[f] ? L.a_inds[f][i] : (int)i;
+  if (o < 0 || o >= n_out || a < 0 || a >= a_rows) {
+    atomicCAS(status, 0, 2);  // row index out of range: reported, not dereferenced
+    return;
+  }
+  table[(long long)f * n_out + o] = a;
+}
+
 // ---------------------------------------------------------------- stable LSD radix sort, 8 bits per pass
 // Three kernels per pass: per-tile digit histograms, one exclusive scan over the (digit, tile)
 // matrix, and a scatter in which the warps of a block take turns (in element order) to claim

@@ -19,13 +19,16 @@ class PeerAllReduce:
     captured in a CUDA graph: the call number that pairs the ranks' calls lives in the buffers."""
 
     def __init__(self, numel: int, rank: int, world: int, peer_ptrs: Sequence[int], keep=None,
-                 timeout_ns: int = 0):
+                 timeout_ns: int = 0, own_sm_smem_bytes: int = 0):
         if numel % 4:
             raise ValueError("numel must be a multiple of 4")
         self.numel, self.rank, self.world = int(numel), int(rank), int(world)
         self._ptrs = (ctypes.c_void_p * world)(*[int(p) for p in peer_ptrs])
         self._keep = keep
         self._timeout_ns = int(timeout_ns)
+        # see cb2_peer_allreduce_args.own_sm_smem_bytes: keeps the kernel's CTAs off SMs that
+        # persistent convolution kernels occupy
+        self.own_sm_smem_bytes = int(own_sm_smem_bytes)
         self._L = _lib.load()
 
     @staticmethod
@@ -61,6 +64,7 @@ class PeerAllReduce:
         a.out_f32 = out_f32.data_ptr() if out_f32 is not None else None
         a.out_f16 = out_f16.data_ptr() if out_f16 is not None else None
         a.numel, a.timeout_ns = self.numel, self._timeout_ns
+        a.own_sm_smem_bytes = self.own_sm_smem_bytes
         _lib.raise_for(self._L.cb2_peer_allreduce(ctypes.byref(a), ctypes.c_void_p(int(stream))))
 
     def last_call_ns(self):

@@ -181,6 +181,36 @@ typedef struct cb2_conv_args {
 int cb2_gemm_run(const cb2_gemm_args *args, void *stream);
 int cb2_conv_run(const cb2_conv_args *args, void *stream);
 
+/*
+ * A layer's sequence of ShuffleAC calls in one launch.  (No counterpart in the reference, whose
+ * callers launch one GemmParams per filter offset: cumm/gemm/main_real.py:196-232.)
+ *
+ * `calls[0 .. count)`, count <= 32, are what the caller would pass to cb2_gemm_run one after the
+ * other for the filter offsets of one sparse-convolution layer: the same A (ptr_A, stride_A,
+ * rows_A), the same C = D (ptr_C, stride_C) with beta = 1 and alpha = 1 (every call accumulates
+ * into the output), no activation, and B matrices that are equally spaced slices of one weight
+ * tensor (ptr_B of call f = ptr_B of call 0 + f * a constant; same stride_B, trans_b, n, k).
+ * Within one call the c_inds are distinct.  The pair lists are scattered into the neighbour
+ * table of one convolution (in the workspace: table, masks, sort order) and the layer runs as one
+ * mask-convolution launch: out[o] = fp16(out[o] + sum_f A[a_f(o)] B_f), summed in fp32 and
+ * rounded once, where the call-by-call sequence rounds to fp16 after every call -- the results
+ * agree to a few fp16 ulps, not bit for bit.  `n_out_rows`: rows of C.  `reuse_tables`: the
+ * workspace still holds the tables of an earlier call with the same pair lists (they depend on
+ * the lists only: build once per scene).  Calls that do not fit these rules are refused with
+ * CB2_ERR_UNSUPPORTED and nothing is launched: run them one by one.
+ */
+typedef struct cb2_gemm_sequence_args {
+  const cb2_gemm_args *calls;
+  int count;
+  int n_out_rows;
+  void *workspace; /* at least cb2_gemm_sequence_workspace_size() bytes, 256-byte aligned */
+  size_t workspace_bytes;
+  int reuse_tables;
+} cb2_gemm_sequence_args;
+
+size_t cb2_gemm_sequence_workspace_size(const cb2_gemm_sequence_args *args);
+int cb2_gemm_sequence_run(const cb2_gemm_sequence_args *args, void *stream);
+
 /* Bytes of scratch the call needs in args->workspace (0 when none).  Replaces
  * GemmAlgoDesp::query_workspace_size / ConvAlgoDesp::query_conv_workspace_size
  * (include/tensorview/gemm/core/params.h:115-132,286-307); unlike the reference the
@@ -313,6 +343,10 @@ typedef struct cb2_peer_allreduce_args {
   void *out_f16;   /* may be null */
   long long numel; /* multiple of 4 */
   unsigned long long timeout_ns;
+  int own_sm_smem_bytes; /* 0, or dynamic shared memory to request per CTA (unused by the kernel): a value above
+                            what the persistent convolution kernels leave free on an SM (about 11 KB) keeps this
+                            kernel's CTAs off the SMs those kernels occupy, so that they run at full speed on the
+                            SMs a caller left free (max_ctas of the convolution calls) instead of beside them */
 } cb2_peer_allreduce_args;
 
 size_t cb2_peer_allreduce_buffer_size(long long numel, int world);

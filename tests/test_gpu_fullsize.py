@@ -128,3 +128,32 @@ def test_native_conv_as_27_gemm_calls_150k(torch, oracle, scene):
     err = np.abs(out.cpu().numpy().astype(np.float32) - want)
     tol = 2e-2 + 1e-2 * np.abs(want)
     assert (err <= tol).all(), f"{int((err > tol).sum())} entries outside tolerance, max abs err {err.max():.4g}"
+
+
+def test_layer_sequence_one_launch_150k(torch, oracle, scene):
+    """The same layer through cb2_gemm_sequence_run: all 27 calls as one launch."""
+    from cumm_b200.sequence import prepare_gemm_sequence
+    from cumm_b200.tensorview.gemm import GemmParams, ShuffleStrideType
+    _, tb = scene
+    C = K = 64
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((tb.n_in, C), dtype=np.float32).astype(np.float16)
+    w = (rng.standard_normal((K, 27, C), dtype=np.float32) / np.sqrt(27 * C)).astype(np.float16)
+    xd, wd = H.dev(x, torch), H.dev(w, torch)
+    out = torch.zeros((tb.n_out, K), dtype=torch.float16, device="cuda")
+    calls = []
+    for f in range(27):
+        o_idx = np.nonzero(tb.indices[f] >= 0)[0].astype(np.int32)
+        if len(o_idx) == 0:
+            continue
+        p = GemmParams()
+        p.algo_desp = H.gemm_desp(ShuffleStrideType.ShuffleAC, n=K, k=C)
+        p.a, p.b, p.c = xd, wd[:, f, :], out
+        p.a_inds, p.c_inds = H.dev(tb.indices[f][o_idx], torch), H.dev(o_idx, torch)
+        p.beta = 1.0
+        calls.append(p)
+    assert len(calls) == 27
+    prepare_gemm_sequence(calls).launch()
+    torch.cuda.synchronize()
+    H.check_status()
+    H.assert_close_f16(out.cpu().numpy(), oracle.np_forward(x, w, tb.indices), "27 calls in one launch")

@@ -204,3 +204,75 @@ def test_unknown_tile_shape_is_refused(torch):
     p.a_inds = p.c_inds = torch.arange(10, dtype=torch.int32, device="cuda")
     with pytest.raises(RuntimeError, match="can't find any suitable algo"):
         GemmMainUnitTest.matmul2(p)
+
+
+def _layer_as_calls(torch, tb, x, w, out):
+    """The GemmParams of a native sparse convolution: one ShuffleAC call per filter offset with pairs."""
+    xd, wd = H.dev(x, torch), H.dev(w, torch)
+    K, C = w.shape[0], w.shape[2]
+    calls = []
+    for f in range(tb.kv):
+        o_idx = np.nonzero(tb.indices[f] >= 0)[0].astype(np.int32)
+        if len(o_idx) == 0:
+            continue
+        p = GemmParams()
+        p.algo_desp = H.gemm_desp(ShuffleStrideType.ShuffleAC, trans_b=True, n=K, k=C)
+        p.a, p.b, p.c = xd, wd[:, f, :], out
+        p.a_inds, p.c_inds = H.dev(tb.indices[f][o_idx], torch), H.dev(o_idx, torch)
+        p.beta = 1.0
+        calls.append(p)
+    return calls
+
+
+@pytest.mark.parametrize("n,C,K", [(3000, 64, 64), (2000, 128, 128), (150, 32, 64)])
+def test_layer_sequence_in_one_launch(torch, oracle, n, C, K):
+    """cb2_gemm_sequence_run: the calls of one layer as one launch, accumulating onto what the
+    output held; fp32 sums over all offsets rounded once (the call-by-call run rounds 27 times)."""
+    from cumm_b200.sequence import prepare_gemm_sequence
+    grid = (8, 24, 24)
+    tb = W.build_tables(W.sample_coords(n, 80 + n, grid), grid=grid)
+    rng = np.random.default_rng(81 + n)
+    x = rng.standard_normal((tb.n_in, C)).astype(np.float16)
+    w = (rng.standard_normal((K, 27, C)) / np.sqrt(27 * C) * 4).astype(np.float16)
+    init = rng.standard_normal((tb.n_out, K)).astype(np.float16)
+    out = H.dev(init, torch)
+    seq = prepare_gemm_sequence(_layer_as_calls(torch, tb, x, w, out))
+    seq.launch()
+    torch.cuda.synchronize()
+    H.check_status()
+    want = oracle.np_forward(x, w, tb.indices) + init.astype(np.float32)
+    H.assert_close_f16(out.cpu().numpy(), want, "sequence, first launch")
+    # a second launch reuses the tables and accumulates once more
+    seq.launch()
+    torch.cuda.synchronize()
+    H.check_status()
+    want2 = oracle.np_forward(x, w, tb.indices) + want.astype(np.float16).astype(np.float32)
+    H.assert_close_f16(out.cpu().numpy(), want2, "sequence, second launch (tables reused)")
+    # and the call-by-call run agrees to a few fp16 ulps
+    out_c = H.dev(init, torch)
+    for p in _layer_as_calls(torch, tb, x, w, out_c):
+        GemmMainUnitTest.matmul2(p)
+    torch.cuda.synchronize()
+    out1 = H.dev(init, torch)
+    prepare_gemm_sequence(_layer_as_calls(torch, tb, x, w, out1)).launch()
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(out1.cpu().numpy().astype(np.float32), out_c.cpu().numpy().astype(np.float32),
+                               rtol=2e-2, atol=2e-2)
+
+
+def test_layer_sequence_refuses_calls_that_are_not_one_layer(torch):
+    from cumm_b200.sequence import prepare_gemm_sequence
+    grid = (8, 24, 24)
+    tb = W.build_tables(W.sample_coords(500, 90, grid), grid=grid)
+    x = np.zeros((tb.n_in, 64), np.float16)
+    w = np.zeros((64, 27, 64), np.float16)
+    out = torch.zeros((tb.n_out, 64), dtype=torch.float16, device="cuda")
+    calls = _layer_as_calls(torch, tb, x, w, out)
+    calls[3].beta = 0.0  # would overwrite instead of accumulate
+    with pytest.raises(RuntimeError, match="does not fit the layer form"):
+        prepare_gemm_sequence(calls).launch()
+    calls = _layer_as_calls(torch, tb, x, w, out)
+    calls[2].a = torch.zeros((tb.n_in, 64), dtype=torch.float16, device="cuda")  # another A
+    with pytest.raises(RuntimeError, match="does not fit the layer form"):
+        prepare_gemm_sequence(calls).launch()
+    assert (out == 0).all()
