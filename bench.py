@@ -46,6 +46,7 @@ L2_BYTES = 126 * 1024 * 1024
 SHARES = tuple(int(v) for v in os.environ.get("CUMM_B200_BENCH_SHARES", "48,48,52").split(","))
 # Several GPUs: the weight gradient runs first on the whole GPU, then forward and backward input side
 # by side on these shares while the exchange runs on the SMs they leave free.
+MULTI_GPU_SCHEDULE = os.environ.get("CUMM_B200_BENCH_MULTI", "branches")  # or "wgrad_first"
 PAIR_SHARES = tuple(int(v) for v in os.environ.get("CUMM_B200_BENCH_PAIR_SHARES", "68,68").split(","))
 
 
@@ -338,7 +339,7 @@ def main():
                 from cumm_b200.peer_allreduce import PeerAllReduce
                 peer_ar = PeerAllReduce.over_process_group(C_OUT * KV * C_IN, dev)
                 # its CTAs go to the SMs the convolution kernels leave free, not beside them
-                peer_ar.own_sm_smem_bytes = 16 * 1024
+                peer_ar.own_sm_smem_bytes = 12 * 1024
                 ok = 1
             except Exception as e:  # noqa: BLE001 - any set-up failure means: use NCCL, and say so
                 print(f"[rank {rank}] peer-memory sum unavailable ({e!r}); using NCCL", file=sys.stderr, flush=True)
@@ -379,11 +380,12 @@ def main():
         input gradient (the two convolutions leave the exchange a few SMs of its own)."""
         s_dgrad.wait_stream(stream)
         s_wgrad.wait_stream(stream)
-        if world == 1:
+        if world == 1 or MULTI_GPU_SCHEDULE == "branches":
             L = s["shared"]
             L.fwd.launch()
             with torch.cuda.stream(s_wgrad):
                 L.wgrad.launch(s_wgrad.cuda_stream)
+                exchange(s, s_wgrad.cuda_stream)
             with torch.cuda.stream(s_dgrad):
                 L.dgrad.launch(s_dgrad.cuda_stream)
         else:
@@ -588,7 +590,8 @@ def main():
         run.update({
             "l2": f"rotating {nsets} buffer sets ({nsets * step_bytes / 1e6:.0f} MB touched) > 126 MB L2",
             "schedule": (f"one CUDA graph per step, three branches side by side (max_ctas {SHARES[0]}/{SHARES[1]}/{SHARES[2]}: "
-                         "forward / backward input / backward weight)" if concurrent and one_graph and world == 1 else
+                         "forward / backward input / backward weight" + (", the exchange after it on the SMs it frees)" if world > 1 else ")")
+                         if concurrent and one_graph and (world == 1 or MULTI_GPU_SCHEDULE == "branches") else
                          f"one CUDA graph per step: backward weight on the whole GPU, then forward / backward input side by "
                          f"side (max_ctas {PAIR_SHARES[0]}/{PAIR_SHARES[1]}) with the exchange on the SMs they leave free"
                          if concurrent and one_graph else

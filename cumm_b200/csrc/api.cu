@@ -930,13 +930,14 @@ struct PeerLayout {
 static void peer_layout(long long numel, int world, PeerLayout *L) {
   const long long n4 = numel / 4;
   L->shard_f4 = (n4 + world - 1) / world;
-  L->shard_bytes = static_cast<long long>(align256(static_cast<size_t>(L->shard_f4) * 16));
-  L->result_bytes = static_cast<long long>(align256(static_cast<size_t>(numel) * 4));
+  // a float4 travels as two 16-byte lines: two floats and two copies of the call number each
+  L->shard_bytes = static_cast<long long>(align256(static_cast<size_t>(L->shard_f4) * cb2::kPeerLineBytesPerF4));
+  L->result_bytes = static_cast<long long>(align256(static_cast<size_t>(n4) * cb2::kPeerLineBytesPerF4));
   L->total = cb2::kPeerControlBytes + 2 * static_cast<size_t>(world) * L->shard_bytes + 2 * static_cast<size_t>(L->result_bytes);
 }
 
 size_t cb2_peer_allreduce_buffer_size(long long numel, int world) {
-  if (numel <= 0 || numel % 4 || world < 1 || world > cb2::kPeerMaxWorld)
+  if (numel <= 0 || numel % 4 || numel / 4 > 0x3fffffff || world < 1 || world > cb2::kPeerMaxWorld)
     return 0;
   PeerLayout L;
   peer_layout(numel, world, &L);
@@ -952,7 +953,7 @@ int cb2_peer_allreduce(const cb2_peer_allreduce_args *a, void *stream_v) {
     return rc;
   CB2_CHECK_ARG(a->world >= 1 && a->world <= cb2::kPeerMaxWorld && a->rank >= 0 && a->rank < a->world,
                 "bad rank / world (%d, %d)", a->rank, a->world);
-  CB2_CHECK_ARG(a->numel > 0 && a->numel % 4 == 0, "numel must be a positive multiple of 4");
+  CB2_CHECK_ARG(a->numel > 0 && a->numel % 4 == 0 && a->numel / 4 <= 0x3fffffff, "numel must be a positive multiple of 4 below 2^32");
   CB2_CHECK_RT(a->peer_buffers && a->src && (a->out_f32 || a->out_f16), "buffers, source and an output must not empty");
   CB2_CHECK_ARG(aligned16(a->src) && aligned16(a->out_f32) && (reinterpret_cast<uintptr_t>(a->out_f16) & 7u) == 0,
                 "source and outputs must be 16-byte (fp16: 8-byte) aligned");
@@ -968,16 +969,16 @@ int cb2_peer_allreduce(const cb2_peer_allreduce_args *a, void *stream_v) {
   p.src = a->src;
   p.out32 = a->out_f32;
   p.out16 = reinterpret_cast<__half *>(a->out_f16);
-  p.numel = a->numel;
-  p.shard_f4 = L.shard_f4;
+  p.n4 = static_cast<int>(a->numel / 4);
+  p.shard_f4 = static_cast<int>(L.shard_f4);
   p.shard_bytes = L.shard_bytes;
   p.result_bytes = L.result_bytes;
   p.rank = a->rank;
   p.world = a->world;
   p.timeout_ns = a->timeout_ns ? a->timeout_ns : 1000000000ull;
   p.status = dev->status;
-  // every CTA waits for flags that the grid's own last CTA stores: the whole grid must be resident
-  // at once, beside whatever else runs (small CTAs: 128 threads, no dynamic shared memory)
+  // every CTA waits for data that other GPUs send only after they have seen this grid's whole
+  // scatter: the whole grid must be resident at once, beside whatever else runs (small CTAs)
   static const int max_grid = [] {
     const char *v = getenv("CUMM_B200_PEER_GRID");
     const int g = v ? atoi(v) : 96;

@@ -1,5 +1,5 @@
-"""The peer-memory sum on one GPU: a world of one (push to itself, flag, reduce), and a wait
-that runs out (a flag that nothing sets) reported through the status word; and, where the box
+"""The peer-memory sum on one GPU: a world of one (scatter to itself, reduce, gather), and a wait
+that runs out (data that nothing sends) reported through the status word; and, where the box
 has two GPUs, a world of two processes checked against the rank-ordered sum (``bench.py --gpus N``
 makes the same check at every N before it times anything)."""
 import numpy as np
@@ -15,7 +15,7 @@ def test_world_of_one_sums_and_casts(cuda_lib):
     numel = 128 * 27 * 128
     buf = torch.zeros(PeerAllReduce.buffer_bytes(numel, 1), dtype=torch.uint8, device="cuda")
     ar = PeerAllReduce(numel, 0, 1, [buf.data_ptr()], keep=buf)
-    for call in range(3):  # both parities, flags only grow
+    for call in range(3):  # both parities, the call number only grows
         src = torch.randn(numel, device="cuda") * (call + 1)
         o16 = torch.zeros(numel, dtype=torch.float16, device="cuda")
         o32 = torch.zeros(numel, dtype=torch.float32, device="cuda")
@@ -26,7 +26,7 @@ def test_world_of_one_sums_and_casts(cuda_lib):
         assert torch.equal(o16, src.to(torch.float16))
 
 
-def test_a_flag_that_nothing_sets_times_out(cuda_lib):
+def test_data_that_nothing_sends_times_out(cuda_lib):
     import torch
     from cumm_b200 import _lib
     from cumm_b200.peer_allreduce import PeerAllReduce

@@ -229,12 +229,13 @@ def test_peer_allreduce_buffer_size_is_a_host_function():
     L.cb2_peer_allreduce_buffer_size.restype = ctypes.c_size_t
     L.cb2_peer_allreduce_buffer_size.argtypes = [ctypes.c_longlong, ctypes.c_int]
     numel = 128 * 27 * 128
-    # control block, then per call parity: one receive slot per GPU of one shard each, and one result array
+    # control block, then per call parity: one receive slot per GPU of one shard each, and one result array;
+    # every float travels beside a copy of the call number (8 bytes per float)
     one = L.cb2_peer_allreduce_buffer_size(numel, 1)
-    assert one == 8192 + 2 * numel * 4 + 2 * numel * 4
-    shard = numel * 4 // 8
+    assert one == 8192 + 2 * numel * 8 + 2 * numel * 8
+    shard = numel * 8 // 8
     assert shard % 256 == 0
-    assert L.cb2_peer_allreduce_buffer_size(numel, 8) == 8192 + 2 * 8 * shard + 2 * numel * 4
+    assert L.cb2_peer_allreduce_buffer_size(numel, 8) == 8192 + 2 * 8 * shard + 2 * numel * 8
     assert L.cb2_peer_allreduce_buffer_size(numel + 2, 8) == 0  # not a multiple of 4
     assert L.cb2_peer_allreduce_buffer_size(numel, 17) == 0
     assert L.cb2_peer_allreduce_buffer_size(0, 2) == 0
