@@ -24,6 +24,7 @@ struct TraceBuf {
   unsigned long long cta[256][3];    // per CTA: start time, end time, steps
   long long prof[256][12];           // per CTA: clock cycles the MMA warp spent per phase
   long long prof2[256][12];          // per CTA: the same for thread 0 of the epilogue
+  long long prof3[256][8];           // per CTA: the scheduler warp
 };
 __device__ TraceBuf g_trace;
 // 1 in the CTA whose events are recorded (a shared-memory flag: testing it must cost next to
@@ -100,9 +101,31 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// The same test without any waiting: try_wait may suspend the thread for a while when the phase
+// is still open (which is what a waiter wants), test_wait returns at once (which is what a
+// thread that has other work to do wants).
+__device__ __forceinline__ bool mbar_poll(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n"
+               ".reg .pred p;\n"
+               "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+               "selp.u32 %0, 1, 0, p;\n"
+               "}\n"
+               : "=r"(ok)
+               : "r"(bar), "r"(parity)
+               : "memory");
+  return ok != 0;
+}
+
 // Time limit of every wait, in nanoseconds of the global timer.  Far above any legitimate
 // delay on this path (whole kernels run for tens of microseconds), far below anything an
 // operator would notice.
+#ifndef CB2_WAIT_SLEEP_MIN
+#define CB2_WAIT_SLEEP_MIN 20
+#endif
+#ifndef CB2_WAIT_SLEEP_MAX
+#define CB2_WAIT_SLEEP_MAX 160
+#endif
 constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;
 
 __device__ __forceinline__ unsigned long long global_timer_ns() {
@@ -120,12 +143,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   if (mbar_test(bar, parity))
     return true;
   unsigned long long t0 = 0;
-  uint32_t backoff = 20;
+  uint32_t backoff = CB2_WAIT_SLEEP_MIN;
   for (uint32_t i = 0;; ++i) {
-    __nanosleep(backoff);
+    if (CB2_WAIT_SLEEP_MAX > 0)
+      __nanosleep(backoff);
     if (mbar_test(bar, parity))
       return true;
-    if (backoff < 160)
+    if (backoff < CB2_WAIT_SLEEP_MAX)
       backoff += backoff;
     if ((i & 63u) == 63u) {
       if (*abort_flag)
@@ -155,7 +179,7 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
 __device__ __forceinline__ bool mbar_test_warp(uint32_t bar, uint32_t parity) {
   int ok = 0;
   if (lane_id() == 0)
-    ok = mbar_test(bar, parity) ? 1 : 0;
+    ok = mbar_poll(bar, parity) ? 1 : 0;
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 

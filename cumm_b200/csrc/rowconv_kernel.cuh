@@ -201,9 +201,14 @@ __device__ __forceinline__ int ring_tile_masks(const RowConvParams &p, const int
   for (int w = 0; w < MW; ++w) {
     if (w < p.mask_words) {
       uint32_t m = 0;
+      if constexpr (MW == 1) {
+        const int4 m4 = *reinterpret_cast<const int4 *>(sl + 136 + 4 * lane);  // four rows' words in one load
+        m = static_cast<uint32_t>(m4.x | m4.y | m4.z | m4.w);
+      } else {
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        m |= static_cast<uint32_t>(sl[136 + (i * 32 + lane) * MW + w]);
+        for (int i = 0; i < 4; ++i)
+          m |= static_cast<uint32_t>(sl[136 + (i * 32 + lane) * MW + w]);
+      }
       m = __reduce_or_sync(0xffffffffu, m) & p.mask_filter;
       const int left = p.kv - 32 * w;  // offsets this word covers
       if (left < 32)
@@ -391,9 +396,12 @@ __device__ __forceinline__ void scheduler_run(const RowConvParams &p, const Ring
   // first tile weighs before it takes a second.
   int issued = 0, accounted = 0, released = 0, held_steps = 0;
   int guess = (conv && dynamic) ? STEP_BUDGET + 1 : 1;
+  // The scheduler's own instructions are what paces a CTA whose tiles carry one offset each: every
+  // poll here is made by all lanes at once (a vote instead of a test by one lane and a shuffle), and releases are only looked at when the
+  // CTA could not draw otherwise.
   auto account = [&]() {
     while (accounted < issued &&
-           mbar_test_warp(rv.landed0 + 8u * (accounted % rv.ring), (accounted / rv.ring) & 1)) {
+           __any_sync(0xffffffffu, mbar_poll(rv.landed0 + 8u * (accounted % rv.ring), (accounted / rv.ring) & 1))) {
       int *sl = rv.slot(accounted % rv.ring);
       uint32_t km[MW];
       const int offsets = ring_tile_masks<MW>(p, sl, sl[0], km);
@@ -417,15 +425,25 @@ __device__ __forceinline__ void scheduler_run(const RowConvParams &p, const Ring
       guess = nsteps;
       ++accounted;
     }
+  };
+  auto account_released = [&]() {
     while (released < accounted &&
-           mbar_test_warp(rv.empty0 + 8u * (released % rv.ring), (released / rv.ring) & 1)) {
+           __any_sync(0xffffffffu, mbar_poll(rv.empty0 + 8u * (released % rv.ring), (released / rv.ring) & 1))) {
       held_steps -= rv.slot(released % rv.ring)[2];
       ++released;
     }
   };
+  auto can_draw = [&]() { return (held_steps <= STEP_BUDGET || released == issued) && (issued - released < rv.ring); };
+  // tables whose tiles can be fetched with two 16-byte copies per lane
+  const bool wide_copies = conv && MW == 1 && p.mask_words == 1 &&
+                           ((reinterpret_cast<uintptr_t>(p.argsort) | reinterpret_cast<uintptr_t>(p.mask)) & 15u) == 0;
   for (;;) {
     account();
-    const bool may_draw = (held_steps <= STEP_BUDGET || released == issued) && (issued - released < rv.ring);
+    bool may_draw = can_draw();
+    if (!may_draw) {
+      account_released();
+      may_draw = can_draw();
+    }
     if (!may_draw) {
       // first learn what the tiles in flight weigh, then wait for the oldest one to be finished
       const bool ok = accounted < issued
@@ -437,8 +455,11 @@ __device__ __forceinline__ void scheduler_run(const RowConvParams &p, const Ring
     }
     const int si = issued % rv.ring;
     const int ticket = draw();
-    if (ticket == 0 && lane == 0)
-      CB2_TRACE_SELECT(1);  // follow the CTA that got the heaviest tile
+#ifndef CB2_TRACE_TICKET
+#define CB2_TRACE_TICKET 0  // 0: follow the CTA that got the heaviest tile
+#endif
+    if (ticket == CB2_TRACE_TICKET && lane == 0)
+      CB2_TRACE_SELECT(1);
     int tile = -1;
     if (ticket < ntiles)
       tile = conv ? (ntiles - 1 - ticket) : ticket;  // the last tiles of the sorted order carry the most offsets
@@ -449,6 +470,10 @@ __device__ __forceinline__ void scheduler_run(const RowConvParams &p, const Ring
       sl[2] = guess;
     }
     held_steps += guess;
+    if (wide_copies && tile >= 0 && (tile + 1) * 128 <= p.n_rows) {
+      cp_async_16(sa + (8 + 4 * lane) * 4, p.argsort + tile * 128 + 4 * lane, 16u);
+      cp_async_16(sa + (136 + 4 * lane) * 4, p.mask + tile * 128 + 4 * lane, 16u);
+    } else
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int j = i * 32 + lane;

@@ -357,7 +357,10 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
     mbar_init_fence();
     misc[1] = 0;
     misc[2] = misc[3] = misc[4] = misc[5] = 1;
-    CB2_TRACE_SELECT(blockIdx.x == 0);
+#ifndef CB2_TRACE_WGRAD_CTA
+#define CB2_TRACE_WGRAD_CTA 0
+#endif
+    CB2_TRACE_SELECT(blockIdx.x == CB2_TRACE_WGRAD_CTA);
   }
   if (warp == 4) {
     tmem_alloc(sbase + Cfg::OFF_MISC, Cfg::TMEM_COLS);
@@ -681,19 +684,51 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmap_dout, const __grid_constan
     // this CTA's share of the offsets with many units: positions [c, c + 1) * kTileF4 / G in runs of 32
     const int q_begin = (int)(((long long)blockIdx.x * kTileF4) / gridDim.x) & ~31;
     const int q_end = blockIdx.x + 1 == gridDim.x ? kTileF4 : ((int)(((long long)(blockIdx.x + 1) * kTileF4) / gridDim.x) & ~31);
-    for (int f = 0; f < p.kv; ++f) {
+    // Which offsets this CTA helps to sum, and which positions of each: worked out once, by one
+    // thread per offset, and packed in offset order (a CTA takes part in two or three offsets; a loop
+    // over all of them, with its divisions run by every thread, cost more than the sums themselves).
+    int *s_take = reinterpret_cast<int *>(smem + Cfg::OFF_ROWIDX);  // the row-index buffers are idle now
+    {
+      bool take = false;
+      int lo = 0, hi = 0;
+      unsigned ballot = 0;
+      if (tid < 128) {
+        const int f = tid;
+        if (f < p.kv && s_units[f] > 0) {
+          if (s_units[f] > kWgradSharedSumUnits) {
+            lo = q_begin, hi = q_end;
+            take = q_begin < q_end;
+          } else {
+            // an offset with few units belongs to a small group of neighbouring CTAs (the groups are
+            // dealt out evenly over the grid), each summing an equal run of positions
+            const int group = max(1, (int)gridDim.x / p.kv);
+            const int member = (int)blockIdx.x - (f * (int)gridDim.x) / p.kv;
+            take = member >= 0 && member < group;
+            lo = ((member * kTileF4) / group) & ~1;
+            hi = member + 1 == group ? kTileF4 : (((member + 1) * kTileF4) / group) & ~1;
+          }
+        }
+        ballot = __ballot_sync(0xffffffffu, take);
+        if (lane == 0)
+          s_take[384 + warp] = static_cast<int>(ballot);
+      }
+      __syncthreads();
+      if (tid < 128 && take) {
+        int rank = __popc(ballot & ((1u << lane) - 1u));
+        for (int w = 0; w < warp; ++w)
+          rank += __popc(static_cast<uint32_t>(s_take[384 + w]));
+        s_take[rank] = tid;
+        s_take[128 + rank] = lo;
+        s_take[256 + rank] = hi;
+      }
+      __syncthreads();
+    }
+    const int n_take = __popc(static_cast<uint32_t>(s_take[384])) + __popc(static_cast<uint32_t>(s_take[385])) +
+                       __popc(static_cast<uint32_t>(s_take[386])) + __popc(static_cast<uint32_t>(s_take[387]));
+    for (int i = 0; i < n_take; ++i) {
+      const int f = s_take[i], lo = s_take[128 + i], hi = s_take[256 + i];
       const int S = s_units[f];
-      if (S == 0)
-        continue;
       const bool shared_sum = S > kWgradSharedSumUnits;
-      // an offset with few units belongs to a small group of neighbouring CTAs (the groups are dealt
-      // out evenly over the grid), each summing an equal run of positions
-      const int group = max(1, (int)gridDim.x / p.kv);
-      const int member = (int)blockIdx.x - (int)(((long long)f * gridDim.x) / p.kv);
-      const int lo = shared_sum ? q_begin : ((member * kTileF4) / group) & ~1;
-      const int hi = shared_sum ? q_end : (member + 1 == group ? kTileF4 : (((member + 1) * kTileF4) / group) & ~1);
-      if (shared_sum ? (q_begin >= q_end) : (member < 0 || member >= group))
-        continue;
       if (tid == 0) {
         // bounded wait for the last unit of f
         const int *flag = p.ctl + 9 + 8 * blockIdx.y + (f >> 5);
