@@ -42,8 +42,10 @@ METRIC = "sparse-conv effective TFLOP/s (fwd+dgrad+wgrad, fp16, C=K=128, 3x3x3 s
 WORKLOAD = "scale-out: 8 scenes x 120k voxels, grid [41,1600,1408], seed 4, fwd+dgrad+wgrad fp16 C=K=128"
 L2_BYTES = 126 * 1024 * 1024
 # SM shares of the three kernels when they run side by side (forward, backward input, backward
-# weight); the weight gradient moves the same bytes with more steps per row tile.
-SHARES = tuple(int(v) for v in os.environ.get("CUMM_B200_BENCH_SHARES", "48,48,52").split(","))
+# weight), picked from measured step times: with several GPUs the exchange follows the weight
+# gradient, so that branch gets a few more SMs.
+SHARES = tuple(int(v) for v in os.environ.get(
+    "CUMM_B200_BENCH_SHARES", "48,48,52" if int(os.environ.get("WORLD_SIZE", "1")) == 1 else "46,46,56").split(","))
 # Several GPUs: the weight gradient runs first on the whole GPU, then forward and backward input side
 # by side on these shares while the exchange runs on the SMs they leave free.
 MULTI_GPU_SCHEDULE = os.environ.get("CUMM_B200_BENCH_MULTI", "branches")  # or "wgrad_first"
