@@ -329,11 +329,12 @@ int cb2_dense_tables_run(const cb2_dense_tables_args *args, void *stream);
  * in the calling process (peer_buffers[rank] is the caller's own), each of
  * cb2_peer_allreduce_buffer_size() bytes, zero-filled once before the first call.  The kernel
  * sends shard s of its array to GPU s (plain stores over NVLink), sums the shards it receives
- * in GPU order and sends the sums to every GPU; each of the two waits lasts at most
- * `timeout_ns` (0 = one second), and a wait that runs out sets status word 1
- * (cb2_device_status) and leaves the outputs untouched.  The kernel's CTAs all have to be
- * resident at the same time; they are small (128 threads) so that they fit beside other
- * kernels, and at most one per SM is launched.
+ * in GPU order and sends the sums to every GPU.  Every float travels beside a copy of the call
+ * number (8 bytes per float in the buffers), and a reader repeats its load until that number is
+ * the current one: no fence or flag round trip separates the GPUs.  Such a wait lasts at most
+ * `timeout_ns` (0 = one second); one that runs out sets status word 1 (cb2_device_status) and
+ * leaves the outputs untouched.  The kernel's CTAs all have to be resident at the same time;
+ * they are small (128 threads), and at most one per SM is launched.
  */
 typedef struct cb2_peer_allreduce_args {
   void *const *peer_buffers;

@@ -43,7 +43,7 @@ def test_float_to_s8_matches_reference_vectors(oracle, gold):
     s, want = gold["f32_to_s8_in"], gold["f32_to_s8_out"]
     got = np.array([oracle.float_to_s8(v) for v in s], np.int8)
     assert (got == want).all()
-    # the survey's hand-checked values
+    # hand-checked values: ties go to even, saturation at both ends
     for v, q in ((0.5, 0), (1.5, 2), (2.5, 2), (127.5, 127), (200.0, 127), (-128.5, -128), (-300.0, -128)):
         assert oracle.float_to_s8(v) == q
     assert oracle.float_to_s8(float("nan")) == 0
