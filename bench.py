@@ -43,9 +43,12 @@ WORKLOAD = "scale-out: 8 scenes x 120k voxels, grid [41,1600,1408], seed 4, fwd+
 L2_BYTES = 126 * 1024 * 1024
 # SM shares of the three kernels when they run side by side (forward, backward input, backward
 # weight), picked from measured step times: with several GPUs the exchange follows the weight
-# gradient, so that branch gets a few more SMs.
+# gradient, so that branch gets more SMs the smaller a GPU's share of the rows is (2 GPUs:
+# measured there; 4 and 8: from one GPU running a rank's rows with a world-of-one exchange).
+_WORLD = int(os.environ.get("WORLD_SIZE", "1"))
 SHARES = tuple(int(v) for v in os.environ.get(
-    "CUMM_B200_BENCH_SHARES", "48,48,52" if int(os.environ.get("WORLD_SIZE", "1")) == 1 else "46,46,56").split(","))
+    "CUMM_B200_BENCH_SHARES",
+    "48,48,52" if _WORLD == 1 else "46,46,56" if _WORLD <= 2 else "42,42,64" if _WORLD <= 4 else "40,40,68").split(","))
 # Several GPUs: the weight gradient runs first on the whole GPU, then forward and backward input side
 # by side on these shares while the exchange runs on the SMs they leave free.
 MULTI_GPU_SCHEDULE = os.environ.get("CUMM_B200_BENCH_MULTI", "branches")  # or "wgrad_first"
