@@ -142,31 +142,22 @@ __device__ __forceinline__ float apply_act(float x, int act_type, float act_alph
   }
 }
 
-// float -> int8, round-to-nearest-even, saturating, NaN -> 0 (what cvt.rni.sat.s8.f32 returns),
-// with the int8 value in the low byte of the result.  Conversion instructions issue at a
-// quarter of the rate of plain arithmetic and the requant epilogue already spends one per
-// element on int32 -> float, so this direction is done in the arithmetic pipes: clamp to
-// [-128, 127] with the NaN-propagating min/max, then add 1.5 * 2^23, which leaves the rounded
-// integer in the low mantissa bits (a NaN stays a NaN, whose low byte is 0).
-__device__ __forceinline__ uint32_t cvt_sat_s8(float t) {
-  float c;
-  asm("max.NaN.f32 %0, %1, 0fC3000000;\n\t"
-      "min.NaN.f32 %0, %0, 0f42FE0000;"
-      : "=f"(c)
-      : "f"(t));
-  return __float_as_uint(__fadd_rn(c, 12582912.0f));
-}
-// The same conversion as one instruction of the conversion unit.  That unit is slow but idle
-// otherwise, so the epilogue sends part of the elements through it and the rest through the
-// arithmetic pipes, which then work side by side.
-__device__ __forceinline__ uint32_t cvt_sat_s8_xu(float t) {
-  int r;
-  asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(t));
-  return static_cast<uint32_t>(r);
-}
-// low bytes of a, b, c, d -> one word (three byte-permutes instead of masks, shifts and ors)
-__device__ __forceinline__ uint32_t pack_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+// Four floats -> four int8 in one word, round-to-nearest-even, saturating, NaN -> 0 (what
+// cvt.rni.sat.s8.f32 returns for each): to int32 first (NaN -> 0, saturating at the int32 range),
+// then two saturating packs of two values each -- the reference's packed converter
+// (include/tensorview/gemm/math/numeric_convert.h:1107-1138).  Six instructions per four values;
+// a clamp-and-magic-add form in the arithmetic pipes took eleven and measured 4 % slower on the
+// stride-2 int8 convolution: the kernel is bound by instruction issue, not by a pipe.
+__device__ __forceinline__ uint32_t cvt_pack4_s8(float a, float b, float c, float d) {
+  int ia, ib, ic, id;
+  asm("cvt.rni.s32.f32 %0, %1;" : "=r"(ia) : "f"(a));
+  asm("cvt.rni.s32.f32 %0, %1;" : "=r"(ib) : "f"(b));
+  asm("cvt.rni.s32.f32 %0, %1;" : "=r"(ic) : "f"(c));
+  asm("cvt.rni.s32.f32 %0, %1;" : "=r"(id) : "f"(d));
+  uint32_t hi, out;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(id), "r"(ic));       // bytes {c, d}
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(ib), "r"(ia), "r"(hi));  // {a, b, c, d}
+  return out;
 }
 
 // Tiles are handed out by one scheduler warp per CTA through a small shared-memory ring.
@@ -671,13 +662,6 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
             dep_waited = true;
           }
           const int o = (p.mode == kModeMaskConv) ? sl[8 + erow] : sl[136 + erow];  // destination row of this thread's tile row
-          int tile_offsets = __popc(kmask_store);  // filter offsets the tile carries
-          if constexpr (MW > 1) {
-            tile_offsets = 0;
-#pragma unroll
-            for (int w = 0; w < MW; ++w)
-              tile_offsets += __popc(static_cast<uint32_t>(sl[4 + w]));
-          }
           if (et == 0 && p.mask_out && blockIdx.y == 0) {
             if constexpr (MW == 1) {
               p.mask_out[tile] = kmask_store;
@@ -709,7 +693,6 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
           const uint32_t trow = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
                                 static_cast<uint32_t>(buf * BLOCK_N);
           const bool use_src = (p.src_mode != kSrcNone) && (p.beta != 0.f);
-          const bool small_acc = KIND == 1 && tile_offsets * kpasses * Cfg::KRED <= 255;
           // fast path: out = cvt(acc); everything else goes through the general epilogue
           const bool plain = !use_src && p.act_type == 0 && p.alpha == 1.f;
           constexpr int ROUNDS = COLS_PER_HALF / 32;
@@ -795,20 +778,9 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
               uint32_t packed[8];
               float t[32];
               {
-                // int32 -> float.  The conversion instruction runs on the slow conversion unit, which the
-                // float -> int8 step also needs.  When the tile's accumulators are known to stay below
-                // 2^22 in magnitude (one filter offset and at most 255 products of |a|, |b| <= 128 per
-                // element) the same value comes out of an integer add and a float subtract, exactly:
-                // 0x4B400000 + n is the float 1.5 * 2^23 + n.
-                if (small_acc) {
 #pragma unroll
-                  for (int i = 0; i < 32; ++i)
-                    t[i] = __fadd_rn(__int_as_float(static_cast<int>(v[i]) + 0x4B400000), -12582912.0f);
-                } else {
-#pragma unroll
-                  for (int i = 0; i < 32; ++i)
-                    t[i] = __int2float_rn(static_cast<int>(v[i]));
-                }
+                for (int i = 0; i < 32; ++i)
+                  t[i] = __int2float_rn(static_cast<int>(v[i]));
                 const float4 *sc4 = reinterpret_cast<const float4 *>(s_scale + col0);
                 const float4 *bi4 = reinterpret_cast<const float4 *>(s_bias + col0);
 #pragma unroll
@@ -846,8 +818,7 @@ rowconv_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
               }
 #pragma unroll
               for (int i = 0; i < 32; i += 4)
-                packed[i / 4] = pack_low_bytes(cvt_sat_s8(t[i]), cvt_sat_s8_xu(t[i + 1]), cvt_sat_s8(t[i + 2]),
-                                               cvt_sat_s8_xu(t[i + 3]));
+                packed[i / 4] = cvt_pack4_s8(t[i], t[i + 1], t[i + 2], t[i + 3]);
 #pragma unroll
               for (int q = 0; q < 2; ++q) {
                 const int c = (col0 / 32) * CH_PER_ROUND + q;
