@@ -799,7 +799,10 @@ def run_nvrtc_conv_kernel(params: ConvParams) -> None:
 class PreparedCall:
     """A validated call with its flat argument record built once, for launch-bound loops
     (replays, CUDA-graph capture): ``launch()`` only crosses the C ABI.  The record owns its
-    tile-ticket counters (``sched_scratch``), so a captured launch shares them with nobody.
+    tile-ticket counters (``sched_scratch``), so a captured launch shares them with nobody --
+    two pairs, used in turn: with programmatic dependent launch a launch may start drawing
+    tickets while its predecessor on the stream still runs, and that predecessor can be the
+    same call.
     ``static_tables``: the caller promises that the neighbour tables (for the weight gradient:
     the reduced masks) keep their contents while the call is in use; the weight gradient then
     plans its schedule on the first launch only (``reuse_plan``)."""
@@ -811,7 +814,8 @@ class PreparedCall:
         self._device = device
         self._stream = int(stream)
         self._keep = keep  # tensors whose memory the record points at
-        self._tickets = torch.zeros(4, dtype=torch.int32, device=f"cuda:{device}")
+        self._tickets = torch.zeros(8, dtype=torch.int32, device=f"cuda:{device}")
+        self._turn = 0
         args.sched_scratch = self._tickets.data_ptr()
         self._plan_once = bool(static_tables) and bool(args.workspace)
         L = _lib.load()
@@ -819,6 +823,8 @@ class PreparedCall:
 
     def launch(self, stream: Optional[int] = None) -> None:
         s = self._stream if stream is None else int(stream)
+        self._args.sched_scratch = self._tickets.data_ptr() + 16 * self._turn
+        self._turn ^= 1
         rc = self._fn(ctypes.byref(self._args), ctypes.c_void_p(s))
         if rc:
             _lib.raise_for(rc)

@@ -92,7 +92,10 @@ typedef struct cb2_gemm_args {
    *   tile-ticket counters of the launch (the kernel returns them to zero).  Without it the launch
    *   takes a pair from a per-device pool in round-robin order, which is safe for eager launches
    *   but lets a captured launch (whose pair is fixed at capture) collide with a later eager one
-   *   running at the same time on another stream.  Give every captured or replayed call its own.
+   *   running at the same time on another stream.  Give every captured or replayed call its own;
+   *   a caller that launches the SAME record twice in a row alternates between two such blocks
+   *   (with programmatic dependent launch the second launch may draw tickets while the first
+   *   still runs).
    * max_ctas: upper bound on the CTAs of the launch (0 = one per SM).  The kernels are persistent
    *   and sized to one CTA per SM; calls that are meant to run side by side on different streams
    *   (forward, backward input and backward weight of one layer) each take a share.
@@ -163,7 +166,10 @@ typedef struct cb2_conv_args {
    *   tile-ticket counters of the launch (the kernel returns them to zero).  Without it the launch
    *   takes a pair from a per-device pool in round-robin order, which is safe for eager launches
    *   but lets a captured launch (whose pair is fixed at capture) collide with a later eager one
-   *   running at the same time on another stream.  Give every captured or replayed call its own.
+   *   running at the same time on another stream.  Give every captured or replayed call its own;
+   *   a caller that launches the SAME record twice in a row alternates between two such blocks
+   *   (with programmatic dependent launch the second launch may draw tickets while the first
+   *   still runs).
    * max_ctas: upper bound on the CTAs of the launch (0 = one per SM).  The kernels are persistent
    *   and sized to one CTA per SM; calls that are meant to run side by side on different streams
    *   (forward, backward input and backward weight of one layer) each take a share.
