@@ -1,7 +1,8 @@
 """Launches that overlap on the GPU: a captured forward replayed on one stream while eager
-forwards loop on another.  Every prepared call owns its tile-ticket counters, so the two
-never draw tiles from the same counter, whatever the library's round-robin pool hands to
-other launches in between; both results are checked against the oracle."""
+forwards loop on another, and one prepared call launched back to back.  Every prepared call
+owns its tile-ticket counters, so two calls never draw tiles from the same counter, whatever
+the library's round-robin pool hands to other launches in between; results are checked against
+the oracle."""
 import numpy as np
 import pytest
 
@@ -53,3 +54,43 @@ def test_graph_replay_beside_eager_launches(cuda_lib, oracle):
     H.check_status()
     H.assert_close_f16(outs[0].cpu().numpy(), wants[0], "captured forward replayed beside eager launches")
     H.assert_close_f16(outs[1].cpu().numpy(), wants[1], "eager forward beside graph replays")
+
+
+def test_the_same_prepared_call_back_to_back(cuda_lib, oracle):
+    """One prepared int8 forward launched many times in a row on one stream, eagerly and from a
+    graph: int8 convolutions are launched with programmatic dependent launch, so a launch starts
+    drawing tiles while its predecessor -- the same call -- still runs.  The call alternates
+    between two pairs of ticket counters; every launch must leave the bit-exact result."""
+    import torch
+    from cumm_b200.layer import DeviceTables, SparseConvLayer
+    grid = (8, 64, 64)
+    C = K = 128
+    tb = W.build_tables(W.sample_coords(20000, 721, grid), grid=grid, stride=(2, 2, 2), subm=False)
+    rng = np.random.default_rng(722)
+    x = rng.integers(-127, 128, (tb.n_in, C)).astype(np.int8)
+    w = rng.integers(-127, 128, (K, 27, C)).astype(np.int8)
+    scale = rng.uniform(1e-3, 1e-2, K).astype(np.float32)
+    bias = rng.standard_normal(K).astype(np.float32)
+    want = oracle.mask_igemm_s8(x, w, np.zeros((tb.n_out, K), np.int8), scale, bias, tb.indices, tb.mask,
+                                tb.mask_argsort)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        out = torch.zeros((tb.n_out, K), dtype=torch.int8, device="cuda")
+        L = SparseConvLayer(DeviceTables.from_host(tb, "cuda"), H.dev(w, torch), H.dev(x, torch), out,
+                            stream=stream.cuda_stream)
+        L.prepare_int8(H.dev(scale, torch), H.dev(bias, torch))
+        for _ in range(7):
+            L.fwd.launch()
+        stream.synchronize()
+        H.check_status()
+        assert (out.cpu().numpy() == want).all(), "eager launches back to back"
+        out.zero_()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for _ in range(5):
+                L.fwd.launch()
+        for _ in range(3):
+            g.replay()
+        stream.synchronize()
+    H.check_status()
+    assert (out.cpu().numpy() == want).all(), "graph of back-to-back launches, replayed"
