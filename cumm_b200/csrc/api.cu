@@ -511,7 +511,9 @@ struct PairgenLayout {
   long long list_cap;        // active outputs a strided conv can have at most
   long long nmax;            // rows the mask sorts may have to hold
   int key_bits;
+  int words;                 // mask words per row
   size_t off_in_keys, off_in_vals, off_set_keys, off_list_a, off_list_b, off_m, off_v, off_hist, off_counters, total;
+  size_t off_rows, off_k;    // several mask words per row: the unsorted rows, and the key array of a word's sort
 };
 
 size_t align256(size_t v) { return (v + 255) / 256 * 256; }
@@ -541,11 +543,12 @@ int pairgen_layout(const cb2_pairgen_args *a, PairgenLayout *L) {
     kv *= a->ksize[i];
     cells *= L->g.ogrid[i];
   }
-  CB2_CHECK_RT(kv <= 32, "kernel volume %lld is not supported (masks are 32 bits)", kv);
+  CB2_CHECK_RT(kv <= 128, "kernel volume %lld is not supported (masks hold up to 128 offsets)", kv);
   if (a->subm)
     for (int i = 0; i < 3; ++i)
       CB2_CHECK_ARG(a->stride[i] == 1, "a submanifold convolution has stride 1");
   L->g.kv = static_cast<int>(kv);
+  L->words = static_cast<int>((kv + 31) / 32);
   L->g.batch_size = a->batch_size;
   L->cap_in = pow2_at_least(2ull * static_cast<unsigned long long>(a->n_in));
   // outputs an input can feed: per axis, the offsets r with (in + pad - r * dil) divisible by the stride
@@ -583,6 +586,11 @@ int pairgen_layout(const cb2_pairgen_args *a, PairgenLayout *L) {
   L->off_v = take(static_cast<size_t>(L->nmax) * 4);
   const long long sort_n = std::max<long long>(L->nmax, L->list_cap);
   L->off_hist = take(static_cast<size_t>(256) * ((sort_n + cb2pg::kSortTile - 1) / cb2pg::kSortTile + 1) * 4);
+  L->off_rows = L->off_k = 0;
+  if (L->words > 1) {
+    L->off_rows = take(static_cast<size_t>(L->nmax) * L->words * 4);
+    L->off_k = take(static_cast<size_t>(L->nmax) * 4);
+  }
   L->total = off;
   return CB2_OK;
 }
@@ -612,6 +620,31 @@ int radix_sort(K *k_result, int *v_result, K *k_scratch, int *v_scratch, int n, 
     std::swap(ks, kd);
     std::swap(vs, vd);
   }
+  return CB2_OK;
+}
+
+// Masks of `words` words per row from a finished table, sorted (see mask_words_from_table_kernel):
+// writes mask [n, words] and mask_argsort [n].
+int sort_mask_words(const int32_t *table, int n, int kv, int words, uint32_t *rows, uint32_t *k_result,
+                    uint32_t *k_scratch, int *v_scratch, uint32_t *mask, int *argsort, int *hist, cudaStream_t s) {
+  const unsigned blocks = static_cast<unsigned>((n + 255) / 256);
+  cb2pg::mask_words_from_table_kernel<<<blocks, 256, 0, s>>>(table, n, kv, words, rows);
+  g_launches.fetch_add(1);
+  for (int w = 0; w < words; ++w) {
+    const int bits = std::min(32, kv - 32 * w);
+    cb2pg::gather_word_kernel<<<blocks, 256, 0, s>>>(rows, w == 0 ? nullptr : argsort, n, words, w,
+                                                     sort_source(k_result, k_scratch, bits),
+                                                     sort_source(argsort, v_scratch, bits));
+    CB2_CUDA(cudaGetLastError());
+    g_launches.fetch_add(1);
+    const int rc = radix_sort<uint32_t, true>(k_result, argsort, k_scratch, v_scratch, n, bits, hist, s);
+    if (rc)
+      return rc;
+  }
+  const long long total = static_cast<long long>(n) * words;
+  cb2pg::gather_rows_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, s>>>(rows, argsort, n, words, mask);
+  CB2_CUDA(cudaGetLastError());
+  g_launches.fetch_add(1);
   return CB2_OK;
 }
 
@@ -710,16 +743,28 @@ int cb2_pairgen_run(const cb2_pairgen_args *a, void *stream_v) {
     out_coords = a->out_coords;
     g_launches.fetch_add(1);
   }
-  cb2pg::probe_kernel<<<(n_out + 255) / 256, 256, 0, stream>>>(out_coords, n_out, L.g, in_keys, in_vals, L.cap_in - 1,
-                                                                a->indices, sort_source(a->mask, m_tmp, L.g.kv),
-                                                                sort_source(a->mask_argsort, v_tmp, L.g.kv));
+  const bool wide = L.words > 1;
+  uint32_t *rows = reinterpret_cast<uint32_t *>(ws + L.off_rows), *k_res = reinterpret_cast<uint32_t *>(ws + L.off_k);
+  // several mask words per row: the probe's one-word mask and row numbers go to scratch, the masks
+  // are built from the finished table instead
+  cb2pg::probe_kernel<<<(n_out + 255) / 256, 256, 0, stream>>>(
+      out_coords, n_out, L.g, in_keys, in_vals, L.cap_in - 1, a->indices,
+      wide ? m_tmp : sort_source(a->mask, m_tmp, L.g.kv), wide ? v_tmp : sort_source(a->mask_argsort, v_tmp, L.g.kv));
   CB2_CUDA(cudaGetLastError());
   g_launches.fetch_add(2);
-  rc = radix_sort<uint32_t, true>(a->mask, a->mask_argsort, m_tmp, v_tmp, n_out, L.g.kv, hist, stream);
+  if (wide)
+    rc = sort_mask_words(a->indices, n_out, L.g.kv, L.words, rows, k_res, m_tmp, v_tmp, a->mask, a->mask_argsort, hist,
+                         stream);
+  else
+    rc = radix_sort<uint32_t, true>(a->mask, a->mask_argsort, m_tmp, v_tmp, n_out, L.g.kv, hist, stream);
   if (rc)
     return rc;
   if (a->tile_masks) {
-    cb2pg::tile_masks_kernel<<<((n_out + 127) / 128 + 7) / 8, 256, 0, stream>>>(a->mask, n_out, a->tile_masks);
+    if (wide)
+      cb2pg::tile_masks_words_kernel<<<((n_out + 127) / 128 + 7) / 8, 256, 0, stream>>>(a->mask, n_out, L.words,
+                                                                                       a->tile_masks);
+    else
+      cb2pg::tile_masks_kernel<<<((n_out + 127) / 128 + 7) / 8, 256, 0, stream>>>(a->mask, n_out, a->tile_masks);
     CB2_CUDA(cudaGetLastError());
     g_launches.fetch_add(1);
   }
@@ -728,12 +773,19 @@ int cb2_pairgen_run(const cb2_pairgen_args *a, void *stream_v) {
     const long long threads = static_cast<long long>(n_out) * L.g.kv;
     cb2pg::invert_table_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(
         a->indices, n_out, L.g.kv, n_in, a->indices_bwd);
-    cb2pg::mask_from_table_kernel<<<(n_in + 255) / 256, 256, 0, stream>>>(
-        a->indices_bwd, n_in, L.g.kv, sort_source(a->mask_bwd, m_tmp, L.g.kv),
-        sort_source(a->mask_argsort_bwd, v_tmp, L.g.kv));
     CB2_CUDA(cudaGetLastError());
-    g_launches.fetch_add(2);
-    rc = radix_sort<uint32_t, true>(a->mask_bwd, a->mask_argsort_bwd, m_tmp, v_tmp, n_in, L.g.kv, hist, stream);
+    g_launches.fetch_add(1);
+    if (wide) {
+      rc = sort_mask_words(a->indices_bwd, n_in, L.g.kv, L.words, rows, k_res, m_tmp, v_tmp, a->mask_bwd,
+                           a->mask_argsort_bwd, hist, stream);
+    } else {
+      cb2pg::mask_from_table_kernel<<<(n_in + 255) / 256, 256, 0, stream>>>(
+          a->indices_bwd, n_in, L.g.kv, sort_source(a->mask_bwd, m_tmp, L.g.kv),
+          sort_source(a->mask_argsort_bwd, v_tmp, L.g.kv));
+      CB2_CUDA(cudaGetLastError());
+      g_launches.fetch_add(1);
+      rc = radix_sort<uint32_t, true>(a->mask_bwd, a->mask_argsort_bwd, m_tmp, v_tmp, n_in, L.g.kv, hist, stream);
+    }
     if (rc)
       return rc;
   }

@@ -220,6 +220,45 @@ __global__ void __launch_bounds__(256) mask_from_table_kernel(const int32_t *__r
   iota[j] = j;
 }
 
+// Kernel volumes above 32: a row's mask is `words` 32-bit words (word w = offsets 32w .. 32w+31),
+// built from the finished table, and rows are sorted as one integer whose LAST word is the most
+// significant: one stable radix sort per word, least significant word first, each on the keys
+// gathered through the order the previous sorts left.
+__global__ void __launch_bounds__(256) mask_words_from_table_kernel(const int32_t *__restrict__ table, int n, int kv,
+                                                                    int words, uint32_t *__restrict__ rows) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= n)
+    return;
+  for (int w = 0; w < words; ++w) {
+    uint32_t m = 0;
+    for (int b = 0; b < 32 && 32 * w + b < kv; ++b)
+      if (table[static_cast<long long>(32 * w + b) * n + j] >= 0)
+        m |= 1u << b;
+    rows[static_cast<long long>(j) * words + w] = m;
+  }
+}
+// key[i] = word w of the row that currently stands at place i; val[i] = that row (order == nullptr:
+// the rows are still in their original order)
+__global__ void __launch_bounds__(256) gather_word_kernel(const uint32_t *__restrict__ rows, const int32_t *order, int n,
+                                                          int words, int w, uint32_t *key, int32_t *val) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n)
+    return;
+  const int r = order ? order[i] : i;
+  key[i] = rows[static_cast<long long>(r) * words + w];
+  val[i] = r;
+}
+// sorted[i, :] = rows[order[i], :]
+__global__ void __launch_bounds__(256) gather_rows_kernel(const uint32_t *__restrict__ rows,
+                                                          const int32_t *__restrict__ order, int n, int words,
+                                                          uint32_t *__restrict__ sorted) {
+  const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= static_cast<long long>(n) * words)
+    return;
+  const int i = static_cast<int>(t / words), w = static_cast<int>(t % words);
+  sorted[t] = rows[static_cast<long long>(order[i]) * words + w];
+}
+
 // A sequence of gather-GEMM-scatter calls (one per filter offset, each with its own pair lists)
 // turned into the neighbour table of ONE convolution: table[f, c_inds_f[i]] = a_inds_f[i].
 // One thread per pair; `first[f]` = pairs before call f.
@@ -355,6 +394,27 @@ __global__ void __launch_bounds__(256) tile_masks_kernel(const uint32_t *__restr
   m = __reduce_or_sync(0xffffffffu, m);
   if (lane == 0)
     tile_masks[tile] = m;
+}
+
+// the same for several mask words per row: tile_masks[tile, w]
+__global__ void __launch_bounds__(256) tile_masks_words_kernel(const uint32_t *__restrict__ sorted_mask, int n, int words,
+                                                               uint32_t *__restrict__ tile_masks) {
+  const int tile = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (tile * 128 >= n)
+    return;
+  for (int w = 0; w < words; ++w) {
+    uint32_t m = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = tile * 128 + i * 32 + lane;
+      if (r < n)
+        m |= sorted_mask[static_cast<long long>(r) * words + w];
+    }
+    m = __reduce_or_sync(0xffffffffu, m);
+    if (lane == 0)
+      tile_masks[static_cast<long long>(tile) * words + w] = m;
+  }
 }
 
 template <typename K>

@@ -4,7 +4,9 @@ convolution calls, replacing the host generator of :mod:`cumm_b200.workloads` in
 The convention is the one :func:`cumm_b200.workloads.build_tables` documents and the tests compare
 bit for bit: offsets in (z, y, x) row-major order, ``indices [kv, n_out]`` with -1 for a missing
 neighbour, masks sorted ascending with a stable sort, active outputs of a strided convolution
-ordered by their linearised (batch, z, y, x)."""
+ordered by their linearised (batch, z, y, x).  Kernel volumes above 32 (up to 128) give masks
+``[n, words]`` (word w = offsets 32w .. 32w+31) sorted as one integer whose last word is the most
+significant, for the ``dynamic_mask`` kernels."""
 from __future__ import annotations
 
 import ctypes
@@ -49,17 +51,19 @@ def build_tables_gpu(in_coords, batch_size: int, grid: Sequence[int], ksize=(3, 
         a.n_out = n_out
         out_coords = in_coords if subm else torch.empty((n_out, 4), dtype=torch.int32, device=dev)
         indices = torch.empty((kv, n_out), dtype=torch.int32, device=dev)
-        mask = torch.empty((n_out,), dtype=torch.int32, device=dev)
+        words = (kv + 31) // 32
+        wide = (words,) if words > 1 else ()
+        mask = torch.empty((n_out,) + wide, dtype=torch.int32, device=dev)
         argsort = torch.empty((n_out,), dtype=torch.int32, device=dev)
         a.out_coords = 0 if subm else out_coords.data_ptr()
         a.indices, a.mask, a.mask_argsort = indices.data_ptr(), mask.data_ptr(), argsort.data_ptr()
         ibwd = mbwd = abwd = None
         if backward:
             ibwd = torch.empty((kv, n_in), dtype=torch.int32, device=dev)
-            mbwd = torch.empty((n_in,), dtype=torch.int32, device=dev)
+            mbwd = torch.empty((n_in,) + wide, dtype=torch.int32, device=dev)
             abwd = torch.empty((n_in,), dtype=torch.int32, device=dev)
             a.indices_bwd, a.mask_bwd, a.mask_argsort_bwd = ibwd.data_ptr(), mbwd.data_ptr(), abwd.data_ptr()
-        mask_output = torch.zeros(((n_out + 127) // 128,), dtype=torch.int32, device=dev)
+        mask_output = torch.zeros(((n_out + 127) // 128,) + wide, dtype=torch.int32, device=dev)
         a.tile_masks = mask_output.data_ptr()
         _lib.raise_for(L.cb2_pairgen_run(ctypes.byref(a), ctypes.c_void_p(stream)))
     # the kernels enqueued above still read the workspace: it lives as long as the tables do

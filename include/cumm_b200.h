@@ -266,6 +266,10 @@ int cb2_static_status(int *status);
  * masks keep their row order); the active outputs of a strided convolution are ordered by their
  * linearised (batch, z, y, x).  The backward arrays are the same for the transposed relation
  * (indices_bwd [kv, n_in], indices_bwd[f, i] = o iff indices[f, o] = i) and may be null.
+ * Kernel volumes above 32, up to 128 (the "dynamic mask" kernels): words = ceil(kv / 32) mask words
+ * per row, mask [n_out, words], mask_bwd [n_in, words], tile_masks [ceil(n_out / 128), words]; word
+ * w holds offsets 32w .. 32w+31, and rows are ordered as one integer whose LAST word is the most
+ * significant (stable).
  *
  * Submanifold (subm != 0): outputs are the inputs, n_out = n_in, one call of cb2_pairgen_run.
  * Otherwise call cb2_pairgen_count_outputs first (it finds and sorts the active outputs inside
@@ -285,10 +289,10 @@ typedef struct cb2_pairgen_args {
   int n_out;                /* subm: ignored (= n_in) */
   int32_t *out_coords;      /* [n_out, 4]; not written when subm */
   int32_t *indices;         /* [kv, n_out] */
-  uint32_t *mask;           /* [n_out] */
+  uint32_t *mask;           /* [n_out] ([n_out, words] for kernel volumes above 32) */
   int32_t *mask_argsort;    /* [n_out] */
   int32_t *indices_bwd;     /* [kv, n_in] or null */
-  uint32_t *mask_bwd;       /* [n_in] or null */
+  uint32_t *mask_bwd;       /* [n_in] ([n_in, words]) or null */
   int32_t *mask_argsort_bwd;/* [n_in] or null */
   void *workspace;          /* at least cb2_pairgen_workspace_size() bytes, 256-byte aligned */
   size_t workspace_bytes;

@@ -76,6 +76,20 @@ def test_regular_convolution(torch, stride, pad, dil, ksize):
     compare(torch, t, oc, W.build_tables(coords, grid=grid, **kw), False)
 
 
+@pytest.mark.parametrize("ksize,subm,stride", [((3, 3, 5), True, (1, 1, 1)), ((5, 5, 5), True, (1, 1, 1)),
+                                               ((4, 4, 4), False, (2, 2, 2)), ((2, 4, 5), False, (1, 2, 1))])
+def test_kernel_volumes_above_32(torch, ksize, subm, stride):
+    """Several mask words per row (45, 125, 64 and 40 offsets): masks [n, words], sorted as one
+    integer whose last word is the most significant, stable; per-tile masks per word."""
+    grid = (10, 26, 22)
+    coords = W.sample_coords(4000, 91, grid)
+    kw = dict(ksize=ksize, stride=stride, subm=subm)
+    t, oc = gpu_tables(torch, coords, 1, grid, **kw)
+    ref = W.build_tables(coords, grid=grid, **kw)
+    assert ref.mask.ndim == 2 and ref.mask.shape[1] == (t.kv + 31) // 32
+    compare(torch, t, oc, ref, subm)
+
+
 def test_benchmark_scene_full_size(torch):
     """The 150 000-voxel scene of the benchmark configurations, submanifold and stride 2."""
     coords = W.sample_coords(150000, 1)
@@ -120,3 +134,41 @@ def test_tables_feed_the_convolution(torch, oracle):
     H.check_status()
     want = oracle.mask_igemm(x, w, np.zeros((ref.n_out, 64), np.float16), ref.indices, ref.mask, ref.mask_argsort)
     H.assert_close_f16(out.cpu().numpy(), want, "forward on GPU-built tables")
+
+
+def test_wide_tables_feed_the_convolution(torch, oracle):
+    """Tables of a 3x3x5 kernel (45 offsets, two mask words per row) from the GPU builder drive the
+    forward kernel and, through the backward tables, the input gradient."""
+    from cumm_b200.conv.main import ConvMainUnitTest
+    from cumm_b200.tensorview.gemm import ConvOpType, ConvParams
+    grid, ksize, C, K = (8, 24, 24), (3, 3, 5), 64, 64
+    kv = 45
+    coords = W.sample_coords(3000, 93, grid)
+    t, _ = gpu_tables(torch, coords, 1, grid, ksize=ksize)
+    ref = W.build_tables(coords, grid=grid, ksize=ksize)
+    rng = np.random.default_rng(94)
+    x = rng.standard_normal((ref.n_in, C)).astype(np.float16)
+    dout = rng.standard_normal((ref.n_out, K)).astype(np.float16)
+    w = (rng.standard_normal((K, kv, C)) / np.sqrt(kv * C) * 4).astype(np.float16)
+    for op, src, tabs, rtabs in ((ConvOpType.Forward, x, (t.indices, t.mask, t.mask_argsort),
+                                  (ref.indices, ref.mask, ref.mask_argsort)),
+                                 (ConvOpType.BackwardInput, dout, (t.indices_bwd, t.mask_bwd, t.mask_argsort_bwd),
+                                  (ref.indices_bwd, ref.mask_bwd, ref.mask_argsort_bwd))):
+        p = ConvParams(3, op)
+        p.conv_algo_desp = H.conv_desp(op, C, K)
+        p.conv_algo_desp.dynamic_mask = True
+        out = torch.zeros((ref.n_out, K) if op == ConvOpType.Forward else (ref.n_in, C), dtype=torch.float16, device="cuda")
+        if op == ConvOpType.Forward:
+            p.input, p.output = H.dev(src, torch), out
+        else:
+            p.input, p.output = out, H.dev(src, torch)
+        p.weight = H.dev(w, torch)
+        p.indices, p.mask, p.mask_argsort = tabs
+        ConvMainUnitTest.implicit_gemm2(p)
+        torch.cuda.synchronize()
+        H.check_status()
+        if op == ConvOpType.Forward:
+            want = oracle.mask_igemm(src, w, np.zeros((ref.n_out, K), np.float16), *rtabs)
+        else:
+            want = oracle.mask_igemm(src, w, np.zeros((ref.n_in, C), np.float16), *rtabs, is_dgrad=True)
+        H.assert_close_f16(out.cpu().numpy(), want, f"{op.name} on GPU-built two-word tables")

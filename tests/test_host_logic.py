@@ -219,7 +219,8 @@ def test_table_builder_workspace_size_is_a_host_function():
     assert 0 < s1 < s2
     assert size(150000, False, stride=(2, 2, 2)) > s1  # the strided case also holds the output set and lists
     assert size(150000, True, stride=(2, 2, 2)) == 0   # a submanifold convolution has stride 1
-    assert size(150000, True, ksize=(3, 3, 5)) == 0    # kernel volume 45 > 32 mask bits
+    assert size(150000, True, ksize=(3, 3, 5)) > size(150000, True)   # kernel volume 45: two mask words per row
+    assert size(150000, True, ksize=(5, 5, 6)) == 0    # kernel volume 150 > 128
     assert size(150000, True, grid=(0, 10, 10)) == 0
     assert size(150000, True, batch=0) == 0
 
